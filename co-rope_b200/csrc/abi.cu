@@ -1,0 +1,197 @@
+// extern "C" entry points of libcorope_b200.so: argument validation, workspace carving, kernel selection.
+#include <atomic>
+
+#include "common.cuh"
+
+namespace corope {
+namespace {
+
+std::atomic<int> g_policy{0};
+std::atomic<int> g_last_family[4] = {{0}, {0}, {0}, {0}};
+
+constexpr size_t kAlign = 256;
+
+bool head_dim_ok(int D) { return D == 32 || D == 64 || D == 128; }
+
+struct RopeWorkspace {
+    size_t packed_tab, delta, dq_acc, total;
+};
+
+RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dtype) {
+    RopeWorkspace w{};
+    size_t off = 0;
+    w.packed_tab = off;
+    off += align_up((size_t)N * (D / 2) * sizeof(uint32_t), kAlign);
+    if (bwd) {
+        w.delta = off;
+        off += align_up((size_t)B * H * N * sizeof(float), kAlign);
+        w.dq_acc = off;
+        if (dtype != COROPE_DTYPE_F32 && D == 128) off += align_up((size_t)B * H * N * D * sizeof(float), kAlign);
+    }
+    w.total = off < kAlign ? kAlign : off;
+    return w;
+}
+
+struct GqaWorkspace {
+    size_t delta, dk_acc, dv_acc, total;
+};
+
+GqaWorkspace gqa_workspace_layout(bool bwd, int B, int Hq, int Hkv, int N, int D) {
+    GqaWorkspace w{};
+    size_t off = 0;
+    if (bwd) {
+        w.delta = off;
+        off += align_up((size_t)B * Hq * N * sizeof(float), kAlign);
+        w.dk_acc = off;
+        off += align_up((size_t)B * Hkv * N * D * sizeof(float), kAlign);
+        w.dv_acc = off;
+        off += align_up((size_t)B * Hkv * N * D * sizeof(float), kAlign);
+    }
+    w.total = off < kAlign ? kAlign : off;
+    return w;
+}
+
+int check_common(int B, int H, int N, int D, int dtype) {
+    if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return COROPE_ERR_BAD_SHAPE;
+    if (!head_dim_ok(D)) return COROPE_ERR_BAD_HEAD_DIM;
+    if (dtype != COROPE_DTYPE_F32 && dtype != COROPE_DTYPE_BF16 && dtype != COROPE_DTYPE_F16) return COROPE_ERR_BAD_DTYPE;
+    if ((size_t)B * H > 65535u * 32u) return COROPE_ERR_TOO_LARGE;
+    return COROPE_OK;
+}
+
+int check_workspace(const void* ws, size_t have, size_t need) {
+    if (!ws || have < need || ((uintptr_t)ws % kAlign) != 0) return COROPE_ERR_WORKSPACE;
+    return COROPE_OK;
+}
+
+}  // namespace
+}  // namespace corope
+
+using namespace corope;
+
+extern "C" {
+
+int corope_abi_version(void) { return 1; }
+
+const char* corope_status_string(int status) {
+    switch (status) {
+        case COROPE_OK: return "ok";
+        case COROPE_ERR_NULL_POINTER: return "null pointer argument";
+        case COROPE_ERR_BAD_SHAPE: return "non-positive tensor extent";
+        case COROPE_ERR_BAD_HEAD_DIM: return "unsupported head dimension (supported: 32, 64, 128)";
+        case COROPE_ERR_BAD_DTYPE: return "unsupported element type";
+        case COROPE_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+        case COROPE_ERR_BAD_GROUP: return "query heads must be a multiple of KV heads with group size <= 8";
+        case COROPE_ERR_SEQ_NOT_128: return "sequence length must be a multiple of 128";
+        case COROPE_ERR_TENSOR_MAP: return "TMA tensor map could not be encoded";
+        case COROPE_ERR_NO_DEVICE: return "no usable CUDA device or driver entry point";
+        case COROPE_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString((cudaError_t)status);
+    return "unknown status";
+}
+
+size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int dtype) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || D <= 0) return 0;
+    switch (op) {
+        case COROPE_OP_ROPE_FWD: return rope_workspace_layout(false, B, Hq, N, D, dtype).total;
+        case COROPE_OP_ROPE_BWD: return rope_workspace_layout(true, B, Hq, N, D, dtype).total;
+        case COROPE_OP_GQA_FWD: return gqa_workspace_layout(false, B, Hq, Hkv, N, D).total;
+        case COROPE_OP_GQA_BWD: return gqa_workspace_layout(true, B, Hq, Hkv, N, D).total;
+        default: return 0;
+    }
+}
+
+int corope_set_kernel_policy(int policy) { return g_policy.exchange(policy); }
+
+int corope_last_kernel_family(int op) { return (op >= 0 && op < 4) ? g_last_family[op].load() : -1; }
+
+int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const float* cos, const float* sin, int64_t table_row_stride, void* o,
+                         float* lse2, int B, int H, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
+                         size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !cos || !sin || !o || !lse2) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_common(B, H, N, D, dtype)) return e;
+    RopeWorkspace w = rope_workspace_layout(false, B, H, N, D, dtype);
+    if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    RopeParams p{};
+    p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
+    p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    if (g_policy.load() == 0 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
+        uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
+        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
+        p.packed_tab = tab;
+        g_last_family[COROPE_OP_ROPE_FWD] = 1;
+        return launch_rope_fwd_tc(p, dtype, s);
+    }
+    g_last_family[COROPE_OP_ROPE_FWD] = 0;
+    return launch_rope_fwd_general(p, dtype, s);
+}
+
+int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, const float* cos,
+                         const float* sin, int64_t table_row_stride, void* dq, void* dk, void* dv, int B, int H, int N, int D, int dtype,
+                         int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !o || !d_o || !lse2 || !cos || !sin || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_common(B, H, N, D, dtype)) return e;
+    RopeWorkspace w = rope_workspace_layout(true, B, H, N, D, dtype);
+    if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    RopeParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.dq = dq; p.dk = dk; p.dv = dv;
+    p.lse2 = const_cast<float*>(lse2);
+    p.delta = reinterpret_cast<float*>((char*)workspace + w.delta);
+    p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
+    p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    if (int e = launch_rope_delta(p, dtype, s)) return e;
+    if (g_policy.load() == 0 && rope_bwd_tc_supported(B, H, N, D, dtype, causal)) {
+        uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
+        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
+        p.packed_tab = tab;
+        p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
+        g_last_family[COROPE_OP_ROPE_BWD] = 1;
+        return launch_rope_bwd_tc(p, dtype, s);
+    }
+    g_last_family[COROPE_OP_ROPE_BWD] = 0;
+    return launch_rope_bwd_general(p, dtype, s);
+}
+
+static int check_gqa(int B, int Hq, int Hkv, int N, int D, int dtype) {
+    if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || D <= 0) return COROPE_ERR_BAD_SHAPE;
+    if (Hq % Hkv != 0 || Hq / Hkv > 8) return COROPE_ERR_BAD_GROUP;
+    return check_common(B, Hq, N, D, dtype);
+}
+
+int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, float* a_diag, int B, int Hq, int Hkv, int N, int D,
+                   int dtype, float sm_scale, float theta, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !o || !lse2 || !a_diag) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
+    GqaWorkspace w = gqa_workspace_layout(false, B, Hq, Hkv, N, D);
+    if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
+    GqaParams p{};
+    p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2; p.a_diag = a_diag;
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
+    g_last_family[COROPE_OP_GQA_FWD] = 0;
+    return launch_gqa_fwd_general(p, dtype, (cudaStream_t)stream);
+}
+
+int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, const float* a_diag,
+                   void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
+                   void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !o || !d_o || !lse2 || !a_diag || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
+    GqaWorkspace w = gqa_workspace_layout(true, B, Hq, Hkv, N, D);
+    if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
+    GqaParams p{};
+    p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.dq = dq; p.dk = dk; p.dv = dv;
+    p.lse2 = const_cast<float*>(lse2); p.a_diag = const_cast<float*>(a_diag);
+    p.delta = reinterpret_cast<float*>((char*)workspace + w.delta);
+    p.dk_acc = reinterpret_cast<float*>((char*)workspace + w.dk_acc);
+    p.dv_acc = reinterpret_cast<float*>((char*)workspace + w.dv_acc);
+    p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
+    g_last_family[COROPE_OP_GQA_BWD] = 0;
+    return launch_gqa_bwd_general(p, dtype, (cudaStream_t)stream);
+}
+
+}  // extern "C"

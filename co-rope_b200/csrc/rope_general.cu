@@ -1,0 +1,442 @@
+// General fused-RoPE attention kernels: fp32 arithmetic on the CUDA cores, any N, causal or not,
+// D in {32, 64, 128}, inputs fp32 / bf16 / fp16.  This is the accuracy path (fp32 inputs must match
+// the fp32 reference to 1e-4, which rules out 16-bit tensor-core operands) and the path for shapes the
+// tensor-core kernels do not take.  Q and every K tile are rotated while being staged into shared
+// memory; rotated values never go back to HBM.
+//
+// Tiling: one CTA = 32 rows (queries for fwd / dQ, keys for dK / dV), 4 warps x 8 rows; the other
+// operand streams through shared memory in tiles of 32.  Within a warp, lane = column of the
+// 32 x 32 score tile for the dot products, and lane = head-dim column (lane + 32 c) for the
+// accumulators.
+//
+// Math follows fused-rope/rope_attn_pytorch.py:108-155 (forward) and :187-222 (backward); the exp2-domain
+// softmax and the log2-domain LSE follow fused-rope/fused_rope_attn.py:103-114, 316.
+#include "common.cuh"
+
+namespace corope {
+namespace {
+
+constexpr int kRows = 32;     // rows per CTA
+constexpr int kTile = 32;     // streamed rows per step
+constexpr int kThreads = 128;
+constexpr int kRowsPerWarp = 8;
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Stage `kTile` rows [r0, r0+32) of X[N][D] into dst[32][LD] as fp32, rotated by the half-layout RoPE
+// and multiplied by `scale`.  Rows >= N become zeros.
+template <typename T, int D, int LD, bool ROTATE>
+__device__ __forceinline__ void stage_rows(float* dst, const T* X, int r0, int N, const float* cosT, const float* sinT, int64_t ts,
+                                           float scale) {
+    constexpr int H2 = D / 2;
+    for (int idx = threadIdx.x; idx < kTile * H2; idx += kThreads) {
+        int r = idx / H2, d = idx % H2;
+        int pos = r0 + r;
+        float y1 = 0.f, y2 = 0.f;
+        if (pos < N) {
+            float x1 = Elem<T>::to_f32(X[(size_t)pos * D + d]);
+            float x2 = Elem<T>::to_f32(X[(size_t)pos * D + d + H2]);
+            if (ROTATE) {
+                float c = cosT[pos * ts + d], s = sinT[pos * ts + d];
+                y1 = (x1 * c - x2 * s) * scale;
+                y2 = (x2 * c + x1 * s) * scale;
+            } else {
+                y1 = x1 * scale;
+                y2 = x2 * scale;
+            }
+        }
+        dst[r * LD + d] = y1;
+        dst[r * LD + d + H2] = y2;
+    }
+}
+
+// 8 x 32 tile of dot products: out[r] = sum_d A[(row0 + r)][d] * Bp[lane][d]; A rows broadcast (stride D),
+// B rows per lane (stride D + 1, conflict-free).
+template <int D>
+__device__ __forceinline__ void dot_rows(float (&out)[kRowsPerWarp], const float* A, int row0, const float* Bp, int lane) {
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) out[r] = 0.f;
+    const float* b = Bp + lane * (D + 1);
+#pragma unroll 4
+    for (int d = 0; d < D; d += 4) {
+        float b0 = b[d], b1 = b[d + 1], b2 = b[d + 2], b3 = b[d + 3];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            float4 a = *reinterpret_cast<const float4*>(A + (row0 + r) * D + d);
+            out[r] = fmaf(a.x, b0, out[r]);
+            out[r] = fmaf(a.y, b1, out[r]);
+            out[r] = fmaf(a.z, b2, out[r]);
+            out[r] = fmaf(a.w, b3, out[r]);
+        }
+    }
+}
+
+// acc[r][c] += sum_j w[r] (held by lane j) * Bp[j][lane + 32 c]
+template <int D, int LD>
+__device__ __forceinline__ void accumulate_cols(float (&acc)[kRowsPerWarp][(D + 31) / 32], const float (&w)[kRowsPerWarp], const float* Bp,
+                                                int lane) {
+    constexpr int NC = D / 32;
+#pragma unroll 4
+    for (int j = 0; j < kTile; ++j) {
+        float bv[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) bv[c] = Bp[j * LD + lane + 32 * c];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            float wj = __shfl_sync(0xffffffffu, w[r], j);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[r][c] = fmaf(wj, bv[c], acc[r][c]);
+        }
+    }
+}
+
+// Inverse rotation of a row held as columns (lane + 32 c), then * scale, stored as T.
+template <typename T, int D>
+__device__ __forceinline__ void store_inverse_rotated(T* dst_row, const float (&a)[(D + 31) / 32], int pos, const float* cosT,
+                                                      const float* sinT, int64_t ts, float scale, int lane, bool rotate) {
+    constexpr int NC = D / 32;
+    constexpr int H2 = D / 2;
+    if (D == 32) {
+        float other = __shfl_xor_sync(0xffffffffu, a[0], 16);
+        int d = lane & 15;
+        float c = rotate ? cosT[pos * ts + d] : 1.f, s = rotate ? sinT[pos * ts + d] : 0.f;
+        float g = lane < 16 ? (a[0] * c + other * s) : (a[0] * c - other * s);
+        dst_row[lane] = Elem<T>::from_f32(g * scale);
+    } else {
+#pragma unroll
+        for (int c2 = 0; c2 < NC / 2; ++c2) {
+            int d = lane + 32 * c2;
+            float c = rotate ? cosT[pos * ts + d] : 1.f, s = rotate ? sinT[pos * ts + d] : 0.f;
+            float a1 = a[c2], a2 = a[c2 + NC / 2];
+            dst_row[d] = Elem<T>::from_f32((a1 * c + a2 * s) * scale);
+            dst_row[d + H2] = Elem<T>::from_f32((a2 * c - a1 * s) * scale);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// forward
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p) {
+    constexpr int NC = D / 32;
+    extern __shared__ __align__(16) float smem[];
+    float* q_s = smem;                       // [32][D]     rotated * sm_scale * log2e
+    float* k_s = q_s + kRows * D;            // [32][D+1]   rotated
+    float* v_s = k_s + kTile * (D + 1);      // [32][D]
+
+    const int N = p.N;
+    const int bh = blockIdx.y;
+    const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;  // longest causal rows first
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* Q = reinterpret_cast<const T*>(p.q) + (size_t)bh * N * D;
+    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bh * N * D;
+    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bh * N * D;
+    T* O = reinterpret_cast<T*>(p.out_o) + (size_t)bh * N * D;
+
+    stage_rows<T, D, D, true>(q_s, Q, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+
+    float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][NC];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        m[r] = -INFINITY;
+        l[r] = 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
+    }
+    const int row0 = warp * kRowsPerWarp;
+    const int n_end = p.causal ? min(N, m0 + kRows) : N;
+    for (int j0 = 0; j0 < n_end; j0 += kTile) {
+        __syncthreads();
+        stage_rows<T, D, D + 1, true>(k_s, K, j0, N, p.cos, p.sin, p.table_stride, 1.f);
+        stage_rows<T, D, D, false>(v_s, V, j0, N, nullptr, nullptr, 0, 1.f);
+        __syncthreads();
+        float s[kRowsPerWarp];
+        dot_rows<D>(s, q_s, row0, k_s, lane);
+        const int j = j0 + lane;
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int i = m0 + row0 + r;
+            bool ok = (j < N) && (!p.causal || j <= i);
+            float sv = ok ? s[r] : -INFINITY;
+            float mx = fmaxf(m[r], warp_max(sv));
+            float alpha = (mx == -INFINITY) ? 1.f : exp2f(m[r] - mx);
+            float pv = (mx == -INFINITY || !ok) ? 0.f : exp2f(sv - mx);
+            l[r] = l[r] * alpha + warp_sum(pv);
+            m[r] = mx;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) acc[r][c] *= alpha;
+            s[r] = pv;
+        }
+        accumulate_cols<D, D>(acc, s, v_s, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int i = m0 + row0 + r;
+        if (i >= N) continue;
+        float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) O[(size_t)i * D + lane + 32 * c] = Elem<T>::from_f32(acc[r][c] * inv);
+        if (lane == 0) p.lse2[(size_t)bh * N + i] = m[r] + log2f(l[r]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// delta = rowsum(O * dO)   (fused_rope_attn.py:324-337)
+// ------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D) {
+    size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float s = 0.f;
+    for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(o[row * D + d]) * Elem<T>::to_f32(d_o[row * D + d]);
+    s = warp_sum(s);
+    if (lane == 0) delta[row] = s;
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, dQ: one CTA per 32 query rows, streams K/V tiles
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParams p) {
+    constexpr int NC = D / 32;
+    extern __shared__ __align__(16) float smem[];
+    float* q_s = smem;                        // [32][D]   rotated * sm_scale * log2e
+    float* do_s = q_s + kRows * D;            // [32][D]
+    float* k_s = do_s + kRows * D;            // [32][D+1] rotated
+    float* v_s = k_s + kTile * (D + 1);       // [32][D+1]
+
+    const int N = p.N;
+    const int bh = blockIdx.y;
+    const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t base = (size_t)bh * N * D;
+    const T* Q = reinterpret_cast<const T*>(p.q) + base;
+    const T* K = reinterpret_cast<const T*>(p.k) + base;
+    const T* V = reinterpret_cast<const T*>(p.v) + base;
+    const T* DO = reinterpret_cast<const T*>(p.d_o) + base;
+    T* DQ = reinterpret_cast<T*>(p.dq) + base;
+
+    stage_rows<T, D, D, true>(q_s, Q, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+    stage_rows<T, D, D, false>(do_s, DO, m0, N, nullptr, nullptr, 0, 1.f);
+
+    const int row0 = warp * kRowsPerWarp;
+    float lse[kRowsPerWarp], dl[kRowsPerWarp], acc[kRowsPerWarp][NC];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int i = m0 + row0 + r;
+        lse[r] = i < N ? p.lse2[(size_t)bh * N + i] : 0.f;
+        dl[r] = i < N ? p.delta[(size_t)bh * N + i] : 0.f;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
+    }
+    const int n_end = p.causal ? min(N, m0 + kRows) : N;
+    for (int j0 = 0; j0 < n_end; j0 += kTile) {
+        __syncthreads();
+        stage_rows<T, D, D + 1, true>(k_s, K, j0, N, p.cos, p.sin, p.table_stride, 1.f);
+        stage_rows<T, D, D + 1, false>(v_s, V, j0, N, nullptr, nullptr, 0, 1.f);
+        __syncthreads();
+        float s[kRowsPerWarp], dp[kRowsPerWarp];
+        dot_rows<D>(s, q_s, row0, k_s, lane);
+        dot_rows<D>(dp, do_s, row0, v_s, lane);
+        const int j = j0 + lane;
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int i = m0 + row0 + r;
+            bool ok = (j < N) && (i < N) && (!p.causal || j <= i);
+            float pv = ok ? exp2f(s[r] - lse[r]) : 0.f;
+            s[r] = pv * (dp[r] - dl[r]);
+        }
+        accumulate_cols<D, D + 1>(acc, s, k_s, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int i = m0 + row0 + r;
+        if (i >= N) continue;  // warp-uniform: i does not depend on the lane
+        store_inverse_rotated<T, D>(DQ + (size_t)i * D, acc[r], i, p.cos, p.sin, p.table_stride, p.sm_scale, lane, true);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, dK / dV: one CTA per 32 keys, streams Q / dO tiles
+// ------------------------------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopeParams p) {
+    constexpr int NC = D / 32;
+    extern __shared__ __align__(16) float smem[];
+    float* k_s = smem;                        // [32][D]   rotated
+    float* v_s = k_s + kRows * D;             // [32][D]
+    float* q_s = v_s + kRows * D;             // [32][D+1] rotated * sm_scale * log2e
+    float* do_s = q_s + kTile * (D + 1);      // [32][D+1]
+    float* lse_s = do_s + kTile * (D + 1);    // [32]
+    float* dl_s = lse_s + kTile;              // [32]
+
+    const int N = p.N;
+    const int bh = blockIdx.y;
+    const int n0 = blockIdx.x * kRows;  // causal: low key blocks are the long ones and come first
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t base = (size_t)bh * N * D;
+    const T* Q = reinterpret_cast<const T*>(p.q) + base;
+    const T* K = reinterpret_cast<const T*>(p.k) + base;
+    const T* V = reinterpret_cast<const T*>(p.v) + base;
+    const T* DO = reinterpret_cast<const T*>(p.d_o) + base;
+    T* DK = reinterpret_cast<T*>(p.dk) + base;
+    T* DV = reinterpret_cast<T*>(p.dv) + base;
+
+    stage_rows<T, D, D, true>(k_s, K, n0, N, p.cos, p.sin, p.table_stride, 1.f);
+    stage_rows<T, D, D, false>(v_s, V, n0, N, nullptr, nullptr, 0, 1.f);
+
+    const int row0 = warp * kRowsPerWarp;
+    float dk[kRowsPerWarp][NC], dv[kRowsPerWarp][NC];
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r)
+#pragma unroll
+        for (int c = 0; c < NC; ++c) dk[r][c] = dv[r][c] = 0.f;
+
+    const int i_begin = p.causal ? n0 : 0;
+    for (int i0 = i_begin; i0 < N; i0 += kTile) {
+        __syncthreads();
+        stage_rows<T, D, D + 1, true>(q_s, Q, i0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+        stage_rows<T, D, D + 1, false>(do_s, DO, i0, N, nullptr, nullptr, 0, 1.f);
+        if (threadIdx.x < kTile) {
+            int i = i0 + threadIdx.x;
+            lse_s[threadIdx.x] = i < N ? p.lse2[(size_t)bh * N + i] : 0.f;
+            dl_s[threadIdx.x] = i < N ? p.delta[(size_t)bh * N + i] : 0.f;
+        }
+        __syncthreads();
+        float s[kRowsPerWarp], dp[kRowsPerWarp];
+        dot_rows<D>(s, k_s, row0, q_s, lane);
+        dot_rows<D>(dp, v_s, row0, do_s, lane);
+        const int i = i0 + lane;
+        const float lse = lse_s[lane], dl = dl_s[lane];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+            const int j = n0 + row0 + r;
+            bool ok = (j < N) && (i < N) && (!p.causal || j <= i);
+            float pv = ok ? exp2f(s[r] - lse) : 0.f;
+            s[r] = pv;
+            dp[r] = pv * (dp[r] - dl);
+        }
+        accumulate_cols<D, D + 1>(dv, s, do_s, lane);
+        accumulate_cols<D, D + 1>(dk, dp, q_s, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int j = n0 + row0 + r;
+        if (j >= N) continue;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) DV[(size_t)j * D + lane + 32 * c] = Elem<T>::from_f32(dv[r][c]);
+        // q_s carried sm_scale * log2e, so dk holds dK~ * log2e: undo with ln2
+        store_inverse_rotated<T, D>(DK + (size_t)j * D, dk[r], j, p.cos, p.sin, p.table_stride, kLn2, lane, true);
+    }
+}
+
+// cos/sin fp32 tables -> compact [N][D/2] half2 (cos, sin) pairs for the tensor-core kernels
+__global__ void pack_tables_kernel(const float* __restrict__ cosT, const float* __restrict__ sinT, int64_t ts, uint32_t* __restrict__ out,
+                                   int N, int half_d) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)N * half_d) return;
+    int n = (int)(idx / half_d), d = (int)(idx % half_d);
+    out[idx] = pack_half2(cosT[n * ts + d], sinT[n * ts + d]);
+}
+
+template <typename T, int D>
+int launch_fwd_t(const RopeParams& p, cudaStream_t s) {
+    size_t smem = sizeof(float) * (kRows * D + kTile * (D + 1) + kTile * D);
+    auto kern = rope_fwd_general_kernel<T, D>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    dim3 grid((p.N + kRows - 1) / kRows, p.B * p.H);
+    kern<<<grid, kThreads, smem, s>>>(p);
+    return (int)cudaGetLastError();
+}
+
+template <typename T, int D>
+int launch_bwd_t(const RopeParams& p, cudaStream_t s) {
+    dim3 grid((p.N + kRows - 1) / kRows, p.B * p.H);
+    {
+        size_t smem = sizeof(float) * (2 * kRows * D + 2 * kTile * (D + 1));
+        auto kern = rope_bwd_dq_general_kernel<T, D>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, s>>>(p);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return (int)e;
+    }
+    {
+        size_t smem = sizeof(float) * (2 * kRows * D + 2 * kTile * (D + 1) + 2 * kTile);
+        auto kern = rope_bwd_dkdv_general_kernel<T, D>;
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, smem, s>>>(p);
+        return (int)cudaGetLastError();
+    }
+}
+
+template <typename T>
+int dispatch_d(const RopeParams& p, cudaStream_t s, bool bwd) {
+    switch (p.D) {
+        case 32: return bwd ? launch_bwd_t<T, 32>(p, s) : launch_fwd_t<T, 32>(p, s);
+        case 64: return bwd ? launch_bwd_t<T, 64>(p, s) : launch_fwd_t<T, 64>(p, s);
+        case 128: return bwd ? launch_bwd_t<T, 128>(p, s) : launch_fwd_t<T, 128>(p, s);
+        default: return COROPE_ERR_BAD_HEAD_DIM;
+    }
+}
+
+}  // namespace
+
+int launch_rope_fwd_general(const RopeParams& p, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case COROPE_DTYPE_F32: return dispatch_d<float>(p, s, false);
+        case COROPE_DTYPE_BF16: return dispatch_d<__nv_bfloat16>(p, s, false);
+        case COROPE_DTYPE_F16: return dispatch_d<__half>(p, s, false);
+        default: return COROPE_ERR_BAD_DTYPE;
+    }
+}
+
+int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s) {
+    switch (dtype) {
+        case COROPE_DTYPE_F32: return dispatch_d<float>(p, s, true);
+        case COROPE_DTYPE_BF16: return dispatch_d<__nv_bfloat16>(p, s, true);
+        case COROPE_DTYPE_F16: return dispatch_d<__half>(p, s, true);
+        default: return COROPE_ERR_BAD_DTYPE;
+    }
+}
+
+int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
+    size_t rows = (size_t)p.B * p.H * p.N;
+    const int warps = 8;
+    unsigned blocks = (unsigned)((rows + warps - 1) / warps);
+    switch (dtype) {
+        case COROPE_DTYPE_F32:
+            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D);
+            break;
+        case COROPE_DTYPE_BF16:
+            rope_delta_kernel<__nv_bfloat16>
+                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D);
+            break;
+        case COROPE_DTYPE_F16:
+            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D);
+            break;
+        default: return COROPE_ERR_BAD_DTYPE;
+    }
+    return (int)cudaGetLastError();
+}
+
+int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s) {
+    size_t n = (size_t)N * half_d;
+    pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace corope

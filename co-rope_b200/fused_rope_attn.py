@@ -1,0 +1,91 @@
+"""Drop-in for the reference's `fused_rope_attn.attention` (fused-rope/fused_rope_attn.py:652-780).
+
+    attention(q, k, v, causal, sm_scale, freqs_cos, freqs_sin, warp_specialize=True) -> o
+
+q, k, v: [B, H, N, D] CUDA tensors of one dtype (bf16, fp16 or fp32).  freqs_cos / freqs_sin: [N, D]
+("cat" layout of precompute_freqs_cis) or [N, D/2]; only columns [0, D/2) are read, as in the
+reference (fused_rope_attn.py:88-93).  Positional-only, like torch.autograd.Function.apply.
+The CUDA kernels are reached through the C ABI in include/corope_b200.h.
+"""
+
+import torch
+
+try:
+    from . import _ext
+except ImportError:  # imported as a top-level module (directory on sys.path, the way the reference's scripts import it)
+    import _ext
+
+SUPPORTED_HEAD_DIMS = (32, 64, 128)
+
+
+def _tables(freqs_cos, freqs_sin, N, D, device):
+    if freqs_cos.shape != freqs_sin.shape or freqs_cos.dim() != 2:
+        raise ValueError("freqs_cos and freqs_sin must be 2-D tensors of the same shape")
+    if freqs_cos.shape[0] < N or freqs_cos.shape[1] < D // 2:
+        raise ValueError("RoPE tables must cover [N, D/2] = [%d, %d], got %s" % (N, D // 2, tuple(freqs_cos.shape)))
+    out = []
+    for t in (freqs_cos, freqs_sin):
+        _ext.require_cuda(t)
+        if t.dtype != torch.float32 or t.stride(1) != 1:
+            t = t.float().contiguous()
+        out.append(t)
+    if out[0].stride(0) != out[1].stride(0):
+        out = [t.contiguous() for t in out]
+    return out[0], out[1], out[0].stride(0)
+
+
+class _attention(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, freqs_cos, freqs_sin, warp_specialize=True):
+        # shape constraints, as fused_rope_attn.py:657-661
+        HEAD_DIM_Q, HEAD_DIM_K = q.shape[-1], k.shape[-1]
+        HEAD_DIM_V = v.shape[-1]
+        assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+        assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+        assert HEAD_DIM_K in SUPPORTED_HEAD_DIMS, "corope_b200 supports head dims %s" % (SUPPORTED_HEAD_DIMS,)
+        assert q.shape == k.shape == v.shape and q.dim() == 4
+        assert q.dtype == k.dtype == v.dtype and q.dtype in _ext.DTYPE_CODES
+        for t in (q, k, v):
+            _ext.require_cuda(t)
+        B, H, N, D = q.shape
+        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+        cos, sin, tstride = _tables(freqs_cos, freqs_sin, N, D, q.device)
+        o = torch.empty_like(qc)
+        M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+        ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD, B, H, H, N, D, q.dtype, q.device)
+        with torch.cuda.device(q.device):
+            rc = _ext.lib().corope_rope_attn_fwd(
+                qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), tstride,
+                o.data_ptr(), M.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
+                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+        _ext.raise_for_status(rc, "corope_rope_attn_fwd")
+        ctx.save_for_backward(qc, kc, vc, o, M, cos, sin)
+        ctx.sm_scale = sm_scale
+        ctx.HEAD_DIM = D
+        ctx.causal = causal
+        ctx.tstride = tstride
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, M, cos, sin = ctx.saved_tensors
+        # the reference asserts contiguity and N % 128 == 0 (fused_rope_attn.py:727-728, 750); these kernels take any
+        # N, and a non-contiguous dO is made contiguous instead of rejected
+        do = do.contiguous()
+        B, H, N, D = q.shape
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD, B, H, H, N, D, q.dtype, q.device)
+        with torch.cuda.device(q.device):
+            rc = _ext.lib().corope_rope_attn_bwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
+                cos.data_ptr(), sin.data_ptr(), ctx.tstride, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(ctx.causal)), float(ctx.sm_scale),
+                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+        _ext.raise_for_status(rc, "corope_rope_attn_bwd")
+        return dq, dk, dv, None, None, None, None, None
+
+
+attention = _attention.apply

@@ -1,0 +1,127 @@
+/*
+ * corope_b200 -- C ABI of the B200 (sm_100a) fused-RoPE attention and Co-RoPE GQA attention kernels.
+ *
+ * Plain pointers and sizes only; no C++ or torch types cross this boundary.  All tensor
+ * pointers are DEVICE pointers.  q/k/v/o/dO/dq/dk/dv are row-major contiguous [B, H, N, D]
+ * in the element type named by `dtype`.  Every call enqueues work on `stream` (a
+ * cudaStream_t passed as void*) and returns without synchronising.
+ *
+ * Return value: 0 = OK, < 0 = argument error found on the host (nothing was launched),
+ * > 0 = a cudaError_t from a launch.  Kernels never trap: a device-side bounded wait that
+ * expires writes a non-zero code into `*status_word` (device memory, may be NULL) and the
+ * kernel exits cleanly.
+ *
+ * Each entry point names the interface of the reference (Superposition09m/Co-RoPE) it stands in for.
+ */
+#ifndef COROPE_B200_H_
+#define COROPE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of q/k/v/o and gradients */
+#define COROPE_DTYPE_F32 0
+#define COROPE_DTYPE_BF16 1
+#define COROPE_DTYPE_F16 2
+
+/* `op` values for corope_workspace_bytes */
+#define COROPE_OP_ROPE_FWD 0
+#define COROPE_OP_ROPE_BWD 1
+#define COROPE_OP_GQA_FWD 2
+#define COROPE_OP_GQA_BWD 3
+
+/* host-side argument errors */
+#define COROPE_OK 0
+#define COROPE_ERR_NULL_POINTER (-1)
+#define COROPE_ERR_BAD_SHAPE (-2)      /* non-positive extent */
+#define COROPE_ERR_BAD_HEAD_DIM (-3)   /* D outside the supported set (fused_rope_attn.py:661 asserts the same way) */
+#define COROPE_ERR_BAD_DTYPE (-4)
+#define COROPE_ERR_WORKSPACE (-5)      /* workspace missing, too small or misaligned (needs 256-byte alignment) */
+#define COROPE_ERR_BAD_GROUP (-6)      /* Hq % Hkv != 0 or group size > 8 (flash_attn_co_rope_gqa_triton.py:421-425) */
+#define COROPE_ERR_SEQ_NOT_128 (-7)    /* backward needs N % 128 == 0 (fused_rope_attn.py:750) -- only when strict_n is set */
+#define COROPE_ERR_TENSOR_MAP (-8)     /* TMA descriptor could not be encoded */
+#define COROPE_ERR_NO_DEVICE (-9)      /* no sm_100 device / driver entry point */
+#define COROPE_ERR_TOO_LARGE (-10)     /* size beyond what the entry point supports */
+
+/* device-side status codes written to *status_word */
+#define COROPE_DEV_OK 0
+#define COROPE_DEV_WAIT_EXPIRED 0x1000 /* | barrier id: a bounded mbarrier wait ran out */
+
+int corope_abi_version(void);
+const char* corope_status_string(int status);
+
+/* Bytes of caller-provided scratch (device memory, 256-byte aligned) an op needs.  Contents
+ * need not be initialised by the caller.  For MHA pass Hkv == Hq. */
+size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int dtype);
+
+/*
+ * Fused RoPE attention forward.  Replaces the launch in _attention.forward
+ * (fused-rope/fused_rope_attn.py:655-722, kernels _attn_fwd / _attn_fwd_inner :47-320).
+ *   cos, sin : fp32 tables, row n at cos + n*table_row_stride, only columns [0, D/2) are read
+ *              (fused_rope_attn.py:88-93, 279-284) -- both [N, D] "cat" and [N, D/2] tables work.
+ *   o        : [B,H,N,D] output in `dtype`.
+ *   lse2     : [B,H,N] fp32, log2-domain log-sum-exp of the scaled scores (the reference's M, :316).
+ */
+int corope_rope_attn_fwd(const void* q, const void* k, const void* v,
+                         const float* cos, const float* sin, int64_t table_row_stride,
+                         void* o, float* lse2,
+                         int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                         void* workspace, size_t workspace_bytes,
+                         int* status_word, void* stream);
+
+/*
+ * Fused RoPE attention backward.  Replaces _attention.backward
+ * (fused-rope/fused_rope_attn.py:725-777: the K pre-scale :746-748, _attn_bwd_preprocess :324-337,
+ * _attn_bwd :474-649).  o and lse2 are the forward's outputs; dq/dk/dv are written in `dtype`.
+ */
+int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                         const float* lse2,
+                         const float* cos, const float* sin, int64_t table_row_stride,
+                         void* dq, void* dk, void* dv,
+                         int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                         void* workspace, size_t workspace_bytes,
+                         int* status_word, void* stream);
+
+/*
+ * Co-RoPE GQA attention forward (causal only).  Replaces the launch in _attention.forward
+ * (corope-exp/flash_attn_co_rope_gqa_triton.py:406-456, kernel _corope_fwd_backbone :47-400);
+ * the math is that of corope-exp/corope_attn_gqa_pytorch.py:56-124.
+ *   q, o   : [B,Hq,N,D];  k, v : [B,Hkv,N,D];  Hq % Hkv == 0, Hq/Hkv <= 8.
+ *   lse2   : [B,Hq,N] fp32 (log2 domain);  a_diag : [B,Hkv,N] fp32, the leader mileage a_ii.
+ */
+int corope_gqa_fwd(const void* q, const void* k, const void* v,
+                   void* o, float* lse2, float* a_diag,
+                   int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
+                   void* workspace, size_t workspace_bytes,
+                   int* status_word, void* stream);
+
+/*
+ * Co-RoPE GQA attention backward.  Replaces _attention.backward
+ * (corope-exp/flash_attn_co_rope_gqa_triton.py:459-577, dense PyTorch there); the math is that of
+ * corope-exp/corope_attn_gqa_pytorch.py:138-300.  dk/dv are [B,Hkv,N,D] (summed over the group).
+ */
+int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                   const float* lse2, const float* a_diag,
+                   void* dq, void* dk, void* dv,
+                   int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
+                   void* workspace, size_t workspace_bytes,
+                   int* status_word, void* stream);
+
+/*
+ * Selects the kernel family for 16-bit inputs: 0 = automatic (tensor-core kernels where the shape
+ * allows, otherwise the general kernels), 1 = always the general (CUDA-core, fp32-arithmetic)
+ * kernels.  Process-wide; meant for tests and A/B timing.  Returns the previous value.
+ */
+int corope_set_kernel_policy(int policy);
+
+/* Which kernel family the last call of each op used on this thread's process: 0 general, 1 tensor-core. */
+int corope_last_kernel_family(int op);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* COROPE_B200_H_ */

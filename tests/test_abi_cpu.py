@@ -1,0 +1,98 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the header declares, and its
+host-only entry points (version, status strings, workspace sizes, argument validation) behave."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from helpers import ext
+
+
+def _declared_symbols():
+    text = open(ext.HEADER_PATH).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(corope_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_is_built_and_exports_every_declared_symbol():
+    ext.build()
+    assert os.path.exists(ext.LIB_PATH)
+    L = ctypes.CDLL(ext.LIB_PATH)
+    syms = _declared_symbols()
+    assert "corope_rope_attn_fwd" in syms and "corope_gqa_bwd" in syms and len(syms) >= 9
+    for s in syms:
+        assert hasattr(L, s), s
+
+
+def test_host_only_entry_points():
+    L = ext.lib()
+    assert L.corope_abi_version() == 1
+    assert L.corope_status_string(0) == b"ok"
+    assert b"head dimension" in L.corope_status_string(-3)
+    # backward workspace of the Llama-7B-4K shape: packed tables + delta + fp32 dQ accumulator
+    nbytes = L.corope_workspace_bytes(ext.OP_ROPE_BWD, 2, 32, 32, 4096, 128, 1)
+    assert nbytes >= 2 * 32 * 4096 * 128 * 4 + 2 * 32 * 4096 * 4 + 4096 * 64 * 4
+    assert nbytes % 256 == 0
+    assert L.corope_workspace_bytes(ext.OP_GQA_BWD, 2, 32, 8, 2048, 128, 1) >= 2 * 2 * 8 * 2048 * 128 * 4
+    assert L.corope_workspace_bytes(99, 1, 1, 1, 1, 64, 0) == 0
+
+
+def test_argument_validation_happens_on_the_host():
+    L = ext.lib()
+    one = ctypes.c_void_p(256)  # never dereferenced: validation fails first
+    rc = L.corope_rope_attn_fwd(None, None, None, None, None, 0, None, None, 1, 1, 1, 64, 0, 1, 1.0, None, 0, None, None)
+    assert rc == -1
+    rc = L.corope_rope_attn_fwd(one, one, one, one, one, 64, one, one, 1, 1, 16, 48, 0, 1, 1.0, one, 1 << 20, None, None)
+    assert rc == -3
+    rc = L.corope_rope_attn_fwd(one, one, one, one, one, 64, one, one, 1, 1, 0, 64, 0, 1, 1.0, one, 1 << 20, None, None)
+    assert rc == -2
+    rc = L.corope_rope_attn_fwd(one, one, one, one, one, 64, one, one, 1, 1, 16, 64, 7, 1, 1.0, one, 1 << 20, None, None)
+    assert rc == -4
+    rc = L.corope_rope_attn_fwd(one, one, one, one, one, 64, one, one, 1, 1, 16, 64, 0, 1, 1.0, one, 8, None, None)
+    assert rc == -5
+    rc = L.corope_gqa_fwd(one, one, one, one, one, one, 1, 6, 4, 16, 64, 0, 1.0, 1e4, one, 1 << 20, None, None)
+    assert rc == -6
+    rc = L.corope_gqa_fwd(one, one, one, one, one, one, 1, 16, 1, 16, 64, 0, 1.0, 1e4, one, 1 << 20, None, None)
+    assert rc == -6
+
+
+def test_entry_points_refuse_cpu_tensors():
+    import torch
+    from helpers import fused_attention, corope_attention
+
+    q = torch.zeros(1, 1, 8, 64)
+    t = torch.zeros(8, 64)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fused_attention(q, q, q, True, 1.0, t, t)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        corope_attention(q, q, q, True, 1.0, 1e4)
+
+
+def test_corope_entry_point_raises_the_reference_errors():
+    import torch
+    from helpers import corope_attention
+
+    q = torch.zeros(1, 4, 8, 64)
+    k = torch.zeros(1, 2, 8, 64)
+    with pytest.raises(ValueError, match="causal=True only"):
+        corope_attention(q, k, k, False, 1.0, 1e4)
+    with pytest.raises(ValueError, match="same shape"):
+        corope_attention(q, k, torch.zeros(1, 2, 8, 32), True, 1.0, 1e4)
+    with pytest.raises(ValueError, match="divisible"):
+        corope_attention(torch.zeros(1, 3, 8, 64), k, k, True, 1.0, 1e4)
+    with pytest.raises(ValueError, match="group_size <= 8"):
+        corope_attention(torch.zeros(1, 32, 8, 64), k, k, True, 1.0, 1e4)
+    with pytest.raises(ValueError, match="shape"):
+        corope_attention(q[0], k, k, True, 1.0, 1e4)
+
+
+def test_fused_entry_point_asserts_head_dim_like_the_reference():
+    import torch
+    from helpers import fused_attention
+
+    q = torch.zeros(1, 1, 8, 48)
+    t = torch.zeros(8, 48)
+    with pytest.raises(AssertionError):
+        fused_attention(q, q, q, True, 1.0, t, t)

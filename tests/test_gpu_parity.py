@@ -1,0 +1,110 @@
+"""GPU parity tests: the CUDA kernels, called through the drop-in entry points (which call the C ABI),
+against the CPU oracle on the same seeded inputs and against the committed golden vectors.
+
+Tolerances are the ones the reference's verification uses for this path and the targets state:
+bf16 / fp16: max-abs <= 1e-2 forward, <= 2e-2 gradients; fp32: <= 1e-4.
+"""
+
+import pytest
+import torch
+
+import oracle
+from helpers import (corope_attention, ext, fused_attention, load_gold, maxdiff, rope_inputs, run_corope, run_fused, draw)
+
+pytestmark = pytest.mark.gpu
+
+TOL_FWD_16, TOL_BWD_16, TOL_32 = 1e-2, 2e-2, 1e-4
+
+
+@pytest.mark.parametrize("name", ["rope_a", "rope_b", "rope_c"])
+def test_fused_rope_golden_fp32(name):
+    g = load_gold(name)
+    B, H, N, D, causal, _ = g["meta"].tolist()
+    sm_scale, theta = g["scal"].tolist()
+    q, k, v, do = (torch.from_numpy(g[x]).float() for x in ("q", "k", "v", "do"))
+    cos, sin = torch.from_numpy(g["cos"]), torch.from_numpy(g["sin"])
+    o, dq, dk, dv = run_fused(q, k, v, do, bool(causal), sm_scale, cos, sin)
+    assert maxdiff(o, torch.from_numpy(g["o"])) < TOL_32
+    assert maxdiff(dq, torch.from_numpy(g["dq"])) < TOL_32
+    assert maxdiff(dk, torch.from_numpy(g["dk"])) < TOL_32
+    assert maxdiff(dv, torch.from_numpy(g["dv"])) < TOL_32
+
+
+@pytest.mark.parametrize("name", ["corope_a", "corope_b", "corope_c"])
+def test_corope_golden_fp32(name):
+    g = load_gold(name)
+    sm_scale, theta = g["scal"].tolist()
+    q, k, v, do = (torch.from_numpy(g[x]).float() for x in ("q", "k", "v", "do"))
+    o, dq, dk, dv = run_corope(q, k, v, do, sm_scale, theta)
+    assert maxdiff(o, torch.from_numpy(g["o"])) < TOL_32
+    assert maxdiff(dq, torch.from_numpy(g["dq"])) < 2 * TOL_32
+    assert maxdiff(dk, torch.from_numpy(g["dk"])) < 2 * TOL_32
+    assert maxdiff(dv, torch.from_numpy(g["dv"])) < TOL_32
+
+
+def test_fused_rope_config1_fp32():
+    # B=4, H=8, N=512, D=64, fp32, causal, sm_scale = 1/sqrt(D)
+    B, H, N, D = 4, 8, 512, 64
+    q, k, v, do = rope_inputs(B, H, N, D, torch.float32, seed=1)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    rdq, rdk, rdv = oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)
+    assert maxdiff(o, ro) < TOL_32
+    assert maxdiff(dq, rdq) < TOL_32 and maxdiff(dk, rdk) < TOL_32 and maxdiff(dv, rdv) < TOL_32
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,causal", [((1, 2, 200, 64), True), ((2, 1, 96, 32), False), ((1, 2, 130, 128), False),
+                                          ((1, 1, 384, 128), True)])
+def test_fused_rope_general_kernels_16bit(dtype, shape, causal):
+    # ragged N, non-causal, D = 32 / 64: shapes the tensor-core kernels do not take
+    B, H, N, D = shape
+    q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=2)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, causal, 0.5, cos[:, : D // 2].contiguous(), sin[:, : D // 2].contiguous())
+    ro = oracle.rope_attn_fwd(q, k, v, causal, 0.5, cos, sin)
+    rdq, rdk, rdv = oracle.rope_attn_bwd(q, k, v, do, causal, 0.5, cos, sin)
+    assert maxdiff(o, ro) < TOL_FWD_16
+    assert maxdiff(dq, rdq) < TOL_BWD_16 and maxdiff(dk, rdk) < TOL_BWD_16 and maxdiff(dv, rdv) < TOL_BWD_16
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128)])
+def test_fused_rope_tensor_core_forward(dtype, shape):
+    B, H, N, D = shape
+    q, k, v, _ = rope_inputs(B, H, N, D, dtype, seed=3)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, _, _, _ = run_fused(q, k, v, None, True, D ** -0.5, cos, sin)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
+    ro, lse2, _ = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin, return_aux=True)
+    assert maxdiff(o, ro) < TOL_FWD_16
+
+
+def test_fused_rope_identity_tables_and_first_row():
+    # the reference's own test_op uses cos = 1, sin = 0 (fused_rope_attn.py:803-804)
+    B, H, N, D = 1, 2, 512, 128
+    q, k, v, _ = rope_inputs(B, H, N, D, torch.bfloat16, seed=4)
+    q, k, v = q * 0.5, k * 0.5, v * 0.5
+    cos, sin = torch.ones(N, D), torch.zeros(N, D)
+    o, _, _, _ = run_fused(q, k, v, None, True, 0.5, cos, sin)
+    p = torch.matmul(q.float(), k.float().transpose(2, 3)) * 0.5
+    p = p.masked_fill(torch.triu(torch.ones(N, N, dtype=torch.bool), 1), float("-inf"))
+    ref = torch.matmul(torch.softmax(p, dim=-1), v.float())
+    assert maxdiff(o, ref) < TOL_FWD_16
+    assert maxdiff(o[..., 0, :], v[..., 0, :]) < 1e-6
+
+
+@pytest.mark.parametrize("dtype,tolf,tolb", [(torch.bfloat16, TOL_FWD_16, TOL_BWD_16), (torch.float32, TOL_32, 2 * TOL_32)])
+@pytest.mark.parametrize("cfg", [(1, 4, 1, 160, 64), (2, 4, 2, 96, 128), (1, 8, 1, 64, 64), (1, 3, 1, 40, 32)])
+def test_corope_general_kernels(dtype, tolf, tolb, cfg):
+    B, Hq, Hkv, N, D = cfg
+    q = draw((B, Hq, N, D), 11, dtype)
+    k = draw((B, Hkv, N, D), 12, dtype)
+    v = draw((B, Hkv, N, D), 13, dtype)
+    do = draw((B, Hq, N, D), 14, dtype)
+    o, dq, dk, dv = run_corope(q, k, v, do, D ** -0.5, 10000.0)
+    ro = oracle.corope_gqa_fwd(q, k, v, True, D ** -0.5, 10000.0)
+    rdq, rdk, rdv = oracle.corope_gqa_bwd(q, k, v, do, True, D ** -0.5, 10000.0)
+    assert maxdiff(o, ro) < tolf
+    assert maxdiff(dq, rdq) < tolb and maxdiff(dk, rdk) < tolb and maxdiff(dv, rdv) < tolb
