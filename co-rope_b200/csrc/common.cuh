@@ -55,7 +55,7 @@ struct RopeParams {
     const float* cos;
     const float* sin;
     int64_t table_stride;
-    const uint32_t* packed_tab;  // [N, D/2] half2 (cos, sin), built per call in the workspace
+    const uint32_t* packed_tab;  // [N, D/2] (cos, sin) pairs in 16-bit fixed point, built per call in the workspace
     int B, H, N, D;
     int causal;
     float sm_scale;
@@ -244,6 +244,19 @@ __device__ __forceinline__ float2 unpack_bf162(uint32_t u) {
 __device__ __forceinline__ uint32_t pack_bf162(float lo, float hi) {
     __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+// (cos, sin) in [-1, 1] as two 16-bit offset-binary fixed-point numbers u = round((x + 1) * 2^15), clamped to
+// 65535 (so +1.0 decodes to 1 - 2^-15; 0 and -1 are exact).  Decoding costs one byte-permute and one FMA per
+// value and no conversion instruction: float(0x4B000000 | u) = 2^23 + u exactly.
+__device__ __forceinline__ uint32_t pack_unorm_pair(float c, float s) {
+    float uc = fminf(fmaxf(rintf((c + 1.f) * 32768.f), 0.f), 65535.f);
+    float us = fminf(fmaxf(rintf((s + 1.f) * 32768.f), 0.f), 65535.f);
+    return (uint32_t)uc | ((uint32_t)us << 16);
+}
+__device__ __forceinline__ float2 unpack_unorm_pair(uint32_t u) {
+    float lo = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7410));  // bytes: u.b0, u.b1, 0x00, 0x4B
+    float hi = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7432));  // bytes: u.b2, u.b3, 0x00, 0x4B
+    return make_float2(fmaf(lo, 1.f / 32768.f, -257.f), fmaf(hi, 1.f / 32768.f, -257.f));
 }
 #endif  // __CUDACC__
 

@@ -60,7 +60,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 // In-place half-layout rotation of a 128 x 128 tile held as two 128-byte-swizzled 128 x 64 boxes
 // (columns [0,64) and [64,128)).  Element (r, c) of a box sits at r*128 + ((c/8) ^ (r%8))*16 + (c%8)*2, so the
 // pair (d, d+64) has the same offset in the two boxes.  8 consecutive threads cover one 128-byte row.
-// tab points at the packed (cos, sin) half2 row of the tile's first position.
+// tab points at the packed (cos, sin) row of the tile's first position (16-bit fixed point, see unpack_unorm_pair).
 template <typename T>
 __device__ __forceinline__ void rotate_tile_inplace(uint8_t* tile, const uint32_t* __restrict__ tab, int tid, float scale) {
 #pragma unroll 2
@@ -79,7 +79,7 @@ __device__ __forceinline__ void rotate_tile_inplace(uint8_t* tile, const uint32_
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
-            float2 c0 = unpack_half2(cs[2 * i]), c1 = unpack_half2(cs[2 * i + 1]);
+            float2 c0 = unpack_unorm_pair(cs[2 * i]), c1 = unpack_unorm_pair(cs[2 * i + 1]);
             float y1x = (fa.x * c0.x - fb.x * c0.y) * scale;
             float y2x = (fb.x * c0.x + fa.x * c0.y) * scale;
             float y1y = (fa.y * c1.x - fb.y * c1.y) * scale;

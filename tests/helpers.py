@@ -57,3 +57,17 @@ def run_corope(q, k, v, do, sm_scale, theta, device="cuda"):
 
 def maxdiff(a, b):
     return (a.float() - b.float()).abs().max().item()
+
+
+_ULP = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11, torch.float32: 2.0 ** -23}
+
+
+def excess(got, ref, abs_tol, dtype):
+    """Largest amount by which |got - ref| exceeds the allowed error, over all elements (<= 0 means pass).
+
+    The allowed error is `abs_tol`, or one unit in the last place of the output dtype at the reference
+    value where that is larger: a bf16 result of magnitude >= 4 cannot be closer than 2^-7 to an arbitrary
+    fp32 reference value, so a pure absolute bound below that is unattainable there by any kernel."""
+    ref = ref.float()
+    allowed = torch.clamp(ref.abs() * _ULP[dtype], min=abs_tol)
+    return ((got.float() - ref).abs() - allowed).max().item()
