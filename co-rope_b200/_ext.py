@@ -78,6 +78,8 @@ def lib():
             L.corope_status_string.argtypes = [i32]
             L.corope_workspace_bytes.restype = sz
             L.corope_workspace_bytes.argtypes = [i32] * 7
+            L.corope_launch_count.restype = ctypes.c_uint64
+            L.corope_launch_count.argtypes = []
             L.corope_set_kernel_policy.restype = i32
             L.corope_set_kernel_policy.argtypes = [i32]
             L.corope_last_kernel_family.restype = i32

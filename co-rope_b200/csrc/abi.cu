@@ -7,6 +7,7 @@ namespace corope {
 namespace {
 
 std::atomic<int> g_policy{0};
+std::atomic<unsigned long long> g_launches{0};
 std::atomic<int> g_last_family[4] = {{0}, {0}, {0}, {0}};
 
 constexpr size_t kAlign = 256;
@@ -65,6 +66,9 @@ int check_workspace(const void* ws, size_t have, size_t need) {
 }
 
 }  // namespace
+
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n); }
+
 }  // namespace corope
 
 using namespace corope;
@@ -102,6 +106,8 @@ size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int 
         default: return 0;
     }
 }
+
+uint64_t corope_launch_count(void) { return (uint64_t)g_launches.load(); }
 
 int corope_set_kernel_policy(int policy) { return g_policy.exchange(policy); }
 

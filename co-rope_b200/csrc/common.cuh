@@ -260,6 +260,9 @@ __device__ __forceinline__ float2 unpack_unorm_pair(uint32_t u) {
 }
 #endif  // __CUDACC__
 
+// Every kernel launch of the library bumps this counter (read through corope_launch_count()).
+void count_launch(int n = 1);
+
 // ---------------------------------------------------------------------------------------------
 // host launchers implemented by the kernel translation units (return cudaError_t as int)
 // ---------------------------------------------------------------------------------------------

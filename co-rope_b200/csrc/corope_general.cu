@@ -402,7 +402,7 @@ int launch_fwd_g(const GqaParams& p, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.N + kWarps - 1) / kWarps, p.B * p.Hkv);
-    kern<<<grid, kThreads, smem, s>>>(p);
+    kern<<<grid, kThreads, smem, s>>>(p); count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -414,7 +414,7 @@ int launch_bwd_g(const GqaParams& p, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.N + kWarps - 1) / kWarps, p.B * p.Hkv);
-    kern<<<grid, kThreads, smem, s>>>(p);
+    kern<<<grid, kThreads, smem, s>>>(p); count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -447,14 +447,14 @@ template <typename T>
 int bwd_all(const GqaParams& p, cudaStream_t s) {
     const size_t rows = (size_t)p.B * p.Hq * p.N;
     const size_t kv_elems = (size_t)p.B * p.Hkv * p.N * p.D;
-    gqa_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)p.o, (const T*)p.d_o, p.delta, rows, p.D);
+    gqa_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)p.o, (const T*)p.d_o, p.delta, rows, p.D); count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dk_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dv_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
     if (int r = dispatch_gd<T>(p, s, true)) return r;
-    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dk_acc, (T*)p.dk, kv_elems);
-    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dv_acc, (T*)p.dv, kv_elems);
+    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dk_acc, (T*)p.dk, kv_elems); count_launch();
+    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dv_acc, (T*)p.dv, kv_elems); count_launch();
     return (int)cudaGetLastError();
 }
 

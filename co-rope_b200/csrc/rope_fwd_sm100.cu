@@ -389,7 +389,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     const unsigned grid = (unsigned)((p.N / (2 * kBM)) * p.B * p.H);
-    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, p);
+    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, p); count_launch();
     return (int)cudaGetLastError();
 }
 

@@ -358,7 +358,7 @@ int launch_fwd_t(const RopeParams& p, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid((p.N + kRows - 1) / kRows, p.B * p.H);
-    kern<<<grid, kThreads, smem, s>>>(p);
+    kern<<<grid, kThreads, smem, s>>>(p); count_launch();
     return (int)cudaGetLastError();
 }
 
@@ -370,7 +370,7 @@ int launch_bwd_t(const RopeParams& p, cudaStream_t s) {
         auto kern = rope_bwd_dq_general_kernel<T, D>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, s>>>(p);
+        kern<<<grid, kThreads, smem, s>>>(p); count_launch();
         e = cudaGetLastError();
         if (e != cudaSuccess) return (int)e;
     }
@@ -379,7 +379,7 @@ int launch_bwd_t(const RopeParams& p, cudaStream_t s) {
         auto kern = rope_bwd_dkdv_general_kernel<T, D>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, s>>>(p);
+        kern<<<grid, kThreads, smem, s>>>(p); count_launch();
         return (int)cudaGetLastError();
     }
 }
@@ -420,14 +420,14 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     unsigned blocks = (unsigned)((rows + warps - 1) / warps);
     switch (dtype) {
         case COROPE_DTYPE_F32:
-            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D);
+            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D); count_launch();
             break;
         case COROPE_DTYPE_BF16:
             rope_delta_kernel<__nv_bfloat16>
-                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D);
+                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D); count_launch();
             break;
         case COROPE_DTYPE_F16:
-            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D);
+            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D); count_launch();
             break;
         default: return COROPE_ERR_BAD_DTYPE;
     }
@@ -436,7 +436,7 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
 
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s) {
     size_t n = (size_t)N * half_d;
-    pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d);
+    pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d); count_launch();
     return (int)cudaGetLastError();
 }
 

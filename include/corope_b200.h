@@ -121,6 +121,9 @@ int corope_set_kernel_policy(int policy);
 /* Which kernel family the last call of each op used on this thread's process: 0 general, 1 tensor-core. */
 int corope_last_kernel_family(int op);
 
+/* Diagnostic: number of GPU kernel launches this library has issued in this process so far. */
+uint64_t corope_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif
