@@ -16,7 +16,7 @@ _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcorope_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "corope_b200.h")
 
-SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu"]
+SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu", "noalloc.cu"]
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 OP_ROPE_FWD, OP_ROPE_BWD, OP_GQA_FWD, OP_GQA_BWD = 0, 1, 2, 3
@@ -86,6 +86,8 @@ def lib():
             L.corope_last_kernel_family.argtypes = [i32]
             L.corope_rope_attn_fwd.restype = i32
             L.corope_rope_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
+            L.corope_rope_attn_fwd_noalloc.restype = i32
+            L.corope_rope_attn_fwd_noalloc.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, vp]
             L.corope_rope_attn_bwd.restype = i32
             L.corope_rope_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32,
                                                vp, sz, vp, vp]

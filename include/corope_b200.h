@@ -74,6 +74,25 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v,
                          int* status_word, void* stream);
 
 /*
+ * Fused RoPE attention forward that allocates nothing and takes no workspace.  It has no counterpart in the
+ * reference.  It exists for callers that may not allocate device memory at the point of the call and have no
+ * spare buffer to lend: code running under a framework that hands out a fixed, fully planned memory arena,
+ * inference servers with a hard memory budget, or a call site where an allocation would synchronise the device.
+ * Same arguments and results as corope_rope_attn_fwd minus the workspace.  The one piece of scratch the forward
+ * uses (the packed cos/sin table) lives in a 2 MiB array inside the library image, per GPU, until the process
+ * exits.  Limit: N * (D/2) <= 524288 (N <= 8192 at D = 128); larger sizes return COROPE_ERR_TOO_LARGE.
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  All calls on a device share the array: two calls
+ * whose kernels can overlap on the GPU (different streams, no ordering between them) race on it; calls ordered
+ * on one stream are safe, and nothing left by an earlier call is ever read.  Calls no cudaMalloc/cudaFree.
+ */
+int corope_rope_attn_fwd_noalloc(const void* q, const void* k, const void* v,
+                                 const float* cos, const float* sin, int64_t table_row_stride,
+                                 void* o, float* lse2,
+                                 int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                                 int* status_word, void* stream);
+
+/*
  * Fused RoPE attention backward.  Replaces _attention.backward
  * (fused-rope/fused_rope_attn.py:725-777: the K pre-scale :746-748, _attn_bwd_preprocess :324-337,
  * _attn_bwd :474-649).  o and lse2 are the forward's outputs; dq/dk/dv are written in `dtype`.
