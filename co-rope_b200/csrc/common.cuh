@@ -135,6 +135,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -258,6 +264,51 @@ __device__ __forceinline__ float2 unpack_unorm_pair(uint32_t u) {
     float hi = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7432));  // bytes: u.b2, u.b3, 0x00, 0x4B
     return make_float2(fmaf(lo, 1.f / 32768.f, -257.f), fmaf(hi, 1.f / 32768.f, -257.f));
 }
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) { return unpack_bf162(u); }
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) { return unpack_half2(u); }
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) { return pack_bf162(a, b); }
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) { return pack_half2(a, b); }
+
+// In-place half-layout rotation of a ROWS x 128 tile held as two 128-byte-swizzled ROWS x 64 boxes
+// (columns [0,64) and [64,128)).  Element (r, c) of a box sits at r*128 + ((c/8) ^ (r%8))*16 + (c%8)*2, so the
+// pair (d, d+64) has the same offset in the two boxes.  8 consecutive threads cover one 128-byte row; 128 threads.
+// The result is written as fp16 whatever the input type T.
+// tab points at the packed (cos, sin) row of the tile's first position (16-bit fixed point, see unpack_unorm_pair).
+template <typename T, int ROWS>
+__device__ __forceinline__ void rotate_tile_inplace(uint8_t* tile, const uint32_t* __restrict__ tab, int tid, float scale) {
+    constexpr int kBoxBytes = ROWS * 128;
+    constexpr int kHalfD = 64;
+#pragma unroll 2
+    for (int it = 0; it < ROWS / 16; ++it) {
+        const int row = it * 16 + (tid >> 3);
+        const int pch = tid & 7;
+        const uint32_t off = row * 128 + pch * 16;
+        const int c = pch ^ (row & 7);
+        uint4 x1 = *reinterpret_cast<uint4*>(tile + off);
+        uint4 x2 = *reinterpret_cast<uint4*>(tile + kBoxBytes + off);
+        const uint4* tp = reinterpret_cast<const uint4*>(tab + row * kHalfD + c * 8);
+        uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+        uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w};
+        uint32_t b[4] = {x2.x, x2.y, x2.z, x2.w};
+        uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
+            float2 c0 = unpack_unorm_pair(cs[2 * i]), c1 = unpack_unorm_pair(cs[2 * i + 1]);
+            float y1x = (fa.x * c0.x - fb.x * c0.y) * scale;
+            float y2x = (fb.x * c0.x + fa.x * c0.y) * scale;
+            float y1y = (fa.y * c1.x - fb.y * c1.y) * scale;
+            float y2y = (fb.y * c1.x + fa.y * c1.y) * scale;
+            a[i] = pack_half2(y1x, y1y);
+            b[i] = pack_half2(y2x, y2y);
+        }
+        *reinterpret_cast<uint4*>(tile + off) = make_uint4(a[0], a[1], a[2], a[3]);
+        *reinterpret_cast<uint4*>(tile + kBoxBytes + off) = make_uint4(b[0], b[1], b[2], b[3]);
+    }
+}
+
 #endif  // __CUDACC__
 
 // Every kernel launch of the library bumps this counter (read through corope_launch_count()).

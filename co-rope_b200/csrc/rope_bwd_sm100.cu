@@ -1,10 +1,405 @@
-// Fused-RoPE flash-attention backward for sm_100a (tensor-core path).
+// Fused-RoPE causal flash-attention backward for sm_100a: TMA -> shared memory -> in-place rotation of K
+// (once) and of every Q tile -> five tcgen05 MMAs per (K block, Q tile) pair with TMEM accumulators.
+// 16-bit inputs, D = 128, N % 128 == 0.
+//
+// One CTA owns one K/V block of 128 keys of one (batch, head) and sweeps the query tiles (64 rows each) at or
+// below the diagonal.  Per step, with everything transposed so that thread = key row:
+//     S^T  = K~ Q~^T                      [128 keys x 64 queries]   (Q~ carries sm_scale*log2e)
+//     dP^T = V dO^T                       [128 x 64]
+//     P^T  = exp2(S^T - lse2_i),  dS^T = P^T o (dP^T - delta_i)     (CUDA cores)
+//     dV  += P^T  dO                      [128 keys x 128]  accumulated in TMEM over the sweep
+//     dK~ += dS^T Q~                      [128 keys x 128]  accumulated in TMEM over the sweep
+//     dQ~^T = K~^T dS^T                   [128 (head dim) x 64 queries]  -> added to a global fp32 accumulator
+// i.e. five tile products per pair (the reference's Triton kernel spends seven, fused_rope_attn.py:341-470).
+// dS^T is written once to shared memory (fp16, 128-byte swizzle) and is read both as the K-major A operand of
+// dK~ and as the MN-major B operand of dQ~^T; K~, Q~ and dO likewise serve two MMAs each from one buffer.
+//
+// Warp roles (576 threads): warp 0 TMA producer; warp 1 MMA issuer + TMEM owner; warps 2-5 rotation group
+// (K block once, every Q tile); warps 6-9 / 10-13 two softmax groups taking alternate steps; warps 14-17 drain
+// dQ~^T from TMEM and add it to the fp32 accumulator with reductions.  After the sweep the softmax groups write
+// dV and dK (inverse rotation and the ln2 factor applied in registers).
+// TMEM columns: S^T/P^T buffers [0,64) [64,128); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
+// A separate small kernel turns the fp32 dQ~ accumulator into dQ (inverse rotation, * sm_scale).
+//
+// Replaces _attn_bwd / _attn_bwd_dkdv / _attn_bwd_dq of the reference (fused-rope/fused_rope_attn.py:341-649).
 #include "common.cuh"
 
 namespace corope {
+namespace {
 
-bool rope_bwd_tc_supported(int, int, int, int, int, int) { return false; }
+constexpr int kD = 128;
+constexpr int kBK = 128;                 // keys per CTA
+constexpr int kBQ = 64;                  // query rows per step
+constexpr int kStages = 3;               // Q / dO ring
+constexpr int kKVBytes = kBK * kD * 2;   // 32 KiB
+constexpr int kKVBox = kKVBytes / 2;
+constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
+constexpr int kQBox = kQBytes / 2;
+constexpr int kDsBytes = kBK * kBQ * 2;  // 16 KiB
+constexpr int kThreads = 576;
+constexpr int kRotWarp0 = 2, kSmxWarp0 = 6, kDrainWarp0 = 14;
 
-int launch_rope_bwd_tc(const RopeParams&, int, cudaStream_t) { return COROPE_ERR_BAD_SHAPE; }
+enum Bar {
+    K_FULL = 0, V_FULL, K_ROT,
+    QDO_FULL,                            // + stage
+    Q_ROT = QDO_FULL + kStages,
+    QDO_EMPTY = Q_ROT + kStages,
+    ST_FULL = QDO_EMPTY + kStages,       // + buffer
+    P_READY = ST_FULL + 2,
+    DQ_FULL = P_READY + 2,
+    DQ_EMPTY = DQ_FULL + 2,
+    ACC_FULL = DQ_EMPTY + 2,
+    NUM_BARS
+};
+
+constexpr size_t kSmemData = 2 * kKVBytes + kStages * 2 * kQBytes + 2 * kDsBytes + kStages * 2 * kBQ * sizeof(float);
+constexpr size_t kSmemBytes = kSmemData + NUM_BARS * 8 + 64 + 1024;
+
+constexpr uint32_t TS0 = 0, TD0 = 128, TDV = 256, TDK = 384;
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO, RopeParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t* sK = sm;
+    uint8_t* sV = sK + kKVBytes;
+    uint8_t* sQ = sV + kKVBytes;                       // [stage] Q tile
+    uint8_t* sDO = sQ + kStages * kQBytes;             // [stage] dO tile
+    uint8_t* sDS = sDO + kStages * kQBytes;            // [2] dS^T
+    float* sLD = reinterpret_cast<float*>(sDS + 2 * kDsBytes);  // [stage][lse 64 | delta 64]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sLD + kStages * 2 * kBQ);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int N = p.N;
+    const int BH = p.B * p.H;
+    const int jb = (int)(blockIdx.x / BH);              // key block; low blocks sweep the most query tiles and go first
+    const int bh = (int)(blockIdx.x % BH);
+    const int row_base = bh * N;
+    const int n_steps = (N - jb * kBK) / kBQ;
+    const int q_first = jb * kBK;                       // first query row this CTA visits
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(&bars[K_FULL], 1);
+        mbar_init(&bars[V_FULL], 1);
+        mbar_init(&bars[K_ROT], 128);
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&bars[QDO_FULL + s], 1);
+            mbar_init(&bars[Q_ROT + s], 128);
+            mbar_init(&bars[QDO_EMPTY + s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&bars[ST_FULL + b], 1);
+            mbar_init(&bars[P_READY + b], 128);
+            mbar_init(&bars[DQ_FULL + b], 1);
+            mbar_init(&bars[DQ_EMPTY + b], 128);
+        }
+        mbar_init(&bars[ACC_FULL], 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&mapQ);
+        tma_prefetch_desc(&mapK);
+        tma_prefetch_desc(&mapV);
+        tma_prefetch_desc(&mapDO);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const int kr = row_base + jb * kBK;
+            mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
+            tma_load_2d(sK, &mapK, 0, kr, &bars[K_FULL]);
+            tma_load_2d(sK + kKVBox, &mapK, 64, kr, &bars[K_FULL]);
+            mbar_arrive_expect_tx(&bars[V_FULL], kKVBytes);
+            tma_load_2d(sV, &mapV, 0, kr, &bars[V_FULL]);
+            tma_load_2d(sV + kKVBox, &mapV, 64, kr, &bars[V_FULL]);
+            for (int s = 0; s < n_steps; ++s) {
+                const int st = s % kStages;
+                if (s >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((s / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) break;
+                const int qr = row_base + q_first + s * kBQ;
+                mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
+                tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
+                tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
+                tma_load_2d(sDO + st * kQBytes, &mapDO, 0, qr, &bars[QDO_FULL + st]);
+                tma_load_2d(sDO + st * kQBytes + kQBox, &mapDO, 64, qr, &bars[QDO_FULL + st]);
+                bulk_load_1d(sLD + st * 2 * kBQ, p.lse2 + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
+                bulk_load_1d(sLD + st * 2 * kBQ + kBQ, p.delta + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr int kTFmt = Elem<T>::kDtype == COROPE_DTYPE_BF16 ? 1 : 0;
+            const uint32_t id_st = make_idesc(0, 0, 0, 0, kBK, kBQ);             // S^T : fp16 x fp16, both K-major
+            const uint32_t id_dp = make_idesc(kTFmt, kTFmt, 0, 0, kBK, kBQ);     // dP^T: T x T, both K-major
+            const uint32_t id_dv = make_idesc(kTFmt, kTFmt, 0, 1, kBK, kD);      // dV  : P^T (TMEM) x dO (MN-major)
+            const uint32_t id_dk = make_idesc(0, 0, 0, 1, kBK, kD);              // dK~ : dS^T (K-major) x Q~ (MN-major)
+            const uint32_t id_dq = make_idesc(0, 0, 1, 1, kD, kBQ);              // dQ~^T: K~ (MN-major) x dS^T (MN-major)
+            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
+                           ds_addr = smem_u32(sDS);
+            auto issue_mma1 = [&](int st, int b) {
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t offA = (kk >> 2) * kKVBox + (kk & 3) * 32, offB = (kk >> 2) * kQBox + (kk & 3) * 32;
+                    umma_ss(tmem + TS0 + b * 64, make_sdesc_sw128(k_addr + offA, 0, 1024), make_sdesc_sw128(q_addr + st * kQBytes + offB, 0, 1024),
+                            id_st, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t offA = (kk >> 2) * kKVBox + (kk & 3) * 32, offB = (kk >> 2) * kQBox + (kk & 3) * 32;
+                    umma_ss(tmem + TD0 + b * 64, make_sdesc_sw128(v_addr + offA, 0, 1024), make_sdesc_sw128(do_addr + st * kQBytes + offB, 0, 1024),
+                            id_dp, kk > 0);
+                }
+            };
+            auto issue_mma2 = [&](int st, int b, bool acc) {
+#pragma unroll
+                for (int kk = 0; kk < kBQ / 16; ++kk)   // dV += P^T dO : K = 64 queries
+                    umma_ts(tmem + TDV, tmem + TS0 + b * 64 + kk * 8, make_sdesc_sw128(do_addr + st * kQBytes + kk * 2048, kQBox, 1024), id_dv,
+                            (acc || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
+                    umma_ss(tmem + TDK, make_sdesc_sw128(ds_addr + b * kDsBytes + kk * 32, 0, 1024),
+                            make_sdesc_sw128(q_addr + st * kQBytes + kk * 2048, kQBox, 1024), id_dk, (acc || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; ++kk)   // dQ~^T = K~^T dS^T : K = 128 keys
+                    umma_ss(tmem + TD0 + b * 64, make_sdesc_sw128(k_addr + kk * 2048, kKVBox, 1024),
+                            make_sdesc_sw128(ds_addr + b * kDsBytes + kk * 2048, kDsBytes, 1024), id_dq, kk > 0);
+            };
+            bool ok = mbar_wait(&bars[K_ROT], 0, p.status, K_ROT, abort_flag) && mbar_wait(&bars[V_FULL], 0, p.status, V_FULL, abort_flag) &&
+                      mbar_wait(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag);
+            if (ok) {
+                tc_fence_after();
+                issue_mma1(0, 0);
+                umma_commit(&bars[ST_FULL + 0]);
+            }
+            for (int s = 0; ok && s < n_steps; ++s) {
+                const int b = s & 1;
+                if (s + 1 < n_steps) {
+                    const int st1 = (s + 1) % kStages, b1 = (s + 1) & 1;
+                    if (!mbar_wait(&bars[Q_ROT + st1], ((s + 1) / kStages) & 1, p.status, Q_ROT, abort_flag)) break;
+                    if (s + 1 >= 2 && !mbar_wait(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
+                    tc_fence_after();
+                    issue_mma1(st1, b1);
+                    umma_commit(&bars[ST_FULL + b1]);
+                }
+                if (!mbar_wait(&bars[P_READY + b], (s >> 1) & 1, p.status, P_READY, abort_flag)) break;
+                tc_fence_after();
+                issue_mma2(s % kStages, b, s > 0);
+                umma_commit(&bars[DQ_FULL + b]);
+                umma_commit(&bars[QDO_EMPTY + s % kStages]);
+            }
+            umma_commit(&bars[ACC_FULL]);
+        }
+        __syncwarp();
+    } else if (warp < kSmxWarp0) {
+        // ------------------------------------------------------------------ rotation group
+        const int tid = threadIdx.x - kRotWarp0 * 32;
+        bool ok = mbar_wait(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
+        if (ok) {
+            rotate_tile_inplace<T, kBK>(sK, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid, 1.0f);
+            fence_proxy_async();
+            mbar_arrive(&bars[K_ROT]);
+        }
+        for (int s = 0; ok && s < n_steps; ++s) {
+            const int st = s % kStages;
+            if (!mbar_wait(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
+            rotate_tile_inplace<T, kBQ>(sQ + st * kQBytes, p.packed_tab + (size_t)(q_first + s * kBQ) * (kD / 2), tid, p.sm_scale * kLog2e);
+            fence_proxy_async();
+            mbar_arrive(&bars[Q_ROT + st]);
+        }
+    } else if (warp < kDrainWarp0) {
+        // ------------------------------------------------------------------ softmax groups (alternate steps)
+        const int wg = (warp - kSmxWarp0) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;                 // key row within the block
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        const uint32_t tS = tmem + lane_base + TS0 + wg * 64;
+        const uint32_t tD = tmem + lane_base + TD0 + wg * 64;
+        uint8_t* ds_row = sDS + wg * kDsBytes + row * 128;
+        const int key = jb * kBK + row;
+        bool ok = true;
+        for (int s = wg; s < n_steps; s += 2) {
+            const int u = s >> 1, st = s % kStages;
+            if (!(ok = mbar_wait(&bars[ST_FULL + wg], u & 1, p.status, ST_FULL + wg, abort_flag))) break;
+            if (!(ok = mbar_wait(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
+            if (u > 0 && !(ok = mbar_wait(&bars[DQ_FULL + wg], (u - 1) & 1, p.status, DQ_FULL + wg, abort_flag))) break;
+            tc_fence_after();
+            const float* lse = sLD + st * 2 * kBQ;
+            const float* dlt = lse + kBQ;
+            const int q0 = q_first + s * kBQ;
+            const bool diag = q0 < jb * kBK + kBK;        // some keys of this block lie above the diagonal for these queries
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t rs[32], rd[32];
+                COROPE_TMEM_LD32(tS + c * 32, rs);
+                COROPE_TMEM_LD32(tD + c * 32, rd);
+                tmem_wait_ld();
+                uint32_t pp[16], dd[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c0 = c * 32 + 2 * i;
+                    const float2 l2 = *reinterpret_cast<const float2*>(lse + c0);
+                    const float2 d2 = *reinterpret_cast<const float2*>(dlt + c0);
+                    float p0 = fast_exp2(__uint_as_float(rs[2 * i]) - l2.x);
+                    float p1 = fast_exp2(__uint_as_float(rs[2 * i + 1]) - l2.y);
+                    if (diag && key > q0 + c0) p0 = 0.f;
+                    if (diag && key > q0 + c0 + 1) p1 = 0.f;
+                    const float s0 = p0 * (__uint_as_float(rd[2 * i]) - d2.x);
+                    const float s1 = p1 * (__uint_as_float(rd[2 * i + 1]) - d2.y);
+                    pp[i] = pack2<T>(p0, p1);
+                    dd[i] = pack_half2(s0, s1);
+                }
+                COROPE_TMEM_ST16(tS + c * 16, pp);
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const int chunk = (c * 4 + w) ^ (row & 7);
+                    *reinterpret_cast<uint4*>(ds_row + chunk * 16) = make_uint4(dd[4 * w], dd[4 * w + 1], dd[4 * w + 2], dd[4 * w + 3]);
+                }
+            }
+            tmem_wait_st();
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&bars[P_READY + wg]);
+        }
+        // epilogue: group 0 writes dV, group 1 writes dK (inverse rotation, * ln2 because Q~ carried log2e)
+        if (ok) ok = mbar_wait(&bars[ACC_FULL], 0, p.status, ACC_FULL, abort_flag);
+        if (ok) {
+            tc_fence_after();
+            const size_t grow = (size_t)row_base + key;
+            if (wg == 0) {
+                T* dst = reinterpret_cast<T*>(p.dv) + grow * kD;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    COROPE_TMEM_LD32(tmem + lane_base + TDV + c * 32, r);
+                    tmem_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+                    uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) d4[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                }
+            } else {
+                T* dst = reinterpret_cast<T*>(p.dk) + grow * kD;
+                const uint32_t* tab = p.packed_tab + (size_t)key * (kD / 2);
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r1[32], r2[32];
+                    COROPE_TMEM_LD32(tmem + lane_base + TDK + c * 32, r1);
+                    COROPE_TMEM_LD32(tmem + lane_base + TDK + 64 + c * 32, r2);
+                    tmem_wait_ld();
+                    uint32_t o1[16], o2[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint2 tt = __ldg(reinterpret_cast<const uint2*>(tab + c * 32 + 2 * i));
+                        const float2 cs0 = unpack_unorm_pair(tt.x), cs1 = unpack_unorm_pair(tt.y);
+                        const float a0 = __uint_as_float(r1[2 * i]), a1 = __uint_as_float(r1[2 * i + 1]);
+                        const float b0 = __uint_as_float(r2[2 * i]), b1 = __uint_as_float(r2[2 * i + 1]);
+                        o1[i] = pack2<T>((a0 * cs0.x + b0 * cs0.y) * kLn2, (a1 * cs1.x + b1 * cs1.y) * kLn2);
+                        o2[i] = pack2<T>((b0 * cs0.x - a0 * cs0.y) * kLn2, (b1 * cs1.x - a1 * cs1.y) * kLn2);
+                    }
+                    uint4* d1 = reinterpret_cast<uint4*>(dst + c * 32);
+                    uint4* d2 = reinterpret_cast<uint4*>(dst + 64 + c * 32);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        d1[i] = make_uint4(o1[4 * i], o1[4 * i + 1], o1[4 * i + 2], o1[4 * i + 3]);
+                        d2[i] = make_uint4(o2[4 * i], o2[4 * i + 1], o2[4 * i + 2], o2[4 * i + 3]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+    } else {
+        // ------------------------------------------------------------------ dQ~^T drain: TMEM -> global fp32 reductions
+        const int quad = warp & 3;
+        const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
+        const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+        for (int s = 0; s < n_steps; ++s) {
+            const int b = s & 1;
+            if (!mbar_wait(&bars[DQ_FULL + b], (s >> 1) & 1, p.status, DQ_FULL + b, abort_flag)) break;
+            tc_fence_after();
+            uint32_t r0[32], r1[32];
+            COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64, r0);
+            COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64 + 32, r1);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&bars[DQ_EMPTY + b]);
+            float* dst = p.dq_acc + ((size_t)row_base + q_first + s * kBQ) * kD + dcol;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)i * kD, __uint_as_float(r0[i]));
+#pragma unroll
+            for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)(32 + i) * kD, __uint_as_float(r1[i]));
+        }
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
+// dQ = inverse_rotate(dQ~ accumulator) * sm_scale, one thread per (row, d < 64) pair
+template <typename T>
+__global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const float* __restrict__ cosT,
+                                            const float* __restrict__ sinT, int64_t ts, size_t rows, int N, float scale) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * 64) return;
+    const size_t row = idx >> 6;
+    const int d = (int)(idx & 63);
+    const int pos = (int)(row % (size_t)N);
+    const float c = cosT[pos * ts + d], s = sinT[pos * ts + d];
+    const float a1 = acc[row * kD + d], a2 = acc[row * kD + d + 64];
+    dq[row * kD + d] = Elem<T>::from_f32((a1 * c + a2 * s) * scale);
+    dq[row * kD + d + 64] = Elem<T>::from_f32((a2 * c - a1 * s) * scale);
+}
+
+template <typename T>
+int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
+    CUtensorMap mq, mk, mv, mdo;
+    const uint64_t rows = (uint64_t)p.B * p.H * p.N;
+    if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mdo, p.d_o, rows, kD, kBQ, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBK, 64, dtype)) return e;
+    cudaError_t e = cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
+    if (e != cudaSuccess) return (int)e;
+    auto kern = rope_bwd_sm100_kernel<T>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    const unsigned grid = (unsigned)((p.N / kBK) * p.B * p.H);
+    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, p); count_launch();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    const size_t n = rows * 64;
+    rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.cos, p.sin,
+                                                                              p.table_stride, rows, p.N, p.sm_scale); count_launch();
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal) {
+    (void)B; (void)H;
+    return causal && D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % kBK == 0;
+}
+
+int launch_rope_bwd_tc(const RopeParams& p, int dtype, cudaStream_t s) {
+    if (dtype == COROPE_DTYPE_BF16) return launch_t<__nv_bfloat16>(p, dtype, s);
+    return launch_t<__half>(p, dtype, s);
+}
 
 }  // namespace corope

@@ -50,48 +50,6 @@ enum Bar {
 constexpr size_t kSmemTiles = (size_t)(2 + kKStages + kVStages) * kTileBytes;
 constexpr size_t kSmemBytes = kSmemTiles + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
 
-template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) { return unpack_bf162(u); }
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) { return unpack_half2(u); }
-template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) { return pack_bf162(a, b); }
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) { return pack_half2(a, b); }
-
-// In-place half-layout rotation of a 128 x 128 tile held as two 128-byte-swizzled 128 x 64 boxes
-// (columns [0,64) and [64,128)).  Element (r, c) of a box sits at r*128 + ((c/8) ^ (r%8))*16 + (c%8)*2, so the
-// pair (d, d+64) has the same offset in the two boxes.  8 consecutive threads cover one 128-byte row.
-// tab points at the packed (cos, sin) row of the tile's first position (16-bit fixed point, see unpack_unorm_pair).
-template <typename T>
-__device__ __forceinline__ void rotate_tile_inplace(uint8_t* tile, const uint32_t* __restrict__ tab, int tid, float scale) {
-#pragma unroll 2
-    for (int it = 0; it < 8; ++it) {
-        const int row = it * 16 + (tid >> 3);
-        const int pch = tid & 7;
-        const uint32_t off = row * 128 + pch * 16;
-        const int c = pch ^ (row & 7);
-        uint4 x1 = *reinterpret_cast<uint4*>(tile + off);
-        uint4 x2 = *reinterpret_cast<uint4*>(tile + kBoxBytes + off);
-        const uint4* tp = reinterpret_cast<const uint4*>(tab + row * (kD / 2) + c * 8);
-        uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
-        uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w};
-        uint32_t b[4] = {x2.x, x2.y, x2.z, x2.w};
-        uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
-            float2 c0 = unpack_unorm_pair(cs[2 * i]), c1 = unpack_unorm_pair(cs[2 * i + 1]);
-            float y1x = (fa.x * c0.x - fb.x * c0.y) * scale;
-            float y2x = (fb.x * c0.x + fa.x * c0.y) * scale;
-            float y1y = (fa.y * c1.x - fb.y * c1.y) * scale;
-            float y2y = (fb.y * c1.x + fa.y * c1.y) * scale;
-            a[i] = pack_half2(y1x, y1y);
-            b[i] = pack_half2(y2x, y2y);
-        }
-        *reinterpret_cast<uint4*>(tile + off) = make_uint4(a[0], a[1], a[2], a[3]);
-        *reinterpret_cast<uint4*>(tile + kBoxBytes + off) = make_uint4(b[0], b[1], b[2], b[3]);
-    }
-}
-
 // bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
 __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
 #pragma unroll 4
@@ -264,14 +222,14 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         for (int i = 0; i < 2 && ok; ++i) {
             ok = mbar_wait(&bars[Q_FULL + i], 0, p.status, Q_FULL, abort_flag);
             if (!ok) break;
-            rotate_tile_inplace<T>(sQ + i * kTileBytes, p.packed_tab + (size_t)(t * 2 * kBM + i * kBM) * (kD / 2), tid, p.sm_scale * kLog2e);
+            rotate_tile_inplace<T, kBM>(sQ + i * kTileBytes, p.packed_tab + (size_t)(t * 2 * kBM + i * kBM) * (kD / 2), tid, p.sm_scale * kLog2e);
             fence_proxy_async();
             mbar_arrive(&bars[Q_ROT + i]);
         }
         for (int j = 0; ok && j < nk; ++j) {
             const int ks = j % kKStages, vs = j % kVStages;
             if (!mbar_wait(&bars[K_FULL + ks], (j / kKStages) & 1, p.status, K_FULL, abort_flag)) break;
-            rotate_tile_inplace<T>(sK + ks * kTileBytes, p.packed_tab + (size_t)(j * kBN) * (kD / 2), tid, 1.0f);
+            rotate_tile_inplace<T, kBM>(sK + ks * kTileBytes, p.packed_tab + (size_t)(j * kBN) * (kD / 2), tid, 1.0f);
             fence_proxy_async();
             mbar_arrive(&bars[K_ROT + ks]);
             if (!mbar_wait(&bars[V_FULL + vs], (j / kVStages) & 1, p.status, V_FULL, abort_flag)) break;

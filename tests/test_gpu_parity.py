@@ -98,6 +98,32 @@ def test_fused_rope_tensor_core_forward(dtype, shape):
     assert excess(o, ro, TOL_FWD_16, dtype) <= 0
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128), (1, 1, 384, 128)])
+def test_fused_rope_tensor_core_backward(dtype, shape):
+    B, H, N, D = shape
+    q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=5)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
+        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+
+
+def test_fused_rope_llama7b_4k_heads_bf16():
+    # two heads of the Llama-7B-4K configuration at full sequence length, forward and backward
+    B, H, N, D = 1, 2, 4096, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=6)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro, lse2, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024)
+    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
+        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+
+
 def test_fused_rope_identity_tables_and_first_row():
     # the reference's own test_op uses cos = 1, sin = 0 (fused_rope_attn.py:803-804)
     B, H, N, D = 1, 2, 512, 128
