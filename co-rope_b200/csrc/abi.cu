@@ -107,6 +107,14 @@ size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int 
     }
 }
 
+#ifdef COROPE_PROFILE
+static long long* g_prof = nullptr;
+void corope_debug_set_profile_buffer(void* ptr) { g_prof = (long long*)ptr; }
+#define COROPE_SET_PROF(p) (p).prof = g_prof
+#else
+#define COROPE_SET_PROF(p) (void)0
+#endif
+
 uint64_t corope_launch_count(void) { return (uint64_t)g_launches.load(); }
 
 int corope_set_kernel_policy(int policy) { return g_policy.exchange(policy); }
@@ -125,6 +133,7 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    COROPE_SET_PROF(p);
     if (g_policy.load() == 0 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
@@ -150,6 +159,7 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
     p.delta = reinterpret_cast<float*>((char*)workspace + w.delta);
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    COROPE_SET_PROF(p);
     if (int e = launch_rope_delta(p, dtype, s)) return e;
     if (g_policy.load() == 0 && rope_bwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);

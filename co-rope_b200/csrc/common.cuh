@@ -60,6 +60,7 @@ struct RopeParams {
     int causal;
     float sm_scale;
     int* status;
+    long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise
 };
 
 struct GqaParams {
@@ -98,6 +99,12 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival per warp: every lane has finished (and fenced) its part, lane 0 arrives.  Barriers signalled this
+// way are initialised with the number of warps, which keeps 128 threads from serialising on one shared word.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar, int lane) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
@@ -126,6 +133,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     *abort_flag = 1;
     if (status) atomicCAS(status, 0, COROPE_DEV_WAIT_EXPIRED | id);
     return false;
+}
+
+// Same, for roles in which all 32 lanes wait: the outcome is made warp-uniform so that the lanes leave together.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, id, abort_flag));
 }
 
 // 2-D tiled TMA load into shared memory, completion on an mbarrier (no multicast).
@@ -197,6 +209,33 @@ __device__ __forceinline__ uint64_t make_sdesc_sw128(uint32_t smem_addr, uint32_
     return d;
 }
 
+// Split form of the same descriptor for the MMA issue loops: a single thread issues every MMA, so the per-MMA
+// instruction count is on the critical path (a freshly built 64-bit descriptor per MMA costs ~190 cycles of
+// dependent integer work, three times the 64 cycles a 128x128x16 MMA takes to execute).  The high word depends
+// only on SBO; the low word is (address >> 4) | (LBO >> 4) << 16, so stepping the start address is one 32-bit add.
+__device__ __forceinline__ uint32_t sdesc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__host__ __device__ constexpr uint32_t sdesc_hi(uint32_t sbo_bytes) { return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29); }
+
+__device__ __forceinline__ void umma_ss2(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_ts2(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // TMEM <-> registers: 32 lanes x 32-bit, N consecutive columns per thread.
 #define COROPE_TMEM_LD32(taddr, r)                                                                                                  \
     asm volatile(                                                                                                                   \
@@ -228,6 +267,25 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory"); }
+
+// Elects one lane of a fully converged warp.  The MMA issuer runs its whole loop warp-uniformly (all 32 lanes wait
+// on the barriers and compute the descriptors) and only the issue itself is predicated on the elected lane: the
+// same loop inside an `if (lane == 0)` branch issued one MMA every ~210 cycles instead of every 64 (measured).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .b32 rx;\n\t.reg .pred px;\n\telect.sync rx|px, 0xffffffff;\n\tselp.u32 %0, 1, 0, px;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
+// register re-allocation between warpgroups (all four warps of a warpgroup must execute the same one)
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -274,39 +332,60 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
 // In-place half-layout rotation of a ROWS x 128 tile held as two 128-byte-swizzled ROWS x 64 boxes
 // (columns [0,64) and [64,128)).  Element (r, c) of a box sits at r*128 + ((c/8) ^ (r%8))*16 + (c%8)*2, so the
 // pair (d, d+64) has the same offset in the two boxes.  8 consecutive threads cover one 128-byte row; 128 threads.
-// The result is written as fp16 whatever the input type T.
-// tab points at the packed (cos, sin) row of the tile's first position (16-bit fixed point, see unpack_unorm_pair).
-template <typename T, int ROWS>
-__device__ __forceinline__ void rotate_tile_inplace(uint8_t* tile, const uint32_t* __restrict__ tab, int tid, float scale) {
-    constexpr int kBoxBytes = ROWS * 128;
-    constexpr int kHalfD = 64;
-#pragma unroll 2
+// The result is written as fp16 whatever the input type T.  The packed (cos, sin) rows of the tile (16-bit fixed
+// point, see unpack_unorm_pair) are fetched into registers by load_table_regs, which does not depend on the tile
+// having landed: callers issue it before waiting for the TMA so that the L2 latency is hidden.
+template <int ROWS>
+struct TabRegs {
+    uint4 t[ROWS / 16 * 2];
+};
+
+template <int ROWS>
+__device__ __forceinline__ void load_table_regs(TabRegs<ROWS>& tr, const uint32_t* __restrict__ tab, int tid) {
+#pragma unroll
     for (int it = 0; it < ROWS / 16; ++it) {
         const int row = it * 16 + (tid >> 3);
-        const int pch = tid & 7;
-        const uint32_t off = row * 128 + pch * 16;
-        const int c = pch ^ (row & 7);
+        const int c = (tid & 7) ^ (row & 7);
+        const uint4* tp = reinterpret_cast<const uint4*>(tab + row * 64 + c * 8);
+        tr.t[2 * it] = __ldg(tp);
+        tr.t[2 * it + 1] = __ldg(tp + 1);
+    }
+}
+
+template <typename T, int ROWS>
+__device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<ROWS>& tr, int tid, float scale) {
+    constexpr int kBoxBytes = ROWS * 128;
+    const float k1 = scale * (1.f / 32768.f), k0 = -257.f * scale;   // decode constants with the scale folded in
+#pragma unroll
+    for (int it = 0; it < ROWS / 16; ++it) {
+        const int row = it * 16 + (tid >> 3);
+        const uint32_t off = row * 128 + (tid & 7) * 16;
         uint4 x1 = *reinterpret_cast<uint4*>(tile + off);
         uint4 x2 = *reinterpret_cast<uint4*>(tile + kBoxBytes + off);
-        const uint4* tp = reinterpret_cast<const uint4*>(tab + row * kHalfD + c * 8);
-        uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+        const uint4 t0 = tr.t[2 * it], t1 = tr.t[2 * it + 1];
         uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w};
         uint32_t b[4] = {x2.x, x2.y, x2.z, x2.w};
-        uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+        const uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
-            float2 c0 = unpack_unorm_pair(cs[2 * i]), c1 = unpack_unorm_pair(cs[2 * i + 1]);
-            float y1x = (fa.x * c0.x - fb.x * c0.y) * scale;
-            float y2x = (fb.x * c0.x + fa.x * c0.y) * scale;
-            float y1y = (fa.y * c1.x - fb.y * c1.y) * scale;
-            float y2y = (fb.y * c1.x + fa.y * c1.y) * scale;
-            a[i] = pack_half2(y1x, y1y);
-            b[i] = pack_half2(y2x, y2y);
+            const float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
+            const float c0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7410)), k1, k0);
+            const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
+            const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
+            const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
+            a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
+            b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
         }
         *reinterpret_cast<uint4*>(tile + off) = make_uint4(a[0], a[1], a[2], a[3]);
         *reinterpret_cast<uint4*>(tile + kBoxBytes + off) = make_uint4(b[0], b[1], b[2], b[3]);
     }
+}
+
+// two floats -> packed fp16 pair, values beyond the fp16 range saturate to +-65504 instead of becoming inf
+__device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 #endif  // __CUDACC__

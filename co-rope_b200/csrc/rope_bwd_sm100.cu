@@ -38,6 +38,7 @@ constexpr int kQBox = kQBytes / 2;
 constexpr int kDsBytes = kBK * kBQ * 2;  // 16 KiB
 constexpr int kThreads = 576;
 constexpr int kRotWarp0 = 2, kSmxWarp0 = 6, kDrainWarp0 = 14;
+constexpr int kHeadChunk = 4;
 
 enum Bar {
     K_FULL = 0, V_FULL, K_ROT,
@@ -76,8 +77,15 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
     const int BH = p.B * p.H;
-    const int jb = (int)(blockIdx.x / BH);              // key block; low blocks sweep the most query tiles and go first
-    const int bh = (int)(blockIdx.x % BH);
+    // CTA order: heads in chunks of kHeadChunk (the CTAs resident at one time then share few heads, so their
+    // Q / dO tiles and above all the fp32 dQ accumulator rows stay in L2); within a chunk low key blocks first,
+    // since they sweep the most query tiles
+    const int n_kb = N / kBK;
+    const int chunk_ctas = kHeadChunk * n_kb;
+    const int chunk = (int)blockIdx.x / chunk_ctas, within = (int)blockIdx.x % chunk_ctas;
+    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
+    const int jb = within / heads_here;
+    const int bh = chunk * kHeadChunk + within % heads_here;
     const int row_base = bh * N;
     const int n_steps = (N - jb * kBK) / kBQ;
     const int q_first = jb * kBK;                       // first query row this CTA visits
@@ -86,17 +94,17 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         *abort_flag = 0;
         mbar_init(&bars[K_FULL], 1);
         mbar_init(&bars[V_FULL], 1);
-        mbar_init(&bars[K_ROT], 128);
+        mbar_init(&bars[K_ROT], 4);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&bars[QDO_FULL + s], 1);
-            mbar_init(&bars[Q_ROT + s], 128);
+            mbar_init(&bars[Q_ROT + s], 4);
             mbar_init(&bars[QDO_EMPTY + s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars[ST_FULL + b], 1);
-            mbar_init(&bars[P_READY + b], 128);
+            mbar_init(&bars[P_READY + b], 4);
             mbar_init(&bars[DQ_FULL + b], 1);
-            mbar_init(&bars[DQ_EMPTY + b], 128);
+            mbar_init(&bars[DQ_EMPTY + b], 4);
         }
         mbar_init(&bars[ACC_FULL], 1);
         fence_mbar_init();
@@ -141,7 +149,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             constexpr int kTFmt = Elem<T>::kDtype == COROPE_DTYPE_BF16 ? 1 : 0;
             const uint32_t id_st = make_idesc(0, 0, 0, 0, kBK, kBQ);             // S^T : fp16 x fp16, both K-major
             const uint32_t id_dp = make_idesc(kTFmt, kTFmt, 0, 0, kBK, kBQ);     // dP^T: T x T, both K-major
@@ -150,75 +159,84 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t id_dq = make_idesc(0, 0, 1, 1, kD, kBQ);              // dQ~^T: K~ (MN-major) x dS^T (MN-major)
             const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
                            ds_addr = smem_u32(sDS);
+            constexpr uint32_t kHi = sdesc_hi(1024);
+            const uint32_t k_lo = sdesc_lo(k_addr, 0), v_lo = sdesc_lo(v_addr, 0), q_lo = sdesc_lo(q_addr, 0), do_lo = sdesc_lo(do_addr, 0);
+            const uint32_t do_mn = sdesc_lo(do_addr, kQBox), q_mn = sdesc_lo(q_addr, kQBox), k_mn = sdesc_lo(k_addr, kKVBox);
+            const uint32_t ds_lo = sdesc_lo(ds_addr, 0);
             auto issue_mma1 = [&](int st, int b) {
+                const uint32_t qb = q_lo + st * (kQBytes >> 4), dob = do_lo + st * (kQBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t offA = (kk >> 2) * kKVBox + (kk & 3) * 32, offB = (kk >> 2) * kQBox + (kk & 3) * 32;
-                    umma_ss(tmem + TS0 + b * 64, make_sdesc_sw128(k_addr + offA, 0, 1024), make_sdesc_sw128(q_addr + st * kQBytes + offB, 0, 1024),
-                            id_st, kk > 0);
+                    const uint32_t offA = ((kk >> 2) * kKVBox + (kk & 3) * 32) >> 4, offB = ((kk >> 2) * kQBox + (kk & 3) * 32) >> 4;
+                    if (leader) umma_ss2(tmem + TS0 + b * 64, k_lo + offA, kHi, qb + offB, kHi, id_st, kk > 0);
                 }
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t offA = (kk >> 2) * kKVBox + (kk & 3) * 32, offB = (kk >> 2) * kQBox + (kk & 3) * 32;
-                    umma_ss(tmem + TD0 + b * 64, make_sdesc_sw128(v_addr + offA, 0, 1024), make_sdesc_sw128(do_addr + st * kQBytes + offB, 0, 1024),
-                            id_dp, kk > 0);
+                    const uint32_t offA = ((kk >> 2) * kKVBox + (kk & 3) * 32) >> 4, offB = ((kk >> 2) * kQBox + (kk & 3) * 32) >> 4;
+                    if (leader) umma_ss2(tmem + TD0 + b * 64, v_lo + offA, kHi, dob + offB, kHi, id_dp, kk > 0);
                 }
             };
             auto issue_mma2 = [&](int st, int b, bool acc) {
+                const uint32_t dob = do_mn + st * (kQBytes >> 4), qb = q_mn + st * (kQBytes >> 4), dsb = ds_lo + b * (kDsBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dV += P^T dO : K = 64 queries
-                    umma_ts(tmem + TDV, tmem + TS0 + b * 64 + kk * 8, make_sdesc_sw128(do_addr + st * kQBytes + kk * 2048, kQBox, 1024), id_dv,
-                            (acc || kk > 0) ? 1u : 0u);
+                    if (leader) umma_ts2(tmem + TDV, tmem + TS0 + b * 64 + kk * 8, dob + kk * (2048 >> 4), kHi, id_dv, (acc || kk > 0) ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
-                    umma_ss(tmem + TDK, make_sdesc_sw128(ds_addr + b * kDsBytes + kk * 32, 0, 1024),
-                            make_sdesc_sw128(q_addr + st * kQBytes + kk * 2048, kQBox, 1024), id_dk, (acc || kk > 0) ? 1u : 0u);
+                    if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < kBK / 16; ++kk)   // dQ~^T = K~^T dS^T : K = 128 keys
-                    umma_ss(tmem + TD0 + b * 64, make_sdesc_sw128(k_addr + kk * 2048, kKVBox, 1024),
-                            make_sdesc_sw128(ds_addr + b * kDsBytes + kk * 2048, kDsBytes, 1024), id_dq, kk > 0);
+                    if (leader) umma_ss2(tmem + TD0 + b * 64, k_mn + kk * (2048 >> 4), kHi, dsb + kk * (2048 >> 4), kHi, id_dq, kk > 0);
             };
-            bool ok = mbar_wait(&bars[K_ROT], 0, p.status, K_ROT, abort_flag) && mbar_wait(&bars[V_FULL], 0, p.status, V_FULL, abort_flag) &&
-                      mbar_wait(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag);
+            bool ok = mbar_wait_warp(&bars[K_ROT], 0, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], 0, p.status, V_FULL, abort_flag) &&
+                      mbar_wait_warp(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag);
             if (ok) {
                 tc_fence_after();
                 issue_mma1(0, 0);
-                umma_commit(&bars[ST_FULL + 0]);
+                if (leader) umma_commit(&bars[ST_FULL + 0]);
             }
             for (int s = 0; ok && s < n_steps; ++s) {
                 const int b = s & 1;
                 if (s + 1 < n_steps) {
                     const int st1 = (s + 1) % kStages, b1 = (s + 1) & 1;
-                    if (!mbar_wait(&bars[Q_ROT + st1], ((s + 1) / kStages) & 1, p.status, Q_ROT, abort_flag)) break;
-                    if (s + 1 >= 2 && !mbar_wait(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
+                    if (!mbar_wait_warp(&bars[Q_ROT + st1], ((s + 1) / kStages) & 1, p.status, Q_ROT, abort_flag)) break;
+                    if (s + 1 >= 2 && !mbar_wait_warp(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
                     tc_fence_after();
                     issue_mma1(st1, b1);
-                    umma_commit(&bars[ST_FULL + b1]);
+                    if (leader) umma_commit(&bars[ST_FULL + b1]);
                 }
-                if (!mbar_wait(&bars[P_READY + b], (s >> 1) & 1, p.status, P_READY, abort_flag)) break;
+                if (!mbar_wait_warp(&bars[P_READY + b], (s >> 1) & 1, p.status, P_READY, abort_flag)) break;
                 tc_fence_after();
                 issue_mma2(s % kStages, b, s > 0);
-                umma_commit(&bars[DQ_FULL + b]);
-                umma_commit(&bars[QDO_EMPTY + s % kStages]);
+                if (leader) umma_commit(&bars[DQ_FULL + b]);
+                if (leader) umma_commit(&bars[QDO_EMPTY + s % kStages]);
             }
-            umma_commit(&bars[ACC_FULL]);
+            if (leader) umma_commit(&bars[ACC_FULL]);
         }
         __syncwarp();
     } else if (warp < kSmxWarp0) {
         // ------------------------------------------------------------------ rotation group
         const int tid = threadIdx.x - kRotWarp0 * 32;
-        bool ok = mbar_wait(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
-        if (ok) {
-            rotate_tile_inplace<T, kBK>(sK, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid, 1.0f);
-            fence_proxy_async();
-            mbar_arrive(&bars[K_ROT]);
+        bool ok;
+        {
+            TabRegs<kBK> trk;
+            load_table_regs<kBK>(trk, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid);
+            ok = mbar_wait_warp(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
+            if (ok) {
+                rotate_tile_regs<T, kBK>(sK, trk, tid, 1.0f);
+                fence_proxy_async();
+                mbar_arrive_warp(&bars[K_ROT], lane);
+            }
         }
+        TabRegs<kBQ> tr;
+        load_table_regs<kBQ>(tr, p.packed_tab + (size_t)q_first * (kD / 2), tid);
         for (int s = 0; ok && s < n_steps; ++s) {
             const int st = s % kStages;
-            if (!mbar_wait(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
-            rotate_tile_inplace<T, kBQ>(sQ + st * kQBytes, p.packed_tab + (size_t)(q_first + s * kBQ) * (kD / 2), tid, p.sm_scale * kLog2e);
+            if (!mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
+            rotate_tile_regs<T, kBQ>(sQ + st * kQBytes, tr, tid, p.sm_scale * kLog2e);
             fence_proxy_async();
-            mbar_arrive(&bars[Q_ROT + st]);
+            mbar_arrive_warp(&bars[Q_ROT + st], lane);
+            if (s + 1 < n_steps) load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ) * (kD / 2), tid);
         }
     } else if (warp < kDrainWarp0) {
         // ------------------------------------------------------------------ softmax groups (alternate steps)
@@ -233,9 +251,9 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         bool ok = true;
         for (int s = wg; s < n_steps; s += 2) {
             const int u = s >> 1, st = s % kStages;
-            if (!(ok = mbar_wait(&bars[ST_FULL + wg], u & 1, p.status, ST_FULL + wg, abort_flag))) break;
-            if (!(ok = mbar_wait(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
-            if (u > 0 && !(ok = mbar_wait(&bars[DQ_FULL + wg], (u - 1) & 1, p.status, DQ_FULL + wg, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&bars[ST_FULL + wg], u & 1, p.status, ST_FULL + wg, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
+            if (u > 0 && !(ok = mbar_wait_warp(&bars[DQ_FULL + wg], (u - 1) & 1, p.status, DQ_FULL + wg, abort_flag))) break;
             tc_fence_after();
             const float* lse = sLD + st * 2 * kBQ;
             const float* dlt = lse + kBQ;
@@ -272,10 +290,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tmem_wait_st();
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive(&bars[P_READY + wg]);
+            mbar_arrive_warp(&bars[P_READY + wg], lane);
         }
         // epilogue: group 0 writes dV, group 1 writes dK (inverse rotation, * ln2 because Q~ carried log2e)
-        if (ok) ok = mbar_wait(&bars[ACC_FULL], 0, p.status, ACC_FULL, abort_flag);
+        if (ok) ok = mbar_wait_warp(&bars[ACC_FULL], 0, p.status, ACC_FULL, abort_flag);
         if (ok) {
             tc_fence_after();
             const size_t grow = (size_t)row_base + key;
@@ -330,14 +348,14 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         for (int s = 0; s < n_steps; ++s) {
             const int b = s & 1;
-            if (!mbar_wait(&bars[DQ_FULL + b], (s >> 1) & 1, p.status, DQ_FULL + b, abort_flag)) break;
+            if (!mbar_wait_warp(&bars[DQ_FULL + b], (s >> 1) & 1, p.status, DQ_FULL + b, abort_flag)) break;
             tc_fence_after();
             uint32_t r0[32], r1[32];
             COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64, r0);
             COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64 + 32, r1);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&bars[DQ_EMPTY + b]);
+            mbar_arrive_warp(&bars[DQ_EMPTY + b], lane);
             float* dst = p.dq_acc + ((size_t)row_base + q_first + s * kBQ) * kD + dcol;
 #pragma unroll
             for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)i * kD, __uint_as_float(r0[i]));

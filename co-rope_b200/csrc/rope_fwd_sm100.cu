@@ -2,14 +2,16 @@
 // tcgen05 MMAs with TMEM accumulators -> online softmax in registers.  16-bit inputs, D = 128.
 //
 // One CTA owns 256 consecutive query rows (two 128-row tiles, "Q0" and "Q1") of one (batch, head)
-// and sweeps the K/V tiles 0 .. 2t+1 they can see.  Warp roles (448 threads):
-//   warp 0        TMA producer: Q tiles once, then the K ring and the V ring
-//   warp 1        MMA issuer (one elected lane) and TMEM owner
-//   warps 2-5     rotation group: rotates Q0/Q1 once (scaled by sm_scale*log2e) and every K tile as it
+// and sweeps the K/V tiles 0 .. 2t+1 they can see.  Warp roles (512 threads = 4 warpgroups; registers are
+// re-divided between the groups with setmaxnreg):
+//   warp 0        TMA producer: Q tiles once, then the K ring (3 stages)
+//   warp 1        TMA producer: the V ring (2 stages)
+//   warp 2        MMA issuer (one elected lane) and TMEM owner;  warp 3 idle
+//   warps 4-7     rotation group: rotates Q0/Q1 once (scaled by sm_scale*log2e) and every K tile as it
 //                 lands, in place in shared memory, as fp16; converts bf16 V tiles to fp16 in place
-//   warps 6-9     softmax group of Q0: thread = row; S from TMEM, running max / sum, P (fp16) written
-//                 back over S in TMEM, lazy rescale of O in TMEM, final normalise + store
-//   warps 10-13   softmax group of Q1
+//   warps 8-11    softmax group of Q0: thread = row; the whole S row from TMEM into registers, running max /
+//                 sum, P (fp16) written back over S in TMEM, lazy rescale of O in TMEM, final normalise + store
+//   warps 12-15   softmax group of Q1
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i aliases the first 64 columns of S_i.
 // MMA order per K tile j:  PV0(j) QK0(j+1) | PV1(j) QK1(j+1)  so that one group's softmax overlaps the
 // other group's MMAs.  The rotated Q / K never leave shared memory.
@@ -24,13 +26,20 @@ namespace {
 constexpr int kD = 128;
 constexpr int kBM = 128;
 constexpr int kBN = 128;
-constexpr int kKStages = 2;
+constexpr int kKStages = 3;
 constexpr int kVStages = 2;
 constexpr int kTileBytes = kBM * kD * 2;   // 32 KiB: two 128 x 64 boxes
 constexpr int kBoxBytes = kTileBytes / 2;
-constexpr int kThreads = 448;
-constexpr int kRotWarp0 = 2;
-constexpr int kSmxWarp0 = 6;
+constexpr int kThreads = 512;          // four warpgroups: control (TMA K, TMA V, MMA, spare) | rotation | softmax 0 | softmax 1
+constexpr int kMmaWarp = 2;
+constexpr int kRotWarp0 = 4;
+constexpr int kSmxWarp0 = 8;
+#ifdef COROPE_REGS_ALT
+constexpr int kRegsCtl = 40, kRegsRot = 96, kRegsSmx = 184;
+#else
+constexpr int kRegsCtl = 56, kRegsRot = 104, kRegsSmx = 176;   // 128 * (56 + 104 + 2 * 176) = 65536 registers
+#endif
+constexpr int kHeadChunk = 8;
 
 enum Bar {
     Q_FULL = 0,                        // +i
@@ -52,19 +61,22 @@ constexpr size_t kSmemBytes = kSmemTiles + NUM_BARS * 8 + 64 + 1024;  // + align
 
 // bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
 __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
-#pragma unroll 4
-    for (int it = 0; it < kTileBytes / (16 * 128); ++it) {
-        uint4* p = reinterpret_cast<uint4*>(tile) + it * 128 + tid;
-        uint4 x = *p;
-        uint32_t w[4] = {x.x, x.y, x.z, x.w};
+    constexpr int kIters = kTileBytes / (16 * 128);   // 16 vectors of 16 bytes per thread, 8 in flight at a time
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            float2 f = unpack_bf162(w[i]);
-            f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-            f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
-            w[i] = pack_half2(f.x, f.y);
+    for (int h = 0; h < kIters; h += 8) {
+        uint4 x[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) x[it] = reinterpret_cast<uint4*>(tile)[(h + it) * 128 + tid];
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            uint32_t w[4] = {x[it].x, x[it].y, x[it].z, x[it].w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = unpack_bf162(w[i]);
+                w[i] = pack_half2_sat(f.x, f.y);
+            }
+            reinterpret_cast<uint4*>(tile)[(h + it) * 128 + tid] = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        *p = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
 
@@ -86,8 +98,13 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int N = p.N;
     const int BH = p.B * p.H;
     const int n_qt = N / (2 * kBM);
-    const int t = n_qt - 1 - (int)(blockIdx.x / BH);   // heaviest (latest) query blocks first
-    const int bh = (int)(blockIdx.x % BH);
+    // CTA order: heads in chunks of kHeadChunk (so that the CTAs resident at one time share few heads and their
+    // K/V stay in L2), within a chunk the heaviest (latest) query blocks first
+    const int chunk_ctas = kHeadChunk * n_qt;
+    const int chunk = (int)blockIdx.x / chunk_ctas, within = (int)blockIdx.x % chunk_ctas;
+    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
+    const int t = n_qt - 1 - within / heads_here;
+    const int bh = chunk * kHeadChunk + within % heads_here;
     const int row_base = bh * N;                        // row in the [B*H*N, D] view
     const int nk = 2 * t + 2;                           // K tiles seen by Q1; Q0 sees nk - 1
     const int nk0 = nk - 1;
@@ -96,19 +113,19 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars[Q_FULL + i], 1);
-            mbar_init(&bars[Q_ROT + i], 128);
+            mbar_init(&bars[Q_ROT + i], 4);
             mbar_init(&bars[S_FULL + i], 1);
-            mbar_init(&bars[P_FULL + i], 128);
+            mbar_init(&bars[P_FULL + i], 4);
             mbar_init(&bars[O_FULL + i], 1);
         }
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&bars[K_FULL + s], 1);
-            mbar_init(&bars[K_ROT + s], 128);
+            mbar_init(&bars[K_ROT + s], 4);
             mbar_init(&bars[K_EMPTY + s], 1);
         }
         for (int s = 0; s < kVStages; ++s) {
             mbar_init(&bars[V_FULL + s], 1);
-            mbar_init(&bars[V_READY + s], 128);
+            mbar_init(&bars[V_READY + s], 4);
             mbar_init(&bars[V_EMPTY + s], 1);
         }
         fence_mbar_init();
@@ -117,7 +134,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tma_prefetch_desc(&mapV);
     }
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -126,121 +143,204 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            for (int i = 0; i < 2; ++i) {
-                const int r = row_base + t * 2 * kBM + i * kBM;
-                mbar_arrive_expect_tx(&bars[Q_FULL + i], kTileBytes);
-                tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
-                tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
-            }
-            for (int j = 0; j < nk; ++j) {
-                const int r = row_base + j * kBN;
-                const int ks = j % kKStages, vs = j % kVStages;
-                if (j >= kKStages && !mbar_wait(&bars[K_EMPTY + ks], ((j / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag)) break;
-                mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
-                tma_load_2d(sK + ks * kTileBytes, &mapK, 0, r, &bars[K_FULL + ks]);
-                tma_load_2d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, &bars[K_FULL + ks]);
-                if (j >= kVStages && !mbar_wait(&bars[V_EMPTY + vs], ((j / kVStages) - 1) & 1, p.status, V_EMPTY, abort_flag)) break;
-                mbar_arrive_expect_tx(&bars[V_FULL + vs], kTileBytes);
-                tma_load_2d(sV + vs * kTileBytes, &mapV, 0, r, &bars[V_FULL + vs]);
-                tma_load_2d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, &bars[V_FULL + vs]);
-            }
-        }
-        __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr int kVFmt = (kConvertV || Elem<T>::kDtype == COROPE_DTYPE_F16) ? 0 : 1;
-            const uint32_t idesc_qk = make_idesc(0, 0, 0, 0, kBM, kBN);
-            const uint32_t idesc_pv = make_idesc(kVFmt, kVFmt, 0, 1, kBM, kD);
-            const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-            auto issue_qk = [&](int i, int ks) {
-#pragma unroll
-                for (int kk = 0; kk < kD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-                    umma_ss(tmem + i * 128, make_sdesc_sw128(q_addr + i * kTileBytes + off, 0, 1024),
-                            make_sdesc_sw128(k_addr + ks * kTileBytes + off, 0, 1024), idesc_qk, kk > 0);
+    if (warp < kRotWarp0) {
+        // producers and the MMA issuer need few registers: hand the rest to the softmax groups
+        reg_dealloc<kRegsCtl>();
+        if (warp == 0) {
+            // -------------------------------------------------------------- TMA producer: Q once, then the K ring
+            if (lane == 0) {
+                for (int i = 0; i < 2; ++i) {
+                    const int r = row_base + t * 2 * kBM + i * kBM;
+                    mbar_arrive_expect_tx(&bars[Q_FULL + i], kTileBytes);
+                    tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
+                    tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
                 }
-            };
-            auto issue_pv = [&](int i, int vs, bool acc) {
-#pragma unroll
-                for (int kk = 0; kk < kBN / 16; ++kk)
-                    umma_ts(tmem + 256 + i * 128, tmem + i * 128 + kk * 8, make_sdesc_sw128(v_addr + vs * kTileBytes + kk * 2048, kBoxBytes, 1024),
-                            idesc_pv, (acc || kk > 0) ? 1u : 0u);
-            };
-            bool ok = mbar_wait(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag) && mbar_wait(&bars[K_ROT + 0], 0, p.status, K_ROT, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0, 0);
-                umma_commit(&bars[S_FULL + 0]);
-                ok = mbar_wait(&bars[Q_ROT + 1], 0, p.status, Q_ROT + 1, abort_flag);
-            }
-            if (ok) {
-                tc_fence_after();
-                issue_qk(1, 0);
-                umma_commit(&bars[S_FULL + 1]);
-                umma_commit(&bars[K_EMPTY + 0]);
-            }
-            for (int j = 0; ok && j < nk; ++j) {
-                const int vs = j % kVStages;
-                const int ks1 = (j + 1) % kKStages;
-                const bool have_next = j + 1 < nk;
-                if (!mbar_wait(&bars[V_READY + vs], (j / kVStages) & 1, p.status, V_READY, abort_flag)) break;
-                if (j < nk0) {
-                    if (!mbar_wait(&bars[P_FULL + 0], j & 1, p.status, P_FULL, abort_flag)) break;
-                    tc_fence_after();
-                    issue_pv(0, vs, j > 0);
-                    umma_commit(&bars[O_FULL + 0]);
+                for (int j = 0; j < nk; ++j) {
+                    const int r = row_base + j * kBN;
+                    const int ks = j % kKStages;
+                    if (j >= kKStages && !mbar_wait(&bars[K_EMPTY + ks], ((j / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag)) break;
+                    mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
+                    tma_load_2d(sK + ks * kTileBytes, &mapK, 0, r, &bars[K_FULL + ks]);
+                    tma_load_2d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, &bars[K_FULL + ks]);
                 }
-                if (have_next) {
-                    if (!mbar_wait(&bars[K_ROT + ks1], ((j + 1) / kKStages) & 1, p.status, K_ROT, abort_flag)) break;
-                    tc_fence_after();
-                    if (j + 1 < nk0) {
-                        issue_qk(0, ks1);
-                        umma_commit(&bars[S_FULL + 0]);
+            }
+            __syncwarp();
+        } else if (warp == 1) {
+            // -------------------------------------------------------------- TMA producer: the V ring
+            if (lane == 0) {
+                for (int j = 0; j < nk; ++j) {
+                    const int r = row_base + j * kBN;
+                    const int vs = j % kVStages;
+                    if (j >= kVStages && !mbar_wait(&bars[V_EMPTY + vs], ((j / kVStages) - 1) & 1, p.status, V_EMPTY, abort_flag)) break;
+                    mbar_arrive_expect_tx(&bars[V_FULL + vs], kTileBytes);
+                    tma_load_2d(sV + vs * kTileBytes, &mapV, 0, r, &bars[V_FULL + vs]);
+                    tma_load_2d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, &bars[V_FULL + vs]);
+                }
+            }
+            __syncwarp();
+        } else if (warp == kMmaWarp) {
+            // -------------------------------------------------------------- MMA issuer
+            {
+                const bool leader = elect_one();
+                constexpr int kVFmt = (kConvertV || Elem<T>::kDtype == COROPE_DTYPE_F16) ? 0 : 1;
+                const uint32_t idesc_qk = make_idesc(0, 0, 0, 0, kBM, kBN);
+                const uint32_t idesc_pv = make_idesc(kVFmt, kVFmt, 0, 1, kBM, kD);
+                const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+                constexpr uint32_t kHi = sdesc_hi(1024);
+                const uint32_t q_lo = sdesc_lo(q_addr, 0), k_lo = sdesc_lo(k_addr, 0), v_lo = sdesc_lo(v_addr, kBoxBytes);
+                auto issue_qk = [&](int i, int ks) {
+                    const uint32_t a0 = q_lo + i * (kTileBytes >> 4), b0 = k_lo + ks * (kTileBytes >> 4), d = tmem + i * 128;
+#pragma unroll
+                    for (int kk = 0; kk < kD / 16; ++kk) {
+                        const uint32_t off = ((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4;
+                        if (leader) umma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, kk > 0);
                     }
+                };
+                auto issue_pv = [&](int i, int vs, bool acc) {
+                    const uint32_t b0 = v_lo + vs * (kTileBytes >> 4), d = tmem + 256 + i * 128, a = tmem + i * 128;
+#pragma unroll
+                    for (int kk = 0; kk < kBN / 16; ++kk)
+                        if (leader) umma_ts2(d, a + kk * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
+                };
+                bool ok = mbar_wait_warp(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag) && mbar_wait_warp(&bars[K_ROT + 0], 0, p.status, K_ROT, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(0, 0);
+                    if (leader) umma_commit(&bars[S_FULL + 0]);
+                    ok = mbar_wait_warp(&bars[Q_ROT + 1], 0, p.status, Q_ROT + 1, abort_flag);
                 }
-                if (!mbar_wait(&bars[P_FULL + 1], j & 1, p.status, P_FULL + 1, abort_flag)) break;
-                tc_fence_after();
-                issue_pv(1, vs, j > 0);
-                umma_commit(&bars[O_FULL + 1]);
-                umma_commit(&bars[V_EMPTY + vs]);
-                if (have_next) {
-                    issue_qk(1, ks1);
-                    umma_commit(&bars[S_FULL + 1]);
-                    umma_commit(&bars[K_EMPTY + ks1]);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(1, 0);
+                    if (leader) umma_commit(&bars[S_FULL + 1]);
+                    if (leader) umma_commit(&bars[K_EMPTY + 0]);
                 }
+#ifdef COROPE_PROFILE
+                long long pw[5] = {0, 0, 0, 0, 0}, pt;
+                const long long pstart = clock64();
+#define PROF_T0 pt = clock64()
+#define PROF_ACC(i) pw[i] += clock64() - pt
+#define PROF_STAMP(k) if (leader && p.prof && blockIdx.x == 0 && j >= 8 && j < 16) p.prof[1024 + (j - 8) * 8 + (k)] = clock64() - pstart
+#else
+#define PROF_T0
+#define PROF_ACC(i)
+#define PROF_STAMP(k)
+#endif
+                for (int j = 0; ok && j < nk; ++j) {
+                    const int vs = j % kVStages;
+                    const int ks1 = (j + 1) % kKStages;
+                    const bool have_next = j + 1 < nk;
+                    PROF_STAMP(0);
+                    PROF_T0;
+                    if (!mbar_wait_warp(&bars[V_READY + vs], (j / kVStages) & 1, p.status, V_READY, abort_flag)) break;
+                    PROF_ACC(0);
+                    if (j < nk0) {
+                        PROF_T0;
+                        if (!mbar_wait_warp(&bars[P_FULL + 0], j & 1, p.status, P_FULL, abort_flag)) break;
+                        PROF_ACC(1);
+                        PROF_STAMP(1);
+                        tc_fence_after();
+                        issue_pv(0, vs, j > 0);
+                        if (leader) umma_commit(&bars[O_FULL + 0]);
+                        PROF_STAMP(2);
+                    }
+                    if (have_next) {
+                        PROF_T0;
+                        if (!mbar_wait_warp(&bars[K_ROT + ks1], ((j + 1) / kKStages) & 1, p.status, K_ROT, abort_flag)) break;
+                        PROF_ACC(2);
+                        PROF_STAMP(3);
+                        tc_fence_after();
+                        if (j + 1 < nk0) {
+                            issue_qk(0, ks1);
+                            if (leader) umma_commit(&bars[S_FULL + 0]);
+                        }
+                        PROF_STAMP(4);
+                    }
+                    PROF_T0;
+                    if (!mbar_wait_warp(&bars[P_FULL + 1], j & 1, p.status, P_FULL + 1, abort_flag)) break;
+                    PROF_ACC(3);
+                    PROF_STAMP(5);
+                    tc_fence_after();
+                    issue_pv(1, vs, j > 0);
+                    if (leader) umma_commit(&bars[O_FULL + 1]);
+                    if (leader) umma_commit(&bars[V_EMPTY + vs]);
+                    PROF_STAMP(6);
+                    if (have_next) {
+                        issue_qk(1, ks1);
+                        if (leader) umma_commit(&bars[S_FULL + 1]);
+                        if (leader) umma_commit(&bars[K_EMPTY + ks1]);
+                    }
+                    PROF_STAMP(7);
+                }
+#ifdef COROPE_PROFILE
+                if (leader && p.prof && blockIdx.x < 64) {
+                    long long* o = p.prof + blockIdx.x * 16;
+                    o[0] = clock64() - pstart; o[1] = pw[0]; o[2] = pw[1]; o[3] = pw[2]; o[4] = pw[3]; o[5] = nk;
+                }
+#endif
             }
+            __syncwarp();
         }
-        __syncwarp();
     } else if (warp < kSmxWarp0) {
         // ------------------------------------------------------------------ rotation group
+        reg_dealloc<kRegsRot>();
         const int tid = threadIdx.x - kRotWarp0 * 32;
         bool ok = true;
+        TabRegs<kBM> tr;
         for (int i = 0; i < 2 && ok; ++i) {
-            ok = mbar_wait(&bars[Q_FULL + i], 0, p.status, Q_FULL, abort_flag);
+            load_table_regs<kBM>(tr, p.packed_tab + (size_t)(t * 2 * kBM + i * kBM) * (kD / 2), tid);
+            ok = mbar_wait_warp(&bars[Q_FULL + i], 0, p.status, Q_FULL, abort_flag);
             if (!ok) break;
-            rotate_tile_inplace<T, kBM>(sQ + i * kTileBytes, p.packed_tab + (size_t)(t * 2 * kBM + i * kBM) * (kD / 2), tid, p.sm_scale * kLog2e);
+            rotate_tile_regs<T, kBM>(sQ + i * kTileBytes, tr, tid, p.sm_scale * kLog2e);
             fence_proxy_async();
-            mbar_arrive(&bars[Q_ROT + i]);
+            mbar_arrive_warp(&bars[Q_ROT + i], lane);
         }
+        load_table_regs<kBM>(tr, p.packed_tab, tid);
+#ifdef COROPE_PROFILE
+        long long rw = 0, rv = 0, rc = 0, rt0;
+#endif
         for (int j = 0; ok && j < nk; ++j) {
             const int ks = j % kKStages, vs = j % kVStages;
-            if (!mbar_wait(&bars[K_FULL + ks], (j / kKStages) & 1, p.status, K_FULL, abort_flag)) break;
-            rotate_tile_inplace<T, kBM>(sK + ks * kTileBytes, p.packed_tab + (size_t)(j * kBN) * (kD / 2), tid, 1.0f);
+#ifdef COROPE_PROFILE
+            rt0 = clock64();
+#endif
+            if (!mbar_wait_warp(&bars[K_FULL + ks], (j / kKStages) & 1, p.status, K_FULL, abort_flag)) break;
+#ifdef COROPE_PROFILE
+            rw += clock64() - rt0; rt0 = clock64();
+#endif
+#ifndef COROPE_KO_ROT
+            rotate_tile_regs<T, kBN>(sK + ks * kTileBytes, tr, tid, 1.0f);
+#endif
             fence_proxy_async();
-            mbar_arrive(&bars[K_ROT + ks]);
-            if (!mbar_wait(&bars[V_FULL + vs], (j / kVStages) & 1, p.status, V_FULL, abort_flag)) break;
+            mbar_arrive_warp(&bars[K_ROT + ks], lane);
+            if (j + 1 < nk) load_table_regs<kBN>(tr, p.packed_tab + (size_t)((j + 1) * kBN) * (kD / 2), tid);  // in flight during the V pass
+#ifdef COROPE_PROFILE
+            rc += clock64() - rt0; rt0 = clock64();
+#endif
+            if (!mbar_wait_warp(&bars[V_FULL + vs], (j / kVStages) & 1, p.status, V_FULL, abort_flag)) break;
+#ifdef COROPE_PROFILE
+            rv += clock64() - rt0; rt0 = clock64();
+#endif
             if (kConvertV) {
+#ifndef COROPE_KO_ROT
                 convert_tile_bf16_to_f16(sV + vs * kTileBytes, tid);
+#endif
                 fence_proxy_async();
             }
-            mbar_arrive(&bars[V_READY + vs]);
+            mbar_arrive_warp(&bars[V_READY + vs], lane);
+#ifdef COROPE_PROFILE
+            rc += clock64() - rt0;
+#endif
         }
+#ifdef COROPE_PROFILE
+        if (p.prof && blockIdx.x < 64 && tid == 0) {
+            long long* o = p.prof + blockIdx.x * 16 + 10;
+            o[0] = rw; o[1] = rv; o[2] = rc;
+        }
+#endif
     } else {
         // ------------------------------------------------------------------ softmax groups
+        reg_alloc<kRegsSmx>();
         const int wg = (warp - kSmxWarp0) >> 2;
         const int quad = warp & 3;  // the TMEM lane quadrant a warp may touch is warp_id % 4
         const int row = quad * 32 + lane;
@@ -250,28 +350,51 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int nk_i = nk0 + wg;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
+#ifdef COROPE_PROFILE
+        long long sw = 0, sc = 0, st0;
+#endif
         for (int j = 0; j < nk_i; ++j) {
-            if (!(ok = mbar_wait(&bars[S_FULL + wg], j & 1, p.status, S_FULL + wg, abort_flag))) break;
+#ifdef COROPE_PROFILE
+            st0 = clock64();
+#endif
+            if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], j & 1, p.status, S_FULL + wg, abort_flag))) break;
+#ifdef COROPE_PROFILE
+            sw += clock64() - st0; st0 = clock64();
+#endif
             tc_fence_after();
             const bool diag = (j == nk_i - 1);
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                COROPE_TMEM_LD32(tS + c * 32, r);
-                tmem_wait_ld();
+#ifdef COROPE_KO_SMX
+            if (j > 0) { tc_fence_before(); mbar_arrive_warp(&bars[P_FULL + wg], lane); continue; }
+#endif
+            // whole S row into registers with one wait
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            COROPE_TMEM_LD32(tS, s0);
+            COROPE_TMEM_LD32(tS + 32, s1);
+            COROPE_TMEM_LD32(tS + 64, s2);
+            COROPE_TMEM_LD32(tS + 96, s3);
+            tmem_wait_ld();
+            if (diag) {   // causal mask on the diagonal tile: key column > query row
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(r[i]);
-                    if (diag && (c * 32 + i > row)) s = -INFINITY;
-                    mx = fmaxf(mx, s);
+                    if (i > row) s0[i] = 0xff800000u;
+                    if (32 + i > row) s1[i] = 0xff800000u;
+                    if (64 + i > row) s2[i] = 0xff800000u;
+                    if (96 + i > row) s3[i] = 0xff800000u;
                 }
             }
-            const float m_new = fmaxf(m, mx);
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+                mx1 = fmax3(mx1, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                mx2 = fmax3(mx2, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+                mx3 = fmax3(mx3, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
+            }
+            const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
             const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
             const float m_use = need ? m_new : m;
             if (j > 0 && __any_sync(0xffffffffu, need)) {
-                if (!(ok = mbar_wait(&bars[O_FULL + wg], (j - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (j - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
                 tc_fence_after();
                 const float alpha = fast_exp2(m - m_use);
 #pragma unroll
@@ -286,28 +409,39 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 l *= alpha;
             }
             m = m_use;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                COROPE_TMEM_LD32(tS + c * 32, r);
-                tmem_wait_ld();
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
-                    float p0 = fast_exp2(s0 - m), p1 = fast_exp2(s1 - m);
-                    if (diag && (c * 32 + 2 * i > row)) p0 = 0.f;
-                    if (diag && (c * 32 + 2 * i + 1 > row)) p1 = 0.f;
-                    l += p0 + p1;
-                    pk[i] = pack_half2(p0, p1);
-                }
-                COROPE_TMEM_ST16(tS + c * 16, pk);
+            float l0 = 0.f, l1 = 0.f;
+#define COROPE_EXP_CHUNK(sx, cidx)                                                       \
+            {                                                                            \
+                uint32_t pk[16];                                                         \
+                _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
+                    const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
+                    const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
+                    l0 += p0;                                                            \
+                    l1 += p1;                                                            \
+                    pk[i] = pack_half2(p0, p1);                                          \
+                }                                                                        \
+                COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
             }
+            COROPE_EXP_CHUNK(s0, 0)
+            COROPE_EXP_CHUNK(s1, 1)
+            COROPE_EXP_CHUNK(s2, 2)
+            COROPE_EXP_CHUNK(s3, 3)
+#undef COROPE_EXP_CHUNK
+            l += l0 + l1;
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[P_FULL + wg]);
+            mbar_arrive_warp(&bars[P_FULL + wg], lane);
+#ifdef COROPE_PROFILE
+            sc += clock64() - st0;
+#endif
         }
-        if (ok) ok = mbar_wait(&bars[O_FULL + wg], (nk_i - 1) & 1, p.status, O_FULL + wg, abort_flag);
+#ifdef COROPE_PROFILE
+        if (p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) {
+            long long* o = p.prof + blockIdx.x * 16 + 6 + wg * 2;
+            o[0] = sw; o[1] = sc;
+        }
+#endif
+        if (ok) ok = mbar_wait_warp(&bars[O_FULL + wg], (nk_i - 1) & 1, p.status, O_FULL + wg, abort_flag);
         if (ok) {
             tc_fence_after();
             const float inv = 1.f / l;
@@ -330,7 +464,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_before();
     }
     __syncthreads();
-    if (warp == 1) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }
