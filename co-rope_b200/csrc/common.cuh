@@ -124,7 +124,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false (after recording `id` in *status) when the limit is hit; callers
 // then leave their loops and fall through to the common exit path.  try_wait itself blocks for
 // a hardware-defined slice, so the limit corresponds to well over a second.
-constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kWaitLimit = 1u << 20;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
     for (uint32_t it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -287,6 +287,14 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
+// volatile variant: keeps its program order relative to the TMEM loads / stores, which bounds how far the compiler
+// can hoist the exponentials of later chunks (and with them the register pressure of the softmax loop)
+__device__ __forceinline__ float fast_exp2_ordered(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -352,32 +360,45 @@ __device__ __forceinline__ void load_table_regs(TabRegs<ROWS>& tr, const uint32_
     }
 }
 
-template <typename T, int ROWS>
+template <typename T, int ROWS, int BOX_BYTES = ROWS * 128>
 __device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<ROWS>& tr, int tid, float scale) {
-    constexpr int kBoxBytes = ROWS * 128;
+    constexpr int kBoxBytes = BOX_BYTES;   // distance between the [0,64) and [64,128) column boxes (ROWS may be part of a taller tile)
+    constexpr int kIters = ROWS / 16;
+    constexpr int kBatch = 4;                                        // rows in flight per thread: loads first, then math, then stores
     const float k1 = scale * (1.f / 32768.f), k0 = -257.f * scale;   // decode constants with the scale folded in
+    uint8_t* base = tile + (tid >> 3) * 128 + (tid & 7) * 16;
 #pragma unroll
-    for (int it = 0; it < ROWS / 16; ++it) {
-        const int row = it * 16 + (tid >> 3);
-        const uint32_t off = row * 128 + (tid & 7) * 16;
-        uint4 x1 = *reinterpret_cast<uint4*>(tile + off);
-        uint4 x2 = *reinterpret_cast<uint4*>(tile + kBoxBytes + off);
-        const uint4 t0 = tr.t[2 * it], t1 = tr.t[2 * it + 1];
-        uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w};
-        uint32_t b[4] = {x2.x, x2.y, x2.z, x2.w};
-        const uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+    for (int h = 0; h < kIters; h += kBatch) {
+        uint4 x1[kBatch], x2[kBatch];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
-            const float c0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7410)), k1, k0);
-            const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
-            const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
-            const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
-            a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
-            b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
+        for (int u = 0; u < kBatch; ++u) {
+            x1[u] = *reinterpret_cast<const uint4*>(base + (h + u) * 2048);
+            x2[u] = *reinterpret_cast<const uint4*>(base + kBoxBytes + (h + u) * 2048);
         }
-        *reinterpret_cast<uint4*>(tile + off) = make_uint4(a[0], a[1], a[2], a[3]);
-        *reinterpret_cast<uint4*>(tile + kBoxBytes + off) = make_uint4(b[0], b[1], b[2], b[3]);
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const uint4 t0 = tr.t[2 * (h + u)], t1 = tr.t[2 * (h + u) + 1];
+            uint32_t a[4] = {x1[u].x, x1[u].y, x1[u].z, x1[u].w};
+            uint32_t b[4] = {x2[u].x, x2[u].y, x2[u].z, x2[u].w};
+            const uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
+                const float c0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7410)), k1, k0);
+                const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
+                const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
+                const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
+                a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
+                b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
+            }
+            x1[u] = make_uint4(a[0], a[1], a[2], a[3]);
+            x2[u] = make_uint4(b[0], b[1], b[2], b[3]);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            *reinterpret_cast<uint4*>(base + (h + u) * 2048) = x1[u];
+            *reinterpret_cast<uint4*>(base + kBoxBytes + (h + u) * 2048) = x2[u];
+        }
     }
 }
 

@@ -14,9 +14,10 @@
 // dS^T is written once to shared memory (fp16, 128-byte swizzle) and is read both as the K-major A operand of
 // dK~ and as the MN-major B operand of dQ~^T; K~, Q~ and dO likewise serve two MMAs each from one buffer.
 //
-// Warp roles (576 threads): warp 0 TMA producer; warp 1 MMA issuer + TMEM owner; warps 2-5 rotation group
-// (K block once, every Q tile); warps 6-9 / 10-13 two softmax groups taking alternate steps; warps 14-17 drain
-// dQ~^T from TMEM and add it to the fp32 accumulator with reductions.  After the sweep the softmax groups write
+// Warp roles (640 threads = 5 warpgroups, registers re-divided with setmaxnreg): warp 0 TMA producer; warp 1 MMA
+// issuer + TMEM owner (warps 2-3 spare); warps 4-7 rotation group (K block once, every Q tile); warps 8-11 / 12-15
+// two softmax groups taking alternate steps; warps 16-19 drain dQ~^T from TMEM and add it to the fp32 accumulator
+// with reductions.  After the sweep the softmax groups write
 // dV and dK (inverse rotation and the ln2 factor applied in registers).
 // TMEM columns: S^T/P^T buffers [0,64) [64,128); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
 // A separate small kernel turns the fp32 dQ~ accumulator into dQ (inverse rotation, * sm_scale).
@@ -36,8 +37,13 @@ constexpr int kKVBox = kKVBytes / 2;
 constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
 constexpr int kQBox = kQBytes / 2;
 constexpr int kDsBytes = kBK * kBQ * 2;  // 16 KiB
-constexpr int kThreads = 576;
-constexpr int kRotWarp0 = 2, kSmxWarp0 = 6, kDrainWarp0 = 14;
+constexpr int kThreads = 640;             // five warpgroups: control (TMA, MMA, 2 spare) | rotation | softmax A | softmax B | dQ drain
+constexpr int kMmaWarp = 1;
+constexpr int kRotWarp0 = 4, kSmxWarp0 = 8, kDrainWarp0 = 16;
+// setmaxnreg only moves registers inside the CTA's own launch allocation (640 threads x 96): what the softmax groups
+// gain must be released by the others first, or their setmaxnreg.inc waits forever.  128 * (48 + 96 + 2 * 128 + 80) = 640 * 96.
+constexpr int kRegsCtl = 48, kRegsRot = 96, kRegsSmx = 128, kRegsDrain = 80;
+static_assert(128 * (kRegsCtl + kRegsRot + 2 * kRegsSmx + kRegsDrain) <= kThreads * 96, "register budget");
 constexpr int kHeadChunk = 4;
 
 enum Bar {
@@ -90,6 +96,9 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int n_steps = (N - jb * kBK) / kBQ;
     const int q_first = jb * kBK;                       // first query row this CTA visits
 
+    // A non-zero status word means an earlier CTA (of this or a previous launch) gave up on a wait: do not pile up
+    // more timeouts behind it.  The word stays set until the host reads and clears it.
+    if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(&bars[K_FULL], 1);
@@ -123,8 +132,11 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
+    // setmaxnreg sits inside each role's branch: placed before the dispatch, the merge point would force the
+    // smallest count on all the code that follows
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        reg_dealloc<kRegsCtl>();
         if (lane == 0) {
             const int kr = row_base + jb * kBK;
             mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
@@ -149,6 +161,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         __syncwarp();
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        reg_dealloc<kRegsCtl>();
         {
             const bool leader = elect_one();
             constexpr int kTFmt = Elem<T>::kDtype == COROPE_DTYPE_BF16 ? 1 : 0;
@@ -214,21 +227,24 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             if (leader) umma_commit(&bars[ACC_FULL]);
         }
         __syncwarp();
+    } else if (warp < kRotWarp0) {
+        reg_dealloc<kRegsCtl>();   // spare warps of the control group
     } else if (warp < kSmxWarp0) {
         // ------------------------------------------------------------------ rotation group
         const int tid = threadIdx.x - kRotWarp0 * 32;
         bool ok;
-        {
-            TabRegs<kBK> trk;
-            load_table_regs<kBK>(trk, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid);
+        TabRegs<kBQ> tr;
+        {   // the K block, once: two halves of 64 rows so that the same 32 table registers serve
+            load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid);
             ok = mbar_wait_warp(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
             if (ok) {
-                rotate_tile_regs<T, kBK>(sK, trk, tid, 1.0f);
+                rotate_tile_regs<T, kBQ, kKVBox>(sK, tr, tid, 1.0f);
+                load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(jb * kBK + kBQ) * (kD / 2), tid);
+                rotate_tile_regs<T, kBQ, kKVBox>(sK + kBQ * 128, tr, tid, 1.0f);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT], lane);
             }
         }
-        TabRegs<kBQ> tr;
         load_table_regs<kBQ>(tr, p.packed_tab + (size_t)q_first * (kD / 2), tid);
         for (int s = 0; ok && s < n_steps; ++s) {
             const int st = s % kStages;
@@ -240,6 +256,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
     } else if (warp < kDrainWarp0) {
         // ------------------------------------------------------------------ softmax groups (alternate steps)
+        reg_alloc<kRegsSmx>();
         const int wg = (warp - kSmxWarp0) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                 // key row within the block
@@ -343,6 +360,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_before();
     } else {
         // ------------------------------------------------------------------ dQ~^T drain: TMEM -> global fp32 reductions
+        reg_dealloc<kRegsDrain>();
         const int quad = warp & 3;
         const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;

@@ -34,11 +34,9 @@ constexpr int kThreads = 512;          // four warpgroups: control (TMA K, TMA V
 constexpr int kMmaWarp = 2;
 constexpr int kRotWarp0 = 4;
 constexpr int kSmxWarp0 = 8;
-#ifdef COROPE_REGS_ALT
-constexpr int kRegsCtl = 40, kRegsRot = 96, kRegsSmx = 184;
-#else
-constexpr int kRegsCtl = 56, kRegsRot = 104, kRegsSmx = 176;   // 128 * (56 + 104 + 2 * 176) = 65536 registers
-#endif
+// setmaxnreg only moves registers inside the CTA's own launch allocation (512 threads x 128): the sum must not exceed it
+constexpr int kRegsCtl = 56, kRegsRot = 120, kRegsSmx = 168;   // 128 * (56 + 120 + 2 * 168) = 65536 registers
+static_assert(128 * (kRegsCtl + kRegsRot + 2 * kRegsSmx) <= kThreads * 128, "register budget");
 constexpr int kHeadChunk = 8;
 
 enum Bar {
@@ -84,7 +82,12 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, RopeParams p) {
+#ifdef COROPE_P_NATIVE
+    constexpr bool kConvertV = false;   // experiment: P in the input's own 16-bit format, V untouched
+#else
     constexpr bool kConvertV = (Elem<T>::kDtype == COROPE_DTYPE_BF16);
+#endif
+    constexpr bool kPBf16 = !kConvertV && Elem<T>::kDtype == COROPE_DTYPE_BF16;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = sm;
@@ -109,6 +112,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int nk = 2 * t + 2;                           // K tiles seen by Q1; Q0 sees nk - 1
     const int nk0 = nk - 1;
 
+    // A non-zero status word means an earlier CTA (of this or a previous launch) gave up on a wait: do not pile up
+    // more timeouts behind it.  The word stays set until the host reads and clears it.
+    if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
@@ -392,11 +398,38 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             }
             const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
             const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
-            const float m_use = need ? m_new : m;
+            const float m_old = m;
+            m = need ? m_new : m;
+            float l0 = 0.f, l1 = 0.f;
+#define COROPE_EXP_CHUNK(sx, cidx)                                                       \
+            {                                                                            \
+                uint32_t pk[16];                                                         \
+                _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
+                    const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
+                    const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
+                    if (kPBf16) {                                                        \
+                        pk[i] = pack_bf162(p0, p1);                                      \
+                        const float2 pr = unpack_bf162(pk[i]);                           \
+                        l0 += pr.x;                                                      \
+                        l1 += pr.y;                                                      \
+                    } else {                                                             \
+                        l0 += p0;                                                        \
+                        l1 += p1;                                                        \
+                        pk[i] = pack_half2(p0, p1);                                      \
+                    }                                                                    \
+                }                                                                        \
+                COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
+            }
+            COROPE_EXP_CHUNK(s0, 0)
+            COROPE_EXP_CHUNK(s1, 1)
+            COROPE_EXP_CHUNK(s2, 2)
+            COROPE_EXP_CHUNK(s3, 3)
+#undef COROPE_EXP_CHUNK
+            // The rescale of O comes after P is written so that the S row is no longer live in registers.
             if (j > 0 && __any_sync(0xffffffffu, need)) {
                 if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (j - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
                 tc_fence_after();
-                const float alpha = fast_exp2(m - m_use);
+                const float alpha = fast_exp2(m_old - m);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -408,25 +441,6 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 }
                 l *= alpha;
             }
-            m = m_use;
-            float l0 = 0.f, l1 = 0.f;
-#define COROPE_EXP_CHUNK(sx, cidx)                                                       \
-            {                                                                            \
-                uint32_t pk[16];                                                         \
-                _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
-                    const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
-                    const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
-                    l0 += p0;                                                            \
-                    l1 += p1;                                                            \
-                    pk[i] = pack_half2(p0, p1);                                          \
-                }                                                                        \
-                COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
-            }
-            COROPE_EXP_CHUNK(s0, 0)
-            COROPE_EXP_CHUNK(s1, 1)
-            COROPE_EXP_CHUNK(s2, 2)
-            COROPE_EXP_CHUNK(s3, 3)
-#undef COROPE_EXP_CHUNK
             l += l0 + l1;
             tmem_wait_st();
             tc_fence_before();

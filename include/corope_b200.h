@@ -9,7 +9,9 @@
  * Return value: 0 = OK, < 0 = argument error found on the host (nothing was launched),
  * > 0 = a cudaError_t from a launch.  Kernels never trap: a device-side bounded wait that
  * expires writes a non-zero code into `*status_word` (device memory, may be NULL) and the
- * kernel exits cleanly.
+ * kernel exits cleanly.  While the word is non-zero, later tensor-core launches that are given the
+ * same word return without computing (their outputs are then undefined): read and clear it on the
+ * host after synchronising.
  *
  * Each entry point names the interface of the reference (Superposition09m/Co-RoPE) it stands in for.
  */
