@@ -40,6 +40,12 @@ WORKLOADS = {
 DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 THETA = 10000.0
 
+# DRAM bytes per launch of the two tensor-core kernels, from one ncu capture each (dram__bytes_read.sum +
+# dram__bytes_write.sum) at B=2 H=64 N=1024 D=128 bf16 -- 113.8 MB forward, 289.5 MB backward -- expressed per byte of
+# one [B,H,N,D] bf16 tensor (33.55 MB there).  Traffic of these kernels is proportional to the tensor bytes as long as a
+# head's K/V (and, backward, its fp32 dQ rows) fit in L2, which holds for every workload here.
+NCU_DRAM_PER_TENSOR_BYTE = {"fused_rope_fwd": 113.8 / 33.55, "fused_rope_bwd": 289.5 / 33.55}
+
 
 def flops_fwd(B, H, N, D):
     return 4.0 * B * H * N * N * D * 0.5
@@ -321,7 +327,11 @@ def main():
         "kernel_family": "tcgen05" if fam == 1 else "cuda-core fp32",
         "achieved": bwd_tf if dom_is_bwd else fwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops"], "peak_source": peaks["source"] + " cuBLAS bf16 burst",
-        "frac_of_sustained": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops_sustained"], "traffic": None,
+        "frac_of_sustained": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops_sustained"],
+        "traffic": (NCU_DRAM_PER_TENSOR_BYTE["fused_rope_bwd" if dom_is_bwd else "fused_rope_fwd"] * q.numel() * q.element_size()
+                    if (kind == "rope" and fam == 1) else None),
+        "traffic_unit": "bytes per launch (ncu capture at N=1024, scaled by tensor bytes)",
+        "algorithmic_flops": (2.5 * F if dom_is_bwd else F),
         "fwd": {"ms": fwd_ms, "tflops": fwd_tf, "frac": fwd_tf / peaks["tflops"]},
         "bwd": {"ms": bwd_ms, "tflops": bwd_tf, "frac": bwd_tf / peaks["tflops"]},
     }

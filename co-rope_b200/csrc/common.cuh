@@ -140,7 +140,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, i
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, id, abort_flag));
 }
 
-// 2-D tiled TMA load into shared memory, completion on an mbarrier (no multicast).
+// 2-D tiled TMA load into shared memory, completion on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
