@@ -163,3 +163,63 @@ def test_corope_general_kernels(dtype, tolf, tolb, cfg):
     assert excess(o, ro, tolf, dtype) <= 0
     for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
         assert excess(got, ref, tolb, dtype) <= 0
+
+
+def test_fused_rope_llama70b_1k_heads_bf16():
+    # heads of the Llama-70B-1K configuration (B=2, H=64, N=1024, D=128): 8 heads, the per-GPU share at 8 GPUs
+    B, H, N, D = 1, 8, 1024, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=7)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
+        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+
+
+def test_fused_rope_long_context_16k_full_gradients():
+    # one head at N = 16384: every output row and all three gradients against the row-blocked oracle
+    B, H, N, D = 1, 1, 16384, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=8)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024)
+    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
+        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+
+
+def test_fused_rope_long_context_64k_sampled_rows():
+    # one head of the Long-64K configuration (N = 65536): O and dQ on the first, a middle and the last block of 1024 rows
+    B, H, N, D = 1, 1, 65536, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=9)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, _, _ = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    blocks = [0, 37, 63]
+    ro, _, rdq, _, _ = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024, row_blocks=blocks)
+    for b in blocks:
+        sl = slice(b * 1024, (b + 1) * 1024)
+        assert excess(o[:, :, sl], ro[:, :, sl], TOL_FWD_16, torch.bfloat16) <= 0
+        assert excess(dq[:, :, sl], rdq[:, :, sl], TOL_BWD_16, torch.bfloat16) <= 0
+
+
+def test_corope_config4_unit_bf16():
+    # one (batch, KV head) unit of the Co-RoPE configuration (group of 4 query heads, D = 128): full check at N = 512,
+    # O / dQ on sampled row blocks at the full N = 2048
+    D, G = 128, 4
+    for N, blocks in ((512, None), (2048, [0, 31, 63])):
+        q = draw((1, G, N, D), 21, torch.bfloat16)
+        k = draw((1, 1, N, D), 22, torch.bfloat16)
+        v = draw((1, 1, N, D), 23, torch.bfloat16)
+        do = draw((1, G, N, D), 24, torch.bfloat16)
+        o, dq, dk, dv = run_corope(q, k, v, do, D ** -0.5, 10000.0)
+        ro, _, _, rdq, rdk, rdv = oracle.corope_gqa_fwd_bwd_chunked(q, k, v, do, D ** -0.5, 10000.0, rows=32, row_blocks=blocks)
+        if blocks is None:
+            assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+            for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
+                assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+        else:
+            for b in blocks:
+                sl = slice(b * 32, (b + 1) * 32)
+                assert excess(o[:, :, sl], ro[:, :, sl], TOL_FWD_16, torch.bfloat16) <= 0
+                assert excess(dq[:, :, sl], rdq[:, :, sl], TOL_BWD_16, torch.bfloat16) <= 0
