@@ -135,6 +135,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return false;
 }
 
+// Non-blocking probe of a phase, and a bounded spin on it.  try_wait parks the thread and wakes it some hundreds of
+// cycles after the phase completes; the MMA issuer sits on the critical path of every step, so it spins instead
+// (one warp; it backs off to try_wait after a while so that a long wait does not burn issue slots).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin_warp(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
+    bool done = false;
+    for (int it = 0; it < 4096 && !done; ++it) done = mbar_test_wait(bar, parity);
+    if (!done) done = mbar_wait(bar, parity, status, id, abort_flag);
+    return __all_sync(0xffffffffu, done);
+}
+
 // Same, for roles in which all 32 lanes wait: the outcome is made warp-uniform so that the lanes leave together.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
     return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, id, abort_flag));

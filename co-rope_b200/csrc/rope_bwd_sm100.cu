@@ -31,7 +31,13 @@ namespace {
 constexpr int kD = 128;
 constexpr int kBK = 128;                 // keys per CTA
 constexpr int kBQ = 64;                  // query rows per step
-constexpr int kStages = 3;               // Q / dO ring
+#ifdef COROPE_STAGES
+constexpr int kStages = COROPE_STAGES;
+#else
+constexpr int kStages = 4;               // Q / dO ring.  The sweep is latency-bound on this ring (stage free -> TMA -> rotation ->
+                                         // MMAs -> stage free): measured 1.56 / 1.08 ms with 2 / 3 stages, so it is as deep as
+                                         // shared memory allows
+#endif
 constexpr int kKVBytes = kBK * kD * 2;   // 32 KiB
 constexpr int kKVBox = kKVBytes / 2;
 constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
@@ -56,11 +62,14 @@ enum Bar {
     DQ_FULL = P_READY + 2,
     DQ_EMPTY = DQ_FULL + 2,
     ACC_FULL = DQ_EMPTY + 2,
-    NUM_BARS
+    DQ_DONE,                             // + buffer: dQ~^T of the step is in TMEM
+    NUM_BARS = DQ_DONE + 2
 };
 
 constexpr size_t kSmemData = 2 * kKVBytes + kStages * 2 * kQBytes + 2 * kDsBytes + kStages * 2 * kBQ * sizeof(float);
-constexpr size_t kSmemBytes = kSmemData + NUM_BARS * 8 + 64 + 1024;
+constexpr size_t kSmemSlack = 512;       // room to round the dynamic shared memory base up to 1024 bytes (checked at run time)
+constexpr size_t kSmemBytes = kSmemData + NUM_BARS * 8 + 64 + kSmemSlack;
+static_assert(kSmemBytes <= 232448, "shared memory budget");
 
 constexpr uint32_t TS0 = 0, TD0 = 128, TDV = 256, TDK = 384;
 
@@ -96,6 +105,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int n_steps = (N - jb * kBK) / kBQ;
     const int q_first = jb * kBK;                       // first query row this CTA visits
 
+    if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
+        return;
+    }
     // A non-zero status word means an earlier CTA (of this or a previous launch) gave up on a wait: do not pile up
     // more timeouts behind it.  The word stays set until the host reads and clears it.
     if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
@@ -111,9 +124,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bars[ST_FULL + b], 1);
-            mbar_init(&bars[P_READY + b], 4);
+            mbar_init(&bars[P_READY + b], 8);
             mbar_init(&bars[DQ_FULL + b], 1);
             mbar_init(&bars[DQ_EMPTY + b], 4);
+            mbar_init(&bars[DQ_DONE + b], 1);
         }
         mbar_init(&bars[ACC_FULL], 1);
         fence_mbar_init();
@@ -176,20 +190,29 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t k_lo = sdesc_lo(k_addr, 0), v_lo = sdesc_lo(v_addr, 0), q_lo = sdesc_lo(q_addr, 0), do_lo = sdesc_lo(do_addr, 0);
             const uint32_t do_mn = sdesc_lo(do_addr, kQBox), q_mn = sdesc_lo(q_addr, kQBox), k_mn = sdesc_lo(k_addr, kKVBox);
             const uint32_t ds_lo = sdesc_lo(ds_addr, 0);
-            auto issue_mma1 = [&](int st, int b) {
-                const uint32_t qb = q_lo + st * (kQBytes >> 4), dob = do_lo + st * (kQBytes >> 4);
+            auto issue_st = [&](int st, int b) {      // S^T = K~ Q~^T
+                const uint32_t qb = q_lo + st * (kQBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t offA = ((kk >> 2) * kKVBox + (kk & 3) * 32) >> 4, offB = ((kk >> 2) * kQBox + (kk & 3) * 32) >> 4;
                     if (leader) umma_ss2(tmem + TS0 + b * 64, k_lo + offA, kHi, qb + offB, kHi, id_st, kk > 0);
                 }
+            };
+            auto issue_dp = [&](int st, int b) {      // dP^T = V dO^T
+                const uint32_t dob = do_lo + st * (kQBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kD / 16; ++kk) {
                     const uint32_t offA = ((kk >> 2) * kKVBox + (kk & 3) * 32) >> 4, offB = ((kk >> 2) * kQBox + (kk & 3) * 32) >> 4;
                     if (leader) umma_ss2(tmem + TD0 + b * 64, v_lo + offA, kHi, dob + offB, kHi, id_dp, kk > 0);
                 }
             };
-            auto issue_mma2 = [&](int st, int b, bool acc) {
+            auto issue_dq = [&](int b) {              // dQ~^T = K~^T dS^T : K = 128 keys
+                const uint32_t dsb = ds_lo + b * (kDsBytes >> 4);
+#pragma unroll
+                for (int kk = 0; kk < kBK / 16; ++kk)
+                    if (leader) umma_ss2(tmem + TD0 + b * 64, k_mn + kk * (2048 >> 4), kHi, dsb + kk * (2048 >> 4), kHi, id_dq, kk > 0);
+            };
+            auto issue_dvdk = [&](int st, int b, bool acc) {
                 const uint32_t dob = do_mn + st * (kQBytes >> 4), qb = q_mn + st * (kQBytes >> 4), dsb = ds_lo + b * (kDsBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dV += P^T dO : K = 64 queries
@@ -197,34 +220,63 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
                     if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
-#pragma unroll
-                for (int kk = 0; kk < kBK / 16; ++kk)   // dQ~^T = K~^T dS^T : K = 128 keys
-                    if (leader) umma_ss2(tmem + TD0 + b * 64, k_mn + kk * (2048 >> 4), kHi, dsb + kk * (2048 >> 4), kHi, id_dq, kk > 0);
             };
             bool ok = mbar_wait_warp(&bars[K_ROT], 0, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], 0, p.status, V_FULL, abort_flag) &&
                       mbar_wait_warp(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_mma1(0, 0);
+                issue_st(0, 0);
+                issue_dp(0, 0);
                 if (leader) umma_commit(&bars[ST_FULL + 0]);
             }
+#ifdef COROPE_PROFILE
+            long long pw[5] = {0, 0, 0, 0, 0}, pt;
+            const long long pstart = clock64();
+#define PROF_T0 pt = clock64()
+#define PROF_ACC(i) pw[i] += clock64() - pt
+#else
+#define PROF_T0
+#define PROF_ACC(i)
+#endif
             for (int s = 0; ok && s < n_steps; ++s) {
                 const int b = s & 1;
                 if (s + 1 < n_steps) {
                     const int st1 = (s + 1) % kStages, b1 = (s + 1) & 1;
+                    PROF_T0;
                     if (!mbar_wait_warp(&bars[Q_ROT + st1], ((s + 1) / kStages) & 1, p.status, Q_ROT, abort_flag)) break;
-                    if (s + 1 >= 2 && !mbar_wait_warp(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
+                    PROF_ACC(0);
                     tc_fence_after();
-                    issue_mma1(st1, b1);
+                    PROF_T0;
+                    issue_st(st1, b1);       // S^T first: it does not need the dQ~^T buffer, so it runs while that drains
+                    PROF_ACC(3);
+                    PROF_T0;
+                    if (s + 1 >= 2 && !mbar_wait_warp(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
+                    PROF_ACC(1);
+                    tc_fence_after();
+                    PROF_T0;
+                    issue_dp(st1, b1);
                     if (leader) umma_commit(&bars[ST_FULL + b1]);
+                    PROF_ACC(3);
                 }
+                PROF_T0;
                 if (!mbar_wait_warp(&bars[P_READY + b], (s >> 1) & 1, p.status, P_READY, abort_flag)) break;
+                PROF_ACC(2);
                 tc_fence_after();
-                issue_mma2(s % kStages, b, s > 0);
-                if (leader) umma_commit(&bars[DQ_FULL + b]);
+                PROF_T0;
+                issue_dq(b);                           // first, so that its drain starts as early as possible
+                if (leader) umma_commit(&bars[DQ_DONE + b]);
+                issue_dvdk(s % kStages, b, s > 0);
+                if (leader) umma_commit(&bars[DQ_FULL + b]);      // everything that reads dS^T / P^T of this buffer is done
                 if (leader) umma_commit(&bars[QDO_EMPTY + s % kStages]);
+                PROF_ACC(4);
             }
             if (leader) umma_commit(&bars[ACC_FULL]);
+#ifdef COROPE_PROFILE
+            if (leader && p.prof && blockIdx.x < 64) {
+                long long* o = p.prof + blockIdx.x * 16;
+                o[0] = clock64() - pstart; o[1] = pw[0]; o[2] = pw[1]; o[3] = pw[2]; o[4] = pw[3]; o[5] = pw[4]; o[6] = n_steps;
+            }
+#endif
         }
         __syncwarp();
     } else if (warp < kRotWarp0) {
@@ -246,42 +298,77 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             }
         }
         load_table_regs<kBQ>(tr, p.packed_tab + (size_t)q_first * (kD / 2), tid);
+#ifdef COROPE_PROFILE
+        long long rw = 0, rc = 0, rt0;
+#endif
         for (int s = 0; ok && s < n_steps; ++s) {
             const int st = s % kStages;
+#ifdef COROPE_PROFILE
+            rt0 = clock64();
+#endif
             if (!mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
+#ifdef COROPE_PROFILE
+            rw += clock64() - rt0; rt0 = clock64();
+#endif
+#ifndef COROPE_KO_ROT
             rotate_tile_regs<T, kBQ>(sQ + st * kQBytes, tr, tid, p.sm_scale * kLog2e);
+#endif
             fence_proxy_async();
             mbar_arrive_warp(&bars[Q_ROT + st], lane);
             if (s + 1 < n_steps) load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ) * (kD / 2), tid);
+#ifdef COROPE_PROFILE
+            rc += clock64() - rt0;
+#endif
         }
+#ifdef COROPE_PROFILE
+        if (p.prof && blockIdx.x < 64 && tid == 0) { p.prof[blockIdx.x * 16 + 7] = rw; p.prof[blockIdx.x * 16 + 8] = rc; }
+#endif
     } else if (warp < kDrainWarp0) {
-        // ------------------------------------------------------------------ softmax groups (alternate steps)
+        // ------------------------------------------------------------------ softmax groups (each takes half the query columns of every step)
         reg_alloc<kRegsSmx>();
         const int wg = (warp - kSmxWarp0) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                 // key row within the block
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const uint32_t tS = tmem + lane_base + TS0 + wg * 64;
-        const uint32_t tD = tmem + lane_base + TD0 + wg * 64;
-        uint8_t* ds_row = sDS + wg * kDsBytes + row * 128;
         const int key = jb * kBK + row;
         bool ok = true;
-        for (int s = wg; s < n_steps; s += 2) {
-            const int u = s >> 1, st = s % kStages;
-            if (!(ok = mbar_wait_warp(&bars[ST_FULL + wg], u & 1, p.status, ST_FULL + wg, abort_flag))) break;
+#ifdef COROPE_PROFILE
+        long long sw = 0, sc = 0, sl = 0, st0;
+#endif
+        for (int s = 0; s < n_steps; ++s) {
+            const int u = s >> 1, st = s % kStages, b = s & 1;
+            const uint32_t tS = tmem + lane_base + TS0 + b * 64;
+            const uint32_t tD = tmem + lane_base + TD0 + b * 64;
+            uint8_t* ds_row = sDS + b * kDsBytes + row * 128;
+#ifdef COROPE_PROFILE
+            st0 = clock64();
+#endif
+            if (!(ok = mbar_wait_warp(&bars[ST_FULL + b], u & 1, p.status, ST_FULL + b, abort_flag))) break;
             if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
-            if (u > 0 && !(ok = mbar_wait_warp(&bars[DQ_FULL + wg], (u - 1) & 1, p.status, DQ_FULL + wg, abort_flag))) break;
+            if (u > 0 && !(ok = mbar_wait_warp(&bars[DQ_FULL + b], (u - 1) & 1, p.status, DQ_FULL + b, abort_flag))) break;
+#ifdef COROPE_PROFILE
+            sw += clock64() - st0; st0 = clock64();
+#endif
             tc_fence_after();
+#ifdef COROPE_KO_SMX
+            if (s > 1) { fence_proxy_async(); tc_fence_before(); mbar_arrive_warp(&bars[P_READY + b], lane); continue; }
+#endif
             const float* lse = sLD + st * 2 * kBQ;
             const float* dlt = lse + kBQ;
             const int q0 = q_first + s * kBQ;
             const bool diag = q0 < jb * kBK + kBK;        // some keys of this block lie above the diagonal for these queries
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
+            {
+                const int c = wg;   // this group's 32 query columns
                 uint32_t rs[32], rd[32];
+#ifdef COROPE_PROFILE
+                const long long l0 = clock64();
+#endif
                 COROPE_TMEM_LD32(tS + c * 32, rs);
                 COROPE_TMEM_LD32(tD + c * 32, rd);
                 tmem_wait_ld();
+#ifdef COROPE_PROFILE
+                sl += clock64() - l0;
+#endif
                 uint32_t pp[16], dd[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -307,8 +394,14 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tmem_wait_st();
             fence_proxy_async();
             tc_fence_before();
-            mbar_arrive_warp(&bars[P_READY + wg], lane);
+            mbar_arrive_warp(&bars[P_READY + b], lane);
+#ifdef COROPE_PROFILE
+            sc += clock64() - st0;
+#endif
         }
+#ifdef COROPE_PROFILE
+        if (p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) { p.prof[blockIdx.x * 16 + 9 + wg * 2] = sw; p.prof[blockIdx.x * 16 + 10 + wg * 2] = sc; if (wg == 0) p.prof[blockIdx.x * 16 + 15] = sl; }
+#endif
         // epilogue: group 0 writes dV, group 1 writes dK (inverse rotation, * ln2 because Q~ carried log2e)
         if (ok) ok = mbar_wait_warp(&bars[ACC_FULL], 0, p.status, ACC_FULL, abort_flag);
         if (ok) {
@@ -364,9 +457,20 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int quad = warp & 3;
         const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
+#ifdef COROPE_PROFILE
+        long long dw = 0, dc = 0, dt0;
+#endif
         for (int s = 0; s < n_steps; ++s) {
             const int b = s & 1;
-            if (!mbar_wait_warp(&bars[DQ_FULL + b], (s >> 1) & 1, p.status, DQ_FULL + b, abort_flag)) break;
+#ifdef COROPE_PROFILE
+            if (s > 0) dc += clock64() - dt0;
+            dt0 = clock64();
+#endif
+            if (!mbar_wait_warp(&bars[DQ_DONE + b], (s >> 1) & 1, p.status, DQ_DONE + b, abort_flag)) break;
+#ifdef COROPE_PROFILE
+            dw += clock64() - dt0; dt0 = clock64();
+            if (s == n_steps - 1 && p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) { p.prof[blockIdx.x * 16 + 13] = dw; p.prof[blockIdx.x * 16 + 14] = dc; }
+#endif
             tc_fence_after();
             uint32_t r0[32], r1[32];
             COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64, r0);
@@ -375,10 +479,14 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tc_fence_before();
             mbar_arrive_warp(&bars[DQ_EMPTY + b], lane);
             float* dst = p.dq_acc + ((size_t)row_base + q_first + s * kBQ) * kD + dcol;
+#ifndef COROPE_KO_DRAIN
 #pragma unroll
             for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)i * kD, __uint_as_float(r0[i]));
 #pragma unroll
             for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)(32 + i) * kD, __uint_as_float(r1[i]));
+#else
+            if (__uint_as_float(r0[0]) == 123.456f && __uint_as_float(r1[3]) == 1.f) dst[0] = 0.f;
+#endif
         }
     }
     __syncthreads();
@@ -388,19 +496,36 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     }
 }
 
-// dQ = inverse_rotate(dQ~ accumulator) * sm_scale, one thread per (row, d < 64) pair
+// dQ = inverse_rotate(dQ~ accumulator) * sm_scale; one thread per (row, 4 consecutive d < 64): 16-byte loads of the
+// accumulator halves and of the tables, 8-byte stores
 template <typename T>
 __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const float* __restrict__ cosT,
                                             const float* __restrict__ sinT, int64_t ts, size_t rows, int N, float scale) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= rows * 64) return;
-    const size_t row = idx >> 6;
-    const int d = (int)(idx & 63);
+    if (idx >= rows * 16) return;
+    const size_t row = idx >> 4;
+    const int d = (int)(idx & 15) * 4;
     const int pos = (int)(row % (size_t)N);
-    const float c = cosT[pos * ts + d], s = sinT[pos * ts + d];
-    const float a1 = acc[row * kD + d], a2 = acc[row * kD + d + 64];
-    dq[row * kD + d] = Elem<T>::from_f32((a1 * c + a2 * s) * scale);
-    dq[row * kD + d + 64] = Elem<T>::from_f32((a2 * c - a1 * s) * scale);
+    const float4 a1 = *reinterpret_cast<const float4*>(acc + row * kD + d);
+    const float4 a2 = *reinterpret_cast<const float4*>(acc + row * kD + d + 64);
+    float c[4], sn[4];
+    if ((ts & 3) == 0 && ((reinterpret_cast<uintptr_t>(cosT) | reinterpret_cast<uintptr_t>(sinT)) & 15) == 0) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosT + pos * ts + d));
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sinT + pos * ts + d));
+        c[0] = c4.x; c[1] = c4.y; c[2] = c4.z; c[3] = c4.w;
+        sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { c[i] = cosT[pos * ts + d + i]; sn[i] = sinT[pos * ts + d + i]; }
+    }
+    const float x1[4] = {a1.x, a1.y, a1.z, a1.w}, x2[4] = {a2.x, a2.y, a2.z, a2.w};
+    uint2 o1, o2;
+    o1.x = pack2<T>((x1[0] * c[0] + x2[0] * sn[0]) * scale, (x1[1] * c[1] + x2[1] * sn[1]) * scale);
+    o1.y = pack2<T>((x1[2] * c[2] + x2[2] * sn[2]) * scale, (x1[3] * c[3] + x2[3] * sn[3]) * scale);
+    o2.x = pack2<T>((x2[0] * c[0] - x1[0] * sn[0]) * scale, (x2[1] * c[1] - x1[1] * sn[1]) * scale);
+    o2.y = pack2<T>((x2[2] * c[2] - x1[2] * sn[2]) * scale, (x2[3] * c[3] - x1[3] * sn[3]) * scale);
+    *reinterpret_cast<uint2*>(dq + row * kD + d) = o1;
+    *reinterpret_cast<uint2*>(dq + row * kD + d + 64) = o2;
 }
 
 template <typename T>
@@ -420,7 +545,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, p); count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
-    const size_t n = rows * 64;
+    const size_t n = rows * 16;
     rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.cos, p.sin,
                                                                               p.table_stride, rows, p.N, p.sm_scale); count_launch();
     return (int)cudaGetLastError();

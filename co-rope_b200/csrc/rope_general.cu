@@ -204,6 +204,29 @@ __global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__
     if (lane == 0) delta[row] = s;
 }
 
+// Same for 16-bit elements and D = 128: 16 threads per row, 16 bytes of O and of dO per thread.
+template <typename T>
+__global__ void rope_delta_d128_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows) {
+    const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t row = t >> 4;
+    const int part = (int)(t & 15);
+    float s = 0.f;
+    if (row < rows) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + row * 128) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + row * 128) + part);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = unpack2<T>(aw[i]), fb = unpack2<T>(bw[i]);
+            s = fmaf(fa.x, fb.x, s);
+            s = fmaf(fa.y, fb.y, s);
+        }
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (part == 0 && row < rows) delta[row] = s;
+}
+
 // ------------------------------------------------------------------------------------------------
 // backward, dQ: one CTA per 32 query rows, streams K/V tiles
 // ------------------------------------------------------------------------------------------------
@@ -416,6 +439,15 @@ int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s) {
 
 int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     size_t rows = (size_t)p.B * p.H * p.N;
+    if (p.D == 128 && dtype != COROPE_DTYPE_F32) {
+        const unsigned blocks = (unsigned)((rows * 16 + 255) / 256);
+        if (dtype == COROPE_DTYPE_BF16)
+            rope_delta_d128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows);
+        else
+            rope_delta_d128_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows);
+        count_launch();
+        return (int)cudaGetLastError();
+    }
     const int warps = 8;
     unsigned blocks = (unsigned)((rows + warps - 1) / warps);
     switch (dtype) {
