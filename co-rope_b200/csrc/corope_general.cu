@@ -27,7 +27,8 @@ namespace {
 constexpr int kWarps = 8;      // query rows per CTA
 constexpr int kTile = 32;      // keys per step
 constexpr int kThreads = kWarps * 32;
-constexpr int kMaxG = 8;
+constexpr int kPad = 4;        // row padding (floats) of the per-lane K / V tiles: rows stay 16-byte aligned and 16-byte loads of 8
+                               // consecutive lanes fall into distinct bank groups
 
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
@@ -59,9 +60,13 @@ __device__ __forceinline__ float warp_suffix_incl(float v, int lane) {
 }
 
 template <bool ACCURATE>
-__device__ __forceinline__ void sincos_phase(float x, float* s, float* c) {
+__device__ __forceinline__ void sincos_phase(float x, float* s, float* c, bool direct) {
     if (ACCURATE) {
         sincosf(x, s, c);
+    } else if (direct) {
+        // phases up to a few thousand radians (N <= 8192): the hardware approximations alone; their internal range
+        // reduction in fp32 costs ~1e-4 rad there, far inside the 16-bit tolerance
+        __sincosf(x, s, c);
     } else {
         // 16-bit inputs: two-constant reduction to [-pi, pi] then the fast hardware approximations
         float kf = rintf(x * 0.15915494309189535f);
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
     extern __shared__ __align__(16) float smem[];
     float* q_s = smem;                         // [G][8][D]
     float* k_s = q_s + G * kWarps * D;         // [32][D+1]
-    float* v_s = k_s + kTile * (D + 1);        // [32][D]
+    float* v_s = k_s + kTile * (D + kPad);        // [32][D]
     float* w_s = v_s + kTile * D;              // [H2] inverse frequencies
 
     const int N = p.N;
@@ -117,21 +122,29 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
     }
     float carry = 0.f;  // sum of z_ik over keys already swept (k > current tile), for this warp's row
     const float sc2 = p.sm_scale * kLog2e;
+    const bool direct = p.N <= 8192;
     const int i_last = min(N - 1, i0 + kWarps - 1);
     for (int j0 = (i_last / kTile) * kTile; j0 >= 0; j0 -= kTile) {
         __syncthreads();
-        stage_plain<T, D>(k_s, D + 1, K, j0, kTile, N);
+        stage_plain<T, D>(k_s, D + kPad, K, j0, kTile, N);
         stage_plain<T, D>(v_s, D, V, j0, kTile, N);
         __syncthreads();
         if (i >= N) continue;
         const int j = j0 + lane;
         const bool vis = (j <= i);  // implies j < N
-        const float* kr = k_s + lane * (D + 1);
+        const float* kr = k_s + lane * (D + kPad);
         const float* qL = q_s + warp * D;
-        // leader score -> z
+        // leader score -> z   (16-byte shared-memory loads throughout: the loop is load-issue bound otherwise)
         float dot = 0.f;
-#pragma unroll 8
-        for (int d = 0; d < D; ++d) dot = fmaf(qL[d], kr[d], dot);
+#pragma unroll 4
+        for (int d = 0; d < D; d += 4) {
+            const float4 a = *reinterpret_cast<const float4*>(qL + d);
+            const float4 b = *reinterpret_cast<const float4*>(kr + d);
+            dot = fmaf(a.x, b.x, dot);
+            dot = fmaf(a.y, b.y, dot);
+            dot = fmaf(a.z, b.z, dot);
+            dot = fmaf(a.w, b.w, dot);
+        }
         float z = vis ? 1.f / (1.f + __expf(-dot * p.sm_scale)) : 0.f;
         // Delta_ij = sum_{k=j+1..i} z_ik = carry + (suffix over lanes above this one)
         float suf = warp_suffix_incl(z, lane);
@@ -141,18 +154,32 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
         float s[G];
 #pragma unroll
         for (int h = 0; h < G; ++h) s[h] = 0.f;
-#pragma unroll 2
-        for (int d = 0; d < H2; ++d) {
-            float sn, cs;
-            sincos_phase<ACCURATE>(delta * w_s[d], &sn, &cs);
-            float k1 = kr[d], k2 = kr[d + H2];
-            float r1 = fmaf(k1, cs, k2 * sn);
-            float r2 = fmaf(k2, cs, -k1 * sn);
+#pragma unroll 1
+        for (int d = 0; d < H2; d += 4) {
+            const float4 w4 = *reinterpret_cast<const float4*>(w_s + d);
+            const float4 k1v = *reinterpret_cast<const float4*>(kr + d);
+            const float4 k2v = *reinterpret_cast<const float4*>(kr + d + H2);
+            const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+            const float k1a[4] = {k1v.x, k1v.y, k1v.z, k1v.w}, k2a[4] = {k2v.x, k2v.y, k2v.z, k2v.w};
+            float r1[4], r2[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sn, cs;
+                sincos_phase<ACCURATE>(delta * wv[e], &sn, &cs, direct);
+                r1[e] = fmaf(k1a[e], cs, k2a[e] * sn);
+                r2[e] = fmaf(k2a[e], cs, -k1a[e] * sn);
+            }
 #pragma unroll
             for (int h = 0; h < G; ++h) {
                 const float* qh = q_s + (h * kWarps + warp) * D;
-                s[h] = fmaf(qh[d], r1, s[h]);
-                s[h] = fmaf(qh[d + H2], r2, s[h]);
+                const float4 q1v = *reinterpret_cast<const float4*>(qh + d);
+                const float4 q2v = *reinterpret_cast<const float4*>(qh + d + H2);
+                float acc = s[h];
+                acc = fmaf(q1v.x, r1[0], acc); acc = fmaf(q2v.x, r2[0], acc);
+                acc = fmaf(q1v.y, r1[1], acc); acc = fmaf(q2v.y, r2[1], acc);
+                acc = fmaf(q1v.z, r1[2], acc); acc = fmaf(q2v.z, r2[2], acc);
+                acc = fmaf(q1v.w, r1[3], acc); acc = fmaf(q2v.w, r2[3], acc);
+                s[h] = acc;
             }
         }
         // online softmax per head (log2 domain), then P V with lane = column
@@ -224,8 +251,8 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     float* q_s = smem;                            // [G][8][D]
     float* do_s = q_s + G * kWarps * D;           // [G][8][D]
     float* k_s = do_s + G * kWarps * D;           // [32][D+1]
-    float* v_s = k_s + kTile * (D + 1);           // [32][D+1]
-    float* dk_t = v_s + kTile * (D + 1);          // [32][D] tile accumulators shared by the CTA's 8 rows
+    float* v_s = k_s + kTile * (D + kPad);           // [32][D+1]
+    float* dk_t = v_s + kTile * (D + kPad);          // [32][D] tile accumulators shared by the CTA's 8 rows
     float* dv_t = dk_t + kTile * D;               // [32][D]
     float* w_s = dv_t + kTile * D;                // [H2]
     float* xch = w_s + H2;                        // [8][kXch]
@@ -264,22 +291,30 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     const float a_ii = i < N ? p.a_diag[(size_t)bg * N + i] : 0.f;
     float carry_a = 0.f, carry_g = 0.f;
     const float sc2 = p.sm_scale * kLog2e;
+    const bool direct = p.N <= 8192;
     const int i_last = min(N - 1, i0 + kWarps - 1);
     for (int j0 = 0; j0 <= i_last; j0 += kTile) {
         __syncthreads();   // previous tile's flush done, accumulators are zero
-        stage_plain<T, D>(k_s, D + 1, K, j0, kTile, N);
-        stage_plain<T, D>(v_s, D + 1, V, j0, kTile, N);
+        stage_plain<T, D>(k_s, D + kPad, K, j0, kTile, N);
+        stage_plain<T, D>(v_s, D + kPad, V, j0, kTile, N);
         __syncthreads();
         if (i < N && j0 <= i) {
             // ---------------- phase A: lane = key
             const int j = j0 + lane;
             const bool vis = (j <= i);
-            const float* kr = k_s + lane * (D + 1);
-            const float* vr = v_s + lane * (D + 1);
+            const float* kr = k_s + lane * (D + kPad);
+            const float* vr = v_s + lane * (D + kPad);
             const float* qL = q_s + warp * D;
             float dot = 0.f;
-#pragma unroll 8
-            for (int d = 0; d < D; ++d) dot = fmaf(qL[d], kr[d], dot);
+#pragma unroll 4
+            for (int d = 0; d < D; d += 4) {
+                const float4 a = *reinterpret_cast<const float4*>(qL + d);
+                const float4 b = *reinterpret_cast<const float4*>(kr + d);
+                dot = fmaf(a.x, b.x, dot);
+                dot = fmaf(a.y, b.y, dot);
+                dot = fmaf(a.z, b.z, dot);
+                dot = fmaf(a.w, b.w, dot);
+            }
             const float z = vis ? 1.f / (1.f + __expf(-dot * p.sm_scale)) : 0.f;
             const float pre = warp_prefix_incl(z, lane);
             const float delta = a_ii - (carry_a + pre);
@@ -287,30 +322,49 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
             float s[G], tq[G], dp[G];
 #pragma unroll
             for (int h = 0; h < G; ++h) s[h] = tq[h] = dp[h] = 0.f;
-#pragma unroll 2
-            for (int d = 0; d < H2; ++d) {
-                float sn, cs;
-                const float w = w_s[d];
-                sincos_phase<ACCURATE>(delta * w, &sn, &cs);
-                float k1 = kr[d], k2 = kr[d + H2];
-                float r1 = fmaf(k1, cs, k2 * sn);
-                float r2 = fmaf(k2, cs, -k1 * sn);
-                float wr1 = w * r1, wr2 = w * r2;
+#pragma unroll 1
+            for (int d = 0; d < H2; d += 4) {
+                const float4 w4 = *reinterpret_cast<const float4*>(w_s + d);
+                const float4 k1v = *reinterpret_cast<const float4*>(kr + d);
+                const float4 k2v = *reinterpret_cast<const float4*>(kr + d + H2);
+                const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+                const float k1a[4] = {k1v.x, k1v.y, k1v.z, k1v.w}, k2a[4] = {k2v.x, k2v.y, k2v.z, k2v.w};
+                float r1[4], r2[4], wr1[4], wr2[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sn, cs;
+                    sincos_phase<ACCURATE>(delta * wv[e], &sn, &cs, direct);
+                    r1[e] = fmaf(k1a[e], cs, k2a[e] * sn);
+                    r2[e] = fmaf(k2a[e], cs, -k1a[e] * sn);
+                    wr1[e] = wv[e] * r1[e];
+                    wr2[e] = wv[e] * r2[e];
+                }
 #pragma unroll
                 for (int h = 0; h < G; ++h) {
                     const float* qh = q_s + (h * kWarps + warp) * D;
-                    float q1 = qh[d], q2 = qh[d + H2];
-                    s[h] = fmaf(q1, r1, s[h]);
-                    s[h] = fmaf(q2, r2, s[h]);
-                    tq[h] = fmaf(q2, wr1, tq[h]);
-                    tq[h] = fmaf(-q1, wr2, tq[h]);
+                    const float4 q1v = *reinterpret_cast<const float4*>(qh + d);
+                    const float4 q2v = *reinterpret_cast<const float4*>(qh + d + H2);
+                    const float q1a[4] = {q1v.x, q1v.y, q1v.z, q1v.w}, q2a[4] = {q2v.x, q2v.y, q2v.z, q2v.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        s[h] = fmaf(q1a[e], r1[e], s[h]);
+                        s[h] = fmaf(q2a[e], r2[e], s[h]);
+                        tq[h] = fmaf(q2a[e], wr1[e], tq[h]);
+                        tq[h] = fmaf(-q1a[e], wr2[e], tq[h]);
+                    }
                 }
             }
-#pragma unroll 4
-            for (int d = 0; d < D; ++d) {
-                float vv = vr[d];
+#pragma unroll 2
+            for (int d = 0; d < D; d += 4) {
+                const float4 vv = *reinterpret_cast<const float4*>(vr + d);
 #pragma unroll
-                for (int h = 0; h < G; ++h) dp[h] = fmaf(do_s[(h * kWarps + warp) * D + d], vv, dp[h]);
+                for (int h = 0; h < G; ++h) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(do_s + (h * kWarps + warp) * D + d);
+                    dp[h] = fmaf(g4.x, vv.x, dp[h]);
+                    dp[h] = fmaf(g4.y, vv.y, dp[h]);
+                    dp[h] = fmaf(g4.z, vv.z, dp[h]);
+                    dp[h] = fmaf(g4.w, vv.w, dp[h]);
+                }
             }
             float gD = 0.f;
 #pragma unroll
@@ -336,8 +390,8 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
                     const int pd = lane + 32 * pi;
                     if (pd < H2) {
                         float sn, cs;
-                        sincos_phase<ACCURATE>(dlt * w_s[pd], &sn, &cs);
-                        float k1 = k_s[jj * (D + 1) + pd], k2 = k_s[jj * (D + 1) + pd + H2];
+                        sincos_phase<ACCURATE>(dlt * w_s[pd], &sn, &cs, direct);
+                        float k1 = k_s[jj * (D + kPad) + pd], k2 = k_s[jj * (D + kPad) + pd + H2];
                         float r1 = fmaf(k1, cs, k2 * sn);
                         float r2 = fmaf(k2, cs, -k1 * sn);
                         float a1 = 0.f, a2 = 0.f;
@@ -397,7 +451,7 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
 template <typename T, int D, int G>
 int launch_fwd_g(const GqaParams& p, cudaStream_t s) {
     constexpr bool kAcc = (Elem<T>::kDtype == COROPE_DTYPE_F32);
-    size_t smem = sizeof(float) * ((size_t)G * kWarps * D + kTile * (D + 1) + kTile * D + D / 2);
+    size_t smem = sizeof(float) * ((size_t)G * kWarps * D + kTile * (D + kPad) + kTile * D + D / 2);
     auto kern = corope_fwd_general_kernel<T, D, G, kAcc>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -409,7 +463,7 @@ int launch_fwd_g(const GqaParams& p, cudaStream_t s) {
 template <typename T, int D, int G>
 int launch_bwd_g(const GqaParams& p, cudaStream_t s) {
     constexpr bool kAcc = (Elem<T>::kDtype == COROPE_DTYPE_F32);
-    size_t smem = sizeof(float) * ((size_t)2 * G * kWarps * D + 2 * kTile * (D + 1) + 2 * kTile * D + D / 2 + (size_t)kWarps * (2 * G + 2) * kTile);
+    size_t smem = sizeof(float) * ((size_t)2 * G * kWarps * D + 2 * kTile * (D + kPad) + 2 * kTile * D + D / 2 + (size_t)kWarps * (2 * G + 2) * kTile);
     auto kern = corope_bwd_general_kernel<T, D, G, kAcc>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
