@@ -22,7 +22,7 @@ RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dt
     RopeWorkspace w{};
     size_t off = 0;
     w.packed_tab = off;
-    off += align_up((size_t)N * (D / 2) * sizeof(uint32_t), kAlign);
+    off += align_up((size_t)N * (D / 2) * sizeof(uint32_t) + 64, kAlign);   // + the work counter behind the table
     if (bwd) {
         w.delta = off;
         off += align_up((size_t)B * H * N * sizeof(float), kAlign);
@@ -138,6 +138,7 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
+        p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));
         g_last_family[COROPE_OP_ROPE_FWD] = 1;
         return launch_rope_fwd_tc(p, dtype, s);
     }

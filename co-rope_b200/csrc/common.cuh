@@ -60,6 +60,7 @@ struct RopeParams {
     int causal;
     float sm_scale;
     int* status;
+    int* sched_counter; // zeroed word in the workspace: next work item of the persistent forward kernel
     long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise
 };
 

@@ -11,7 +11,7 @@ namespace {
 // Scratch: packed (cos, sin) table, one 32-bit entry per (position, d < D/2).  2 MiB per GPU that loads the
 // library, held until the process exits.  Enough for N * D/2 <= 524288, i.e. N <= 8192 at D = 128.
 constexpr size_t kNoAllocMaxEntries = (size_t)8192 * 64;
-static __device__ __align__(256) uint32_t g_noalloc_table[kNoAllocMaxEntries];
+static __device__ __align__(256) uint32_t g_noalloc_table[kNoAllocMaxEntries + 64];   // + the forward kernel's work counter behind the table
 
 // In host code `g_noalloc_table` is only a handle for the runtime, not an address a kernel can use; the device
 // address is looked up once per device (with that device current) and cached here.
@@ -62,6 +62,7 @@ extern "C" int corope_rope_attn_fwd_noalloc(const void* q, const void* k, const 
         // the table is rebuilt in full for rows [0, N) on every call, so stale contents of an earlier call are never read
         if (int e = launch_pack_tables(cos, sin, table_row_stride, table, N, D / 2, s)) return e;
         p.packed_tab = table;
+        p.sched_counter = reinterpret_cast<int*>(table + (size_t)N * (D / 2));
         return launch_rope_fwd_tc(p, dtype, s);
     }
     return launch_rope_fwd_general(p, dtype, s);  // the general kernels use no scratch at all

@@ -19,7 +19,7 @@
 // two softmax groups taking alternate steps; warps 16-19 drain dQ~^T from TMEM and add it to the fp32 accumulator
 // with reductions.  After the sweep the softmax groups write
 // dV and dK (inverse rotation and the ln2 factor applied in registers).
-// TMEM columns: S^T/P^T buffers [0,64) [64,128); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
+// TMEM columns: S^T/P^T buffers [0,64) [64,128) (P^T of queries 0-31 in columns 0-15, of queries 32-63 in columns 32-47); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
 // A separate small kernel turns the fp32 dQ~ accumulator into dQ (inverse rotation, * sm_scale).
 //
 // Replaces _attn_bwd / _attn_bwd_dkdv / _attn_bwd_dq of the reference (fused-rope/fused_rope_attn.py:341-649).
@@ -216,7 +216,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const uint32_t dob = do_mn + st * (kQBytes >> 4), qb = q_mn + st * (kQBytes >> 4), dsb = ds_lo + b * (kDsBytes >> 4);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dV += P^T dO : K = 64 queries
-                    if (leader) umma_ts2(tmem + TDV, tmem + TS0 + b * 64 + kk * 8, dob + kk * (2048 >> 4), kHi, id_dv, (acc || kk > 0) ? 1u : 0u);
+                    if (leader) umma_ts2(tmem + TDV, tmem + TS0 + b * 64 + (kk >> 1) * 32 + (kk & 1) * 8, dob + kk * (2048 >> 4), kHi, id_dv, (acc || kk > 0) ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
                     if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
@@ -384,7 +384,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     pp[i] = pack2<T>(p0, p1);
                     dd[i] = pack_half2(s0, s1);
                 }
-                COROPE_TMEM_ST16(tS + c * 16, pp);
+                COROPE_TMEM_ST16(tS + c * 32, pp);   // each group writes P^T over the start of its own 32 S^T columns: the other group's S^T may still be unread
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const int chunk = (c * 4 + w) ^ (row & 7);

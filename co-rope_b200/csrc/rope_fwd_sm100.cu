@@ -38,6 +38,8 @@ constexpr int kSmxWarp0 = 8;
 constexpr int kRegsCtl = 56, kRegsRot = 120, kRegsSmx = 168;   // 128 * (56 + 120 + 2 * 168) = 65536 registers
 static_assert(128 * (kRegsCtl + kRegsRot + 2 * kRegsSmx) <= kThreads * 128, "register budget");
 constexpr int kHeadChunk = 8;
+constexpr int kItemSlots = 4;
+constexpr int kItemReaders = 1 + 1 + 4 + 4 + 4;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
 
 enum Bar {
     Q_FULL = 0,                        // +i
@@ -51,11 +53,15 @@ enum Bar {
     S_FULL = V_EMPTY + kVStages,       // +i
     P_FULL = S_FULL + 2,
     O_FULL = P_FULL + 2,
-    NUM_BARS = O_FULL + 2
+    Q_EMPTY = O_FULL + 2,              // +i: the item's last Q_i K^T has completed, the Q_i buffer may be reloaded
+    O_FREE = Q_EMPTY + 2,              // +i: the item's output has been read out of TMEM, O_i may be overwritten
+    ITEM_FULL = O_FREE + 2,            // +slot: a work item index has been published in the item ring
+    ITEM_EMPTY = ITEM_FULL + kItemSlots,   // +slot: every role has read it
+    NUM_BARS = ITEM_EMPTY + kItemSlots
 };
 
 constexpr size_t kSmemTiles = (size_t)(2 + kKStages + kVStages) * kTileBytes;
-constexpr size_t kSmemBytes = kSmemTiles + NUM_BARS * 8 + 64 + 1024;  // + alignment slack
+constexpr size_t kSmemBytes = kSmemTiles + NUM_BARS * 8 + 64 + 1024;  // + alignment slack (tmem slot, abort flag and the item ring live in the 64)
 
 // bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
 __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
@@ -78,16 +84,45 @@ __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid)
     }
 }
 
+// Work items (one = 256 query rows of one head) in the order CTAs take them: heads in chunks of kHeadChunk so that
+// the items in flight at one time share few heads (their K/V stay in L2), heaviest query blocks first inside a chunk.
+struct WorkItem {
+    int t, bh;
+};
+__device__ __forceinline__ WorkItem work_item(int w, int n_qt, int BH) {
+    const int chunk_items = kHeadChunk * n_qt;
+    const int chunk = w / chunk_items, within = w % chunk_items;
+    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
+    WorkItem it;
+    it.t = n_qt - 1 - within / heads_here;
+    it.bh = chunk * kHeadChunk + within % heads_here;
+    return it;
+}
+
+// Consumer side of the item ring: the n-th item of this CTA, or -1 when there is none left (or a wait gave up).
+// Warp roles call it with all 32 lanes (one arrival per warp); the V producer calls it from its single thread.
+__device__ __forceinline__ int fetch_item(uint64_t* bars, volatile int* item_ring, int n, int lane, bool whole_warp, int* status,
+                                          volatile int* abort_flag) {
+    const int slot = n % kItemSlots;
+    const uint32_t parity = (n / kItemSlots) & 1;
+    int w = -1;
+    if (whole_warp) {
+        if (!mbar_wait_warp(&bars[ITEM_FULL + slot], parity, status, ITEM_FULL, abort_flag)) return -1;
+        w = item_ring[slot];
+        mbar_arrive_warp(&bars[ITEM_EMPTY + slot], lane);
+    } else {
+        if (!mbar_wait(&bars[ITEM_FULL + slot], parity, status, ITEM_FULL, abort_flag)) return -1;
+        w = item_ring[slot];
+        mbar_arrive(&bars[ITEM_EMPTY + slot]);
+    }
+    return w;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, RopeParams p) {
-#ifdef COROPE_P_NATIVE
-    constexpr bool kConvertV = false;   // experiment: P in the input's own 16-bit format, V untouched
-#else
     constexpr bool kConvertV = (Elem<T>::kDtype == COROPE_DTYPE_BF16);
-#endif
-    constexpr bool kPBf16 = !kConvertV && Elem<T>::kDtype == COROPE_DTYPE_BF16;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = sm;
@@ -96,21 +131,19 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kVStages * kTileBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* item_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [kItemSlots]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
     const int BH = p.B * p.H;
     const int n_qt = N / (2 * kBM);
-    // CTA order: heads in chunks of kHeadChunk (so that the CTAs resident at one time share few heads and their
-    // K/V stay in L2), within a chunk the heaviest (latest) query blocks first
-    const int chunk_ctas = kHeadChunk * n_qt;
-    const int chunk = (int)blockIdx.x / chunk_ctas, within = (int)blockIdx.x % chunk_ctas;
-    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
-    const int t = n_qt - 1 - within / heads_here;
-    const int bh = chunk * kHeadChunk + within % heads_here;
-    const int row_base = bh * N;                        // row in the [B*H*N, D] view
-    const int nk = 2 * t + 2;                           // K tiles seen by Q1; Q0 sees nk - 1
-    const int nk0 = nk - 1;
+    const int n_items = n_qt * BH;
+    // Persistent CTAs with a dynamic schedule: the first item of CTA c is c, further ones come from a global counter
+    // (heavy items first, so the greedy order balances to a few percent; a static round-robin was 19 % off).  The K
+    // producer fetches an item, publishes it in a small shared-memory ring and every other role reads it from there.
+    // Every role walks the same item sequence and keeps running counters (K tiles, V tiles, S tiles per group, items) from which ring stages and mbarrier parities follow, so the
+    // pipeline runs across item boundaries: the next item's Q and K tiles are loaded and rotated while the current
+    // item's last tiles are still in the MMAs and its output is being written.
 
     // A non-zero status word means an earlier CTA (of this or a previous launch) gave up on a wait: do not pile up
     // more timeouts behind it.  The word stays set until the host reads and clears it.
@@ -120,9 +153,15 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars[Q_FULL + i], 1);
             mbar_init(&bars[Q_ROT + i], 4);
+            mbar_init(&bars[Q_EMPTY + i], 1);
             mbar_init(&bars[S_FULL + i], 1);
             mbar_init(&bars[P_FULL + i], 4);
             mbar_init(&bars[O_FULL + i], 1);
+            mbar_init(&bars[O_FREE + i], 4);
+        }
+        for (int i = 0; i < kItemSlots; ++i) {
+            mbar_init(&bars[ITEM_FULL + i], 1);
+            mbar_init(&bars[ITEM_EMPTY + i], kItemReaders);
         }
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&bars[K_FULL + s], 1);
@@ -153,137 +192,138 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         // producers and the MMA issuer need few registers: hand the rest to the softmax groups
         reg_dealloc<kRegsCtl>();
         if (warp == 0) {
-            // -------------------------------------------------------------- TMA producer: Q once, then the K ring
+            // -------------------------------------------------------------- TMA producer: Q per item, and the K ring
             if (lane == 0) {
-                for (int i = 0; i < 2; ++i) {
-                    const int r = row_base + t * 2 * kBM + i * kBM;
-                    mbar_arrive_expect_tx(&bars[Q_FULL + i], kTileBytes);
-                    tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
-                    tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
-                }
-                for (int j = 0; j < nk; ++j) {
-                    const int r = row_base + j * kBN;
-                    const int ks = j % kKStages;
-                    if (j >= kKStages && !mbar_wait(&bars[K_EMPTY + ks], ((j / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag)) break;
-                    mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
-                    tma_load_2d(sK + ks * kTileBytes, &mapK, 0, r, &bars[K_FULL + ks]);
-                    tma_load_2d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, &bars[K_FULL + ks]);
+                int gk = 0;
+                bool ok = true;
+                for (int n = 0; ok; ++n) {
+                    const int slot = n % kItemSlots;
+                    if (n >= kItemSlots && !(ok = mbar_wait(&bars[ITEM_EMPTY + slot], ((n / kItemSlots) - 1) & 1, p.status, ITEM_EMPTY, abort_flag))) break;
+                    int w = n == 0 ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+                    if (w >= n_items) w = -1;
+                    item_ring[slot] = w;
+                    mbar_arrive(&bars[ITEM_FULL + slot]);
+                    if (w < 0) break;
+                    const WorkItem wi = work_item(w, n_qt, BH);
+                    const int row_base = wi.bh * N, nk = 2 * wi.t + 2;
+                    for (int i = 0; i < 2; ++i) {
+                        if (n > 0 && !(ok = mbar_wait(&bars[Q_EMPTY + i], (n - 1) & 1, p.status, Q_EMPTY, abort_flag))) break;
+                        const int r = row_base + wi.t * 2 * kBM + i * kBM;
+                        mbar_arrive_expect_tx(&bars[Q_FULL + i], kTileBytes);
+                        tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
+                        tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
+                    }
+                    for (int j = 0; ok && j < nk; ++j, ++gk) {
+                        const int r = row_base + j * kBN;
+                        const int ks = gk % kKStages;
+                        if (gk >= kKStages && !(ok = mbar_wait(&bars[K_EMPTY + ks], ((gk / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag))) break;
+                        mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
+                        tma_load_2d(sK + ks * kTileBytes, &mapK, 0, r, &bars[K_FULL + ks]);
+                        tma_load_2d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, &bars[K_FULL + ks]);
+                    }
                 }
             }
             __syncwarp();
         } else if (warp == 1) {
             // -------------------------------------------------------------- TMA producer: the V ring
             if (lane == 0) {
-                for (int j = 0; j < nk; ++j) {
-                    const int r = row_base + j * kBN;
-                    const int vs = j % kVStages;
-                    if (j >= kVStages && !mbar_wait(&bars[V_EMPTY + vs], ((j / kVStages) - 1) & 1, p.status, V_EMPTY, abort_flag)) break;
-                    mbar_arrive_expect_tx(&bars[V_FULL + vs], kTileBytes);
-                    tma_load_2d(sV + vs * kTileBytes, &mapV, 0, r, &bars[V_FULL + vs]);
-                    tma_load_2d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, &bars[V_FULL + vs]);
+                int gv = 0;
+                bool ok = true;
+                for (int n = 0; ok; ++n) {
+                    const int w = fetch_item(bars, item_ring, n, lane, false, p.status, abort_flag);
+                    if (w < 0) break;
+                    const WorkItem wi = work_item(w, n_qt, BH);
+                    const int row_base = wi.bh * N, nk = 2 * wi.t + 2;
+                    for (int j = 0; j < nk; ++j, ++gv) {
+                        const int r = row_base + j * kBN;
+                        const int vs = gv % kVStages;
+                        if (gv >= kVStages && !(ok = mbar_wait(&bars[V_EMPTY + vs], ((gv / kVStages) - 1) & 1, p.status, V_EMPTY, abort_flag))) break;
+                        mbar_arrive_expect_tx(&bars[V_FULL + vs], kTileBytes);
+                        tma_load_2d(sV + vs * kTileBytes, &mapV, 0, r, &bars[V_FULL + vs]);
+                        tma_load_2d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, &bars[V_FULL + vs]);
+                    }
                 }
             }
             __syncwarp();
         } else if (warp == kMmaWarp) {
             // -------------------------------------------------------------- MMA issuer
-            {
-                const bool leader = elect_one();
-                constexpr int kVFmt = (kConvertV || Elem<T>::kDtype == COROPE_DTYPE_F16) ? 0 : 1;
-                const uint32_t idesc_qk = make_idesc(0, 0, 0, 0, kBM, kBN);
-                const uint32_t idesc_pv = make_idesc(kVFmt, kVFmt, 0, 1, kBM, kD);
-                const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-                constexpr uint32_t kHi = sdesc_hi(1024);
-                const uint32_t q_lo = sdesc_lo(q_addr, 0), k_lo = sdesc_lo(k_addr, 0), v_lo = sdesc_lo(v_addr, kBoxBytes);
-                auto issue_qk = [&](int i, int ks) {
-                    const uint32_t a0 = q_lo + i * (kTileBytes >> 4), b0 = k_lo + ks * (kTileBytes >> 4), d = tmem + i * 128;
+            const bool leader = elect_one();
+            constexpr int kVFmt = (kConvertV || Elem<T>::kDtype == COROPE_DTYPE_F16) ? 0 : 1;
+            const uint32_t idesc_qk = make_idesc(0, 0, 0, 0, kBM, kBN);
+            const uint32_t idesc_pv = make_idesc(kVFmt, kVFmt, 0, 1, kBM, kD);
+            constexpr uint32_t kHi = sdesc_hi(1024);
+            const uint32_t q_lo = sdesc_lo(smem_u32(sQ), 0), k_lo = sdesc_lo(smem_u32(sK), 0), v_lo = sdesc_lo(smem_u32(sV), kBoxBytes);
+            auto issue_qk = [&](int i, int ks) {
+                const uint32_t a0 = q_lo + i * (kTileBytes >> 4), b0 = k_lo + ks * (kTileBytes >> 4), d = tmem + i * 128;
 #pragma unroll
-                    for (int kk = 0; kk < kD / 16; ++kk) {
-                        const uint32_t off = ((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4;
-                        if (leader) umma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, kk > 0);
-                    }
-                };
-                auto issue_pv = [&](int i, int vs, bool acc) {
-                    const uint32_t b0 = v_lo + vs * (kTileBytes >> 4), d = tmem + 256 + i * 128, a = tmem + i * 128;
+                for (int kk = 0; kk < kD / 16; ++kk) {
+                    const uint32_t off = ((kk >> 2) * kBoxBytes + (kk & 3) * 32) >> 4;
+                    if (leader) umma_ss2(d, a0 + off, kHi, b0 + off, kHi, idesc_qk, kk > 0);
+                }
+            };
+            auto issue_pv = [&](int i, int vs, bool acc) {
+                const uint32_t b0 = v_lo + vs * (kTileBytes >> 4), d = tmem + 256 + i * 128, a = tmem + i * 128;
 #pragma unroll
-                    for (int kk = 0; kk < kBN / 16; ++kk)
-                        if (leader) umma_ts2(d, a + kk * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
-                };
-                bool ok = mbar_wait_warp(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag) && mbar_wait_warp(&bars[K_ROT + 0], 0, p.status, K_ROT, abort_flag);
-                if (ok) {
-                    tc_fence_after();
-                    issue_qk(0, 0);
-                    if (leader) umma_commit(&bars[S_FULL + 0]);
-                    ok = mbar_wait_warp(&bars[Q_ROT + 1], 0, p.status, Q_ROT + 1, abort_flag);
-                }
-                if (ok) {
-                    tc_fence_after();
-                    issue_qk(1, 0);
-                    if (leader) umma_commit(&bars[S_FULL + 1]);
-                    if (leader) umma_commit(&bars[K_EMPTY + 0]);
-                }
-#ifdef COROPE_PROFILE
-                long long pw[5] = {0, 0, 0, 0, 0}, pt;
-                const long long pstart = clock64();
-#define PROF_T0 pt = clock64()
-#define PROF_ACC(i) pw[i] += clock64() - pt
-#define PROF_STAMP(k) if (leader && p.prof && blockIdx.x == 0 && j >= 8 && j < 16) p.prof[1024 + (j - 8) * 8 + (k)] = clock64() - pstart
-#else
-#define PROF_T0
-#define PROF_ACC(i)
-#define PROF_STAMP(k)
-#endif
-                for (int j = 0; ok && j < nk; ++j) {
-                    const int vs = j % kVStages;
-                    const int ks1 = (j + 1) % kKStages;
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    if (leader) umma_ts2(d, a + kk * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
+            };
+            int gk = 0, gv = 0, s0 = 0, s1 = 0;   // K tiles, V tiles, S tiles of group 0 / 1 so far
+            bool ok = true;
+            for (int n = 0; ok; ++n) {
+                const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
+                if (w < 0) break;
+                const WorkItem wi = work_item(w, n_qt, BH);
+                const int nk = 2 * wi.t + 2, nk0 = nk - 1;
+                // first K tile of the item: S0 = Q0 K^T, S1 = Q1 K^T
+                if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&bars[K_ROT + gk % kKStages], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
+                tc_fence_after();
+                issue_qk(0, gk % kKStages);
+                if (leader) umma_commit(&bars[S_FULL + 0]);
+                if (!(ok = mbar_wait_warp(&bars[Q_ROT + 1], n & 1, p.status, Q_ROT + 1, abort_flag))) break;
+                tc_fence_after();
+                issue_qk(1, gk % kKStages);
+                if (leader) umma_commit(&bars[S_FULL + 1]);
+                if (leader) umma_commit(&bars[K_EMPTY + gk % kKStages]);
+                if (nk0 == 1 && leader) umma_commit(&bars[Q_EMPTY + 0]);      // Q0 sees a single K tile: that was its last use
+                ++gk;
+                for (int j = 0; j < nk; ++j, ++gv) {
+                    const int vs = gv % kVStages;
+                    const int ks1 = gk % kKStages;
                     const bool have_next = j + 1 < nk;
-                    PROF_STAMP(0);
-                    PROF_T0;
-                    if (!mbar_wait_warp(&bars[V_READY + vs], (j / kVStages) & 1, p.status, V_READY, abort_flag)) break;
-                    PROF_ACC(0);
+                    if (!(ok = mbar_wait_warp(&bars[V_READY + vs], (gv / kVStages) & 1, p.status, V_READY, abort_flag))) break;
                     if (j < nk0) {
-                        PROF_T0;
-                        if (!mbar_wait_warp(&bars[P_FULL + 0], j & 1, p.status, P_FULL, abort_flag)) break;
-                        PROF_ACC(1);
-                        PROF_STAMP(1);
+                        if (!(ok = mbar_wait_warp(&bars[P_FULL + 0], s0 & 1, p.status, P_FULL, abort_flag))) break;
+                        if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 0], (n - 1) & 1, p.status, O_FREE, abort_flag))) break;
                         tc_fence_after();
                         issue_pv(0, vs, j > 0);
                         if (leader) umma_commit(&bars[O_FULL + 0]);
-                        PROF_STAMP(2);
+                        ++s0;
                     }
                     if (have_next) {
-                        PROF_T0;
-                        if (!mbar_wait_warp(&bars[K_ROT + ks1], ((j + 1) / kKStages) & 1, p.status, K_ROT, abort_flag)) break;
-                        PROF_ACC(2);
-                        PROF_STAMP(3);
+                        if (!(ok = mbar_wait_warp(&bars[K_ROT + ks1], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
                         tc_fence_after();
                         if (j + 1 < nk0) {
                             issue_qk(0, ks1);
                             if (leader) umma_commit(&bars[S_FULL + 0]);
+                            if (j + 2 == nk0 && leader) umma_commit(&bars[Q_EMPTY + 0]);   // last use of Q0 in this item
                         }
-                        PROF_STAMP(4);
                     }
-                    PROF_T0;
-                    if (!mbar_wait_warp(&bars[P_FULL + 1], j & 1, p.status, P_FULL + 1, abort_flag)) break;
-                    PROF_ACC(3);
-                    PROF_STAMP(5);
+                    if (!(ok = mbar_wait_warp(&bars[P_FULL + 1], s1 & 1, p.status, P_FULL + 1, abort_flag))) break;
+                    if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 1], (n - 1) & 1, p.status, O_FREE + 1, abort_flag))) break;
                     tc_fence_after();
                     issue_pv(1, vs, j > 0);
                     if (leader) umma_commit(&bars[O_FULL + 1]);
                     if (leader) umma_commit(&bars[V_EMPTY + vs]);
-                    PROF_STAMP(6);
+                    ++s1;
                     if (have_next) {
                         issue_qk(1, ks1);
                         if (leader) umma_commit(&bars[S_FULL + 1]);
                         if (leader) umma_commit(&bars[K_EMPTY + ks1]);
+                        if (j + 2 == nk && leader) umma_commit(&bars[Q_EMPTY + 1]);       // last use of Q1 in this item
+                        ++gk;
                     }
-                    PROF_STAMP(7);
                 }
-#ifdef COROPE_PROFILE
-                if (leader && p.prof && blockIdx.x < 64) {
-                    long long* o = p.prof + blockIdx.x * 16;
-                    o[0] = clock64() - pstart; o[1] = pw[0]; o[2] = pw[1]; o[3] = pw[2]; o[4] = pw[3]; o[5] = nk;
-                }
-#endif
             }
             __syncwarp();
         }
@@ -293,57 +333,36 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int tid = threadIdx.x - kRotWarp0 * 32;
         bool ok = true;
         TabRegs<kBM> tr;
-        for (int i = 0; i < 2 && ok; ++i) {
-            load_table_regs<kBM>(tr, p.packed_tab + (size_t)(t * 2 * kBM + i * kBM) * (kD / 2), tid);
-            ok = mbar_wait_warp(&bars[Q_FULL + i], 0, p.status, Q_FULL, abort_flag);
-            if (!ok) break;
-            rotate_tile_regs<T, kBM>(sQ + i * kTileBytes, tr, tid, p.sm_scale * kLog2e);
-            fence_proxy_async();
-            mbar_arrive_warp(&bars[Q_ROT + i], lane);
-        }
-        load_table_regs<kBM>(tr, p.packed_tab, tid);
-#ifdef COROPE_PROFILE
-        long long rw = 0, rv = 0, rc = 0, rt0;
-#endif
-        for (int j = 0; ok && j < nk; ++j) {
-            const int ks = j % kKStages, vs = j % kVStages;
-#ifdef COROPE_PROFILE
-            rt0 = clock64();
-#endif
-            if (!mbar_wait_warp(&bars[K_FULL + ks], (j / kKStages) & 1, p.status, K_FULL, abort_flag)) break;
-#ifdef COROPE_PROFILE
-            rw += clock64() - rt0; rt0 = clock64();
-#endif
-#ifndef COROPE_KO_ROT
-            rotate_tile_regs<T, kBN>(sK + ks * kTileBytes, tr, tid, 1.0f);
-#endif
-            fence_proxy_async();
-            mbar_arrive_warp(&bars[K_ROT + ks], lane);
-            if (j + 1 < nk) load_table_regs<kBN>(tr, p.packed_tab + (size_t)((j + 1) * kBN) * (kD / 2), tid);  // in flight during the V pass
-#ifdef COROPE_PROFILE
-            rc += clock64() - rt0; rt0 = clock64();
-#endif
-            if (!mbar_wait_warp(&bars[V_FULL + vs], (j / kVStages) & 1, p.status, V_FULL, abort_flag)) break;
-#ifdef COROPE_PROFILE
-            rv += clock64() - rt0; rt0 = clock64();
-#endif
-            if (kConvertV) {
-#ifndef COROPE_KO_ROT
-                convert_tile_bf16_to_f16(sV + vs * kTileBytes, tid);
-#endif
+        int gk = 0, gv = 0;
+        for (int n = 0; ok; ++n) {
+            const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
+            if (w < 0) break;
+            const WorkItem wi = work_item(w, n_qt, BH);
+            const int nk = 2 * wi.t + 2;
+            for (int i = 0; i < 2 && ok; ++i) {
+                load_table_regs<kBM>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM) * (kD / 2), tid);
+                if (!(ok = mbar_wait_warp(&bars[Q_FULL + i], n & 1, p.status, Q_FULL, abort_flag))) break;
+                rotate_tile_regs<T, kBM>(sQ + i * kTileBytes, tr, tid, p.sm_scale * kLog2e);
                 fence_proxy_async();
+                mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
-            mbar_arrive_warp(&bars[V_READY + vs], lane);
-#ifdef COROPE_PROFILE
-            rc += clock64() - rt0;
-#endif
+            if (!ok) break;
+            load_table_regs<kBM>(tr, p.packed_tab, tid);
+            for (int j = 0; j < nk; ++j, ++gk, ++gv) {
+                const int ks = gk % kKStages, vs = gv % kVStages;
+                if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
+                rotate_tile_regs<T, kBN>(sK + ks * kTileBytes, tr, tid, 1.0f);
+                fence_proxy_async();
+                mbar_arrive_warp(&bars[K_ROT + ks], lane);
+                if (j + 1 < nk) load_table_regs<kBN>(tr, p.packed_tab + (size_t)((j + 1) * kBN) * (kD / 2), tid);  // in flight during the V pass
+                if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
+                if (kConvertV) {
+                    convert_tile_bf16_to_f16(sV + vs * kTileBytes, tid);
+                    fence_proxy_async();
+                }
+                mbar_arrive_warp(&bars[V_READY + vs], lane);
+            }
         }
-#ifdef COROPE_PROFILE
-        if (p.prof && blockIdx.x < 64 && tid == 0) {
-            long long* o = p.prof + blockIdx.x * 16 + 10;
-            o[0] = rw; o[1] = rv; o[2] = rc;
-        }
-#endif
     } else {
         // ------------------------------------------------------------------ softmax groups
         reg_alloc<kRegsSmx>();
@@ -353,113 +372,91 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
         const uint32_t tS = tmem + lane_base + wg * 128;
         const uint32_t tO = tmem + lane_base + 256 + wg * 128;
-        const int nk_i = nk0 + wg;
-        float m = -INFINITY, l = 0.f;
+        int gs = 0;   // S tiles of this group so far (across items): parity of S_FULL / O_FULL
         bool ok = true;
-#ifdef COROPE_PROFILE
-        long long sw = 0, sc = 0, st0;
-#endif
-        for (int j = 0; j < nk_i; ++j) {
-#ifdef COROPE_PROFILE
-            st0 = clock64();
-#endif
-            if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], j & 1, p.status, S_FULL + wg, abort_flag))) break;
-#ifdef COROPE_PROFILE
-            sw += clock64() - st0; st0 = clock64();
-#endif
-            tc_fence_after();
-            const bool diag = (j == nk_i - 1);
-#ifdef COROPE_KO_SMX
-            if (j > 0) { tc_fence_before(); mbar_arrive_warp(&bars[P_FULL + wg], lane); continue; }
-#endif
-            // whole S row into registers with one wait
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            COROPE_TMEM_LD32(tS, s0);
-            COROPE_TMEM_LD32(tS + 32, s1);
-            COROPE_TMEM_LD32(tS + 64, s2);
-            COROPE_TMEM_LD32(tS + 96, s3);
-            tmem_wait_ld();
-            if (diag) {   // causal mask on the diagonal tile: key column > query row
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (i > row) s0[i] = 0xff800000u;
-                    if (32 + i > row) s1[i] = 0xff800000u;
-                    if (64 + i > row) s2[i] = 0xff800000u;
-                    if (96 + i > row) s3[i] = 0xff800000u;
-                }
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-                mx1 = fmax3(mx1, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-                mx2 = fmax3(mx2, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
-                mx3 = fmax3(mx3, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
-            }
-            const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
-            const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
-            const float m_old = m;
-            m = need ? m_new : m;
-            float l0 = 0.f, l1 = 0.f;
-#define COROPE_EXP_CHUNK(sx, cidx)                                                       \
-            {                                                                            \
-                uint32_t pk[16];                                                         \
-                _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
-                    const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
-                    const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
-                    if (kPBf16) {                                                        \
-                        pk[i] = pack_bf162(p0, p1);                                      \
-                        const float2 pr = unpack_bf162(pk[i]);                           \
-                        l0 += pr.x;                                                      \
-                        l1 += pr.y;                                                      \
-                    } else {                                                             \
-                        l0 += p0;                                                        \
-                        l1 += p1;                                                        \
-                        pk[i] = pack_half2(p0, p1);                                      \
-                    }                                                                    \
-                }                                                                        \
-                COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
-            }
-            COROPE_EXP_CHUNK(s0, 0)
-            COROPE_EXP_CHUNK(s1, 1)
-            COROPE_EXP_CHUNK(s2, 2)
-            COROPE_EXP_CHUNK(s3, 3)
-#undef COROPE_EXP_CHUNK
-            // The rescale of O comes after P is written so that the S row is no longer live in registers.
-            if (j > 0 && __any_sync(0xffffffffu, need)) {
-                if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (j - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
+        for (int n = 0; ok; ++n) {
+            const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
+            if (w < 0) break;
+            const WorkItem wi = work_item(w, n_qt, BH);
+            const int nk_i = 2 * wi.t + 1 + wg;
+            float m = -INFINITY, l = 0.f;
+            for (int j = 0; j < nk_i; ++j, ++gs) {
+                if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], gs & 1, p.status, S_FULL + wg, abort_flag))) break;
                 tc_fence_after();
-                const float alpha = fast_exp2(m_old - m);
+                const bool diag = (j == nk_i - 1);
+                // whole S row into registers with one wait
+                uint32_t s0[32], s1[32], s2[32], s3[32];
+                COROPE_TMEM_LD32(tS, s0);
+                COROPE_TMEM_LD32(tS + 32, s1);
+                COROPE_TMEM_LD32(tS + 64, s2);
+                COROPE_TMEM_LD32(tS + 96, s3);
+                tmem_wait_ld();
+                if (diag) {   // causal mask on the diagonal tile: key column > query row
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    COROPE_TMEM_LD32(tO + c * 32, r);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                    COROPE_TMEM_ST32(tO + c * 32, r);
+                    for (int i = 0; i < 32; ++i) {
+                        if (i > row) s0[i] = 0xff800000u;
+                        if (32 + i > row) s1[i] = 0xff800000u;
+                        if (64 + i > row) s2[i] = 0xff800000u;
+                        if (96 + i > row) s3[i] = 0xff800000u;
+                    }
                 }
-                l *= alpha;
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+                    mx1 = fmax3(mx1, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+                    mx2 = fmax3(mx2, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+                    mx3 = fmax3(mx3, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
+                }
+                const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+                const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
+                const float m_old = m;
+                m = need ? m_new : m;
+                float l0 = 0.f, l1 = 0.f;
+#define COROPE_EXP_CHUNK(sx, cidx)                                                           \
+                {                                                                            \
+                    uint32_t pk[16];                                                         \
+                    _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
+                        const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
+                        const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
+                        l0 += p0;                                                            \
+                        l1 += p1;                                                            \
+                        pk[i] = pack_half2(p0, p1);                                          \
+                    }                                                                        \
+                    COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
+                }
+                COROPE_EXP_CHUNK(s0, 0)
+                COROPE_EXP_CHUNK(s1, 1)
+                COROPE_EXP_CHUNK(s2, 2)
+                COROPE_EXP_CHUNK(s3, 3)
+#undef COROPE_EXP_CHUNK
+                // The rescale of O comes after P is written so that the S row is no longer live in registers.
+                if (j > 0 && __any_sync(0xffffffffu, need)) {
+                    if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
+                    tc_fence_after();
+                    const float alpha = fast_exp2(m_old - m);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        COROPE_TMEM_LD32(tO + c * 32, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        COROPE_TMEM_ST32(tO + c * 32, r);
+                    }
+                    l *= alpha;
+                }
+                l += l0 + l1;
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive_warp(&bars[P_FULL + wg], lane);
             }
-            l += l0 + l1;
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive_warp(&bars[P_FULL + wg], lane);
-#ifdef COROPE_PROFILE
-            sc += clock64() - st0;
-#endif
-        }
-#ifdef COROPE_PROFILE
-        if (p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) {
-            long long* o = p.prof + blockIdx.x * 16 + 6 + wg * 2;
-            o[0] = sw; o[1] = sc;
-        }
-#endif
-        if (ok) ok = mbar_wait_warp(&bars[O_FULL + wg], (nk_i - 1) & 1, p.status, O_FULL + wg, abort_flag);
-        if (ok) {
+            if (!ok) break;
+            // output of this item: wait for its last P V, normalise, store; then hand O back to the MMA issuer
+            if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
             tc_fence_after();
             const float inv = 1.f / l;
-            const size_t grow = (size_t)row_base + (size_t)(2 * t + wg) * kBM + row;
+            const size_t grow = (size_t)wi.bh * N + (size_t)(2 * wi.t + wg) * kBM + row;
             T* orow = reinterpret_cast<T*>(p.out_o) + grow * kD;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -473,6 +470,8 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
             }
+            tc_fence_before();
+            mbar_arrive_warp(&bars[O_FREE + wg], lane);
             p.lse2[grow] = m + log2f(l);
         }
         tc_fence_before();
@@ -494,7 +493,11 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     auto kern = rope_fwd_sm100_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    const unsigned grid = (unsigned)((p.N / (2 * kBM)) * p.B * p.H);
+    const unsigned items = (unsigned)((p.N / (2 * kBM)) * p.B * p.H);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    const unsigned grid = items < (unsigned)sms ? items : (unsigned)sms;   // persistent: one CTA per SM
     kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, p); count_launch();
     return (int)cudaGetLastError();
 }

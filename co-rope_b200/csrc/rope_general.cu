@@ -369,6 +369,7 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
 __global__ void pack_tables_kernel(const float* __restrict__ cosT, const float* __restrict__ sinT, int64_t ts, uint32_t* __restrict__ out,
                                    int N, int half_d) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx == 0) out[(size_t)N * half_d] = 0u;   // the word after the table: work counter of the persistent forward kernel
     if (idx >= (size_t)N * half_d) return;
     int n = (int)(idx / half_d), d = (int)(idx % half_d);
     out[idx] = pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]);
