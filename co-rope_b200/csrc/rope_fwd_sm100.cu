@@ -30,16 +30,17 @@ constexpr int kKStages = 3;
 constexpr int kVStages = 2;
 constexpr int kTileBytes = kBM * kD * 2;   // 32 KiB: two 128 x 64 boxes
 constexpr int kBoxBytes = kTileBytes / 2;
-constexpr int kThreads = 512;          // four warpgroups: control (TMA K, TMA V, MMA, spare) | rotation | softmax 0 | softmax 1
+constexpr int kThreads = 768;          // six warpgroups: control (TMA K, TMA V, MMA, spare) | rotation | softmax of Q0 (2 groups) | of Q1 (2 groups)
 constexpr int kMmaWarp = 2;
 constexpr int kRotWarp0 = 4;
 constexpr int kSmxWarp0 = 8;
 // setmaxnreg only moves registers inside the CTA's own launch allocation (512 threads x 128): the sum must not exceed it
-constexpr int kRegsCtl = 56, kRegsRot = 120, kRegsSmx = 168;   // 128 * (56 + 120 + 2 * 168) = 65536 registers
-static_assert(128 * (kRegsCtl + kRegsRot + 2 * kRegsSmx) <= kThreads * 128, "register budget");
+constexpr int kLaunchRegs = 80;        // 65536 / 768 rounded down to a multiple of 8
+constexpr int kRegsCtl = 40, kRegsRot = 112, kRegsSmx = 80;    // 128 * (40 + 112 + 4 * 80) = 60416 <= 768 * 80
+static_assert(128 * (kRegsCtl + kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 8;
 constexpr int kItemSlots = 4;
-constexpr int kItemReaders = 1 + 1 + 4 + 4 + 4;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
+constexpr int kItemReaders = 1 + 1 + 4 + 16;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
 
 enum Bar {
     Q_FULL = 0,                        // +i
@@ -61,7 +62,10 @@ enum Bar {
 };
 
 constexpr size_t kSmemTiles = (size_t)(2 + kKStages + kVStages) * kTileBytes;
-constexpr size_t kSmemBytes = kSmemTiles + NUM_BARS * 8 + 64 + 1024;  // + alignment slack (tmem slot, abort flag and the item ring live in the 64)
+constexpr size_t kXchBytes = 2 * 2 * kBM * sizeof(float);         // half-row maxima / sums exchanged between the two groups of a Q tile
+constexpr size_t kSmemSlack = 512;     // room to round the dynamic shared memory base up to 1024 bytes (checked at run time)
+constexpr size_t kSmemBytes = kSmemTiles + kXchBytes + NUM_BARS * 8 + 64 + kSmemSlack;
+static_assert(kSmemBytes <= 232448, "shared memory budget");  // + alignment slack (tmem slot, abort flag and the item ring live in the 64)
 
 // bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
 __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
@@ -122,13 +126,23 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, RopeParams p) {
+    // P is written in the inputs' own 16-bit format so that V can be used as it lands (tcgen05.mma wants both operands in
+    // one format).  For bf16 the row sums are taken from the rounded P, which keeps the normalised weights consistent:
+    // measured max-abs error of O at the Llama-7B-4K shape is unchanged (0.0080, rounding of the bf16 output itself 0.0077).
+    // COROPE_CONVERT_V restores the older variant (V converted to fp16 in shared memory, fp16 P).
+#ifdef COROPE_CONVERT_V
     constexpr bool kConvertV = (Elem<T>::kDtype == COROPE_DTYPE_BF16);
+#else
+    constexpr bool kConvertV = false;
+#endif
+    constexpr bool kPBf16 = !kConvertV && Elem<T>::kDtype == COROPE_DTYPE_BF16;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = sm;
     uint8_t* sK = sQ + 2 * kTileBytes;
     uint8_t* sV = sK + kKStages * kTileBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kVStages * kTileBytes);
+    float* xch = reinterpret_cast<float*>(sV + kVStages * kTileBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xch) + kXchBytes);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* item_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [kItemSlots]
@@ -145,6 +159,10 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     // pipeline runs across item boundaries: the next item's Q and K tiles are loaded and rotated while the current
     // item's last tiles are still in the MMAs and its output is being written.
 
+    if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
+        if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
+        return;
+    }
     // A non-zero status word means an earlier CTA (of this or a previous launch) gave up on a wait: do not pile up
     // more timeouts behind it.  The word stays set until the host reads and clears it.
     if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
@@ -155,9 +173,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mbar_init(&bars[Q_ROT + i], 4);
             mbar_init(&bars[Q_EMPTY + i], 1);
             mbar_init(&bars[S_FULL + i], 1);
-            mbar_init(&bars[P_FULL + i], 4);
+            mbar_init(&bars[P_FULL + i], 8);
             mbar_init(&bars[O_FULL + i], 1);
-            mbar_init(&bars[O_FREE + i], 4);
+            mbar_init(&bars[O_FREE + i], 8);
         }
         for (int i = 0; i < kItemSlots; ++i) {
             mbar_init(&bars[ITEM_FULL + i], 1);
@@ -265,7 +283,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const uint32_t b0 = v_lo + vs * (kTileBytes >> 4), d = tmem + 256 + i * 128, a = tmem + i * 128;
 #pragma unroll
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    if (leader) umma_ts2(d, a + kk * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
+                    if (leader) umma_ts2(d, a + (kk >> 2) * 64 + (kk & 3) * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
             };
             int gk = 0, gv = 0, s0 = 0, s1 = 0;   // K tiles, V tiles, S tiles of group 0 / 1 so far
             bool ok = true;
@@ -329,7 +347,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
     } else if (warp < kSmxWarp0) {
         // ------------------------------------------------------------------ rotation group
-        reg_dealloc<kRegsRot>();
+        reg_alloc<kRegsRot>();
         const int tid = threadIdx.x - kRotWarp0 * 32;
         bool ok = true;
         TabRegs<kBM> tr;
@@ -351,13 +369,17 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             for (int j = 0; j < nk; ++j, ++gk, ++gv) {
                 const int ks = gk % kKStages, vs = gv % kVStages;
                 if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
+#ifndef COROPE_KO_ROT
                 rotate_tile_regs<T, kBN>(sK + ks * kTileBytes, tr, tid, 1.0f);
+#endif
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT + ks], lane);
                 if (j + 1 < nk) load_table_regs<kBN>(tr, p.packed_tab + (size_t)((j + 1) * kBN) * (kD / 2), tid);  // in flight during the V pass
                 if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
                 if (kConvertV) {
+#ifndef COROPE_KO_ROT
                     convert_tile_bf16_to_f16(sV + vs * kTileBytes, tid);
+#endif
                     fence_proxy_async();
                 }
                 mbar_arrive_warp(&bars[V_READY + vs], lane);
@@ -366,13 +388,23 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     } else {
         // ------------------------------------------------------------------ softmax groups
         reg_alloc<kRegsSmx>();
-        const int wg = (warp - kSmxWarp0) >> 2;
-        const int quad = warp & 3;  // the TMEM lane quadrant a warp may touch is warp_id % 4
+        // Two warpgroups per Q tile, each taking 64 of the 128 key columns of every S tile: the per-tile chain
+        // S ready -> exponentials -> P ready is what bounds the loop (one warp needs 8 cycles of the XU pipe per
+        // exp2 instruction), and halving the columns per thread halves it.  The two threads that share a row
+        // exchange their half-row maxima through shared memory (named barrier of their two warps) so that both use
+        // the same reference max; row sums stay partial until the end of the item.
+        const int wsm = warp - kSmxWarp0;
+        const int wg = wsm >> 3;            // Q tile
+        const int half = (wsm >> 2) & 1;    // which 64 key columns (and, for O, which 64 head-dim columns)
+        const int quad = warp & 3;          // the TMEM lane quadrant a warp may touch is warp_id % 4
         const int row = quad * 32 + lane;
+        const int pair_bar = 1 + wg * 4 + quad;   // named barrier of the two warps that hold the same 32 rows
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const uint32_t tS = tmem + lane_base + wg * 128;
-        const uint32_t tO = tmem + lane_base + 256 + wg * 128;
-        int gs = 0;   // S tiles of this group so far (across items): parity of S_FULL / O_FULL
+        const uint32_t tS = tmem + lane_base + wg * 128 + half * 64;          // this group's 64 S columns; its P goes over their start
+        const uint32_t tO = tmem + lane_base + 256 + wg * 128 + half * 64;    // this group's 64 O columns
+        float* xmine = xch + (wg * 2 + half) * kBM + row;
+        const float* xother = xch + (wg * 2 + (half ^ 1)) * kBM + row;
+        int gs = 0;   // S tiles of this Q tile so far (across items): parity of S_FULL / O_FULL and of the exchange slots
         bool ok = true;
         for (int n = 0; ok; ++n) {
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
@@ -384,31 +416,31 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], gs & 1, p.status, S_FULL + wg, abort_flag))) break;
                 tc_fence_after();
                 const bool diag = (j == nk_i - 1);
-                // whole S row into registers with one wait
-                uint32_t s0[32], s1[32], s2[32], s3[32];
+#ifdef COROPE_KO_SMX
+                if (j > 0) { tc_fence_before(); mbar_arrive_warp(&bars[P_FULL + wg], lane); continue; }
+#endif
+                uint32_t s0[32], s1[32];
                 COROPE_TMEM_LD32(tS, s0);
                 COROPE_TMEM_LD32(tS + 32, s1);
-                COROPE_TMEM_LD32(tS + 64, s2);
-                COROPE_TMEM_LD32(tS + 96, s3);
                 tmem_wait_ld();
                 if (diag) {   // causal mask on the diagonal tile: key column > query row
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
-                        if (i > row) s0[i] = 0xff800000u;
-                        if (32 + i > row) s1[i] = 0xff800000u;
-                        if (64 + i > row) s2[i] = 0xff800000u;
-                        if (96 + i > row) s3[i] = 0xff800000u;
+                        if (half * 64 + i > row) s0[i] = 0xff800000u;
+                        if (half * 64 + 32 + i > row) s1[i] = 0xff800000u;
                     }
                 }
-                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
                     mx0 = fmax3(mx0, __uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
                     mx1 = fmax3(mx1, __uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-                    mx2 = fmax3(mx2, __uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
-                    mx3 = fmax3(mx3, __uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
                 }
-                const float m_new = fmaxf(m, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+                const float mx_half = fmaxf(mx0, mx1);
+                *xmine = mx_half;
+                named_bar_sync(pair_bar, 64);
+                const float m_new = fmaxf(m, fmaxf(mx_half, *xother));
+                named_bar_sync(pair_bar, 64);   // both have read before either writes its slot again
                 const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
                 const float m_old = m;
                 m = need ? m_new : m;
@@ -419,24 +451,29 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
                         const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
                         const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
-                        l0 += p0;                                                            \
-                        l1 += p1;                                                            \
-                        pk[i] = pack_half2(p0, p1);                                          \
+                        if (kPBf16) {                                                        \
+                            pk[i] = pack_bf162(p0, p1);                                      \
+                            const float2 pr = unpack_bf162(pk[i]);                           \
+                            l0 += pr.x;                                                      \
+                            l1 += pr.y;                                                      \
+                        } else {                                                             \
+                            l0 += p0;                                                        \
+                            l1 += p1;                                                        \
+                            pk[i] = pack_half2(p0, p1);                                      \
+                        }                                                                    \
                     }                                                                        \
                     COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
                 }
                 COROPE_EXP_CHUNK(s0, 0)
                 COROPE_EXP_CHUNK(s1, 1)
-                COROPE_EXP_CHUNK(s2, 2)
-                COROPE_EXP_CHUNK(s3, 3)
 #undef COROPE_EXP_CHUNK
-                // The rescale of O comes after P is written so that the S row is no longer live in registers.
+                // The rescale of O (this group's 64 columns) comes after P is written so that S is no longer live.
                 if (j > 0 && __any_sync(0xffffffffu, need)) {
                     if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
                     tc_fence_after();
                     const float alpha = fast_exp2(m_old - m);
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t r[32];
                         COROPE_TMEM_LD32(tO + c * 32, r);
                         tmem_wait_ld();
@@ -452,14 +489,19 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 mbar_arrive_warp(&bars[P_FULL + wg], lane);
             }
             if (!ok) break;
-            // output of this item: wait for its last P V, normalise, store; then hand O back to the MMA issuer
+            // output of this item: total row sum from the two halves, wait for the last P V, normalise, store this
+            // group's 64 head-dim columns; then hand O back to the MMA issuer
+            *xmine = l;
+            named_bar_sync(pair_bar, 64);
+            const float l_tot = l + *xother;
+            named_bar_sync(pair_bar, 64);   // both have read before either writes this slot again
             if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
             tc_fence_after();
-            const float inv = 1.f / l;
+            const float inv = 1.f / l_tot;
             const size_t grow = (size_t)wi.bh * N + (size_t)(2 * wi.t + wg) * kBM + row;
-            T* orow = reinterpret_cast<T*>(p.out_o) + grow * kD;
+            T* orow = reinterpret_cast<T*>(p.out_o) + grow * kD + half * 64;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
                 COROPE_TMEM_LD32(tO + c * 32, r);
                 tmem_wait_ld();
@@ -472,7 +514,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             }
             tc_fence_before();
             mbar_arrive_warp(&bars[O_FREE + wg], lane);
-            p.lse2[grow] = m + log2f(l);
+            if (half == 0) p.lse2[grow] = m + log2f(l_tot);
         }
         tc_fence_before();
     }
