@@ -382,11 +382,11 @@ __device__ __forceinline__ void load_table_regs(TabRegs<ROWS>& tr, const uint32_
     }
 }
 
-template <typename T, int ROWS, int BOX_BYTES = ROWS * 128>
+template <typename T, int ROWS, int BOX_BYTES = ROWS * 128, int BATCH = 4>
 __device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<ROWS>& tr, int tid, float scale) {
     constexpr int kBoxBytes = BOX_BYTES;   // distance between the [0,64) and [64,128) column boxes (ROWS may be part of a taller tile)
     constexpr int kIters = ROWS / 16;
-    constexpr int kBatch = 4;                                        // rows in flight per thread: loads first, then math, then stores
+    constexpr int kBatch = BATCH;                                    // rows in flight per thread: loads first, then math, then stores
     const float k1 = scale * (1.f / 32768.f), k0 = -257.f * scale;   // decode constants with the scale folded in
     uint8_t* base = tile + (tid >> 3) * 128 + (tid & 7) * 16;
 #pragma unroll

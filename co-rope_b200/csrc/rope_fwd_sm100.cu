@@ -1,18 +1,20 @@
 // Fused-RoPE causal flash-attention forward for sm_100a: TMA -> shared memory -> in-place rotation ->
 // tcgen05 MMAs with TMEM accumulators -> online softmax in registers.  16-bit inputs, D = 128.
 //
-// One CTA owns 256 consecutive query rows (two 128-row tiles, "Q0" and "Q1") of one (batch, head)
-// and sweeps the K/V tiles 0 .. 2t+1 they can see.  Warp roles (512 threads = 4 warpgroups; registers are
-// re-divided between the groups with setmaxnreg):
-//   warp 0        TMA producer: Q tiles once, then the K ring (3 stages)
+// A work item is 256 consecutive query rows (two 128-row tiles, "Q0" and "Q1") of one (batch, head) with the K/V
+// tiles 0 .. 2t+1 they can see.  CTAs are persistent (one per SM) and take items from a global counter, heaviest
+// first.  Warp roles (896 threads = 7 warpgroups; registers are re-divided between the groups with setmaxnreg):
+//   warp 0        TMA producer: fetches work items, loads Q per item and the K ring (3 stages)
 //   warp 1        TMA producer: the V ring (2 stages)
-//   warp 2        MMA issuer (one elected lane) and TMEM owner;  warp 3 idle
-//   warps 4-7     rotation group: rotates Q0/Q1 once (scaled by sm_scale*log2e) and every K tile as it
-//                 lands, in place in shared memory, as fp16; converts bf16 V tiles to fp16 in place
-//   warps 8-11    softmax group of Q0: thread = row; the whole S row from TMEM into registers, running max /
-//                 sum, P (fp16) written back over S in TMEM, lazy rescale of O in TMEM, final normalise + store
-//   warps 12-15   softmax group of Q1
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i aliases the first 64 columns of S_i.
+//   warp 2        MMA issuer (warp-uniform loop, issue predicated on one elected lane) and TMEM owner;  warp 3 idle
+//   warps 4-11    two rotation groups: group r rotates rows [64r, 64r+64) of Q0/Q1 (scaled by sm_scale*log2e, once
+//                 per item) and of every K tile as it lands, in place in shared memory, as fp16
+//   warps 12-19   two softmax groups of Q0, each taking 64 of the 128 key columns: thread = row; half an S row from
+//                 TMEM into registers, half-row max exchanged with the partner group, exp2, row sum, P written back
+//                 over S in TMEM, lazy rescale of its 64 O columns in TMEM, final normalise + store
+//   warps 20-27   the same for Q1
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i (16-bit) is written over S_i: keys 0-63 in
+// columns 0-31, keys 64-127 in columns 64-95 (each softmax group writes only over columns it has already read).
 // MMA order per K tile j:  PV0(j) QK0(j+1) | PV1(j) QK1(j+1)  so that one group's softmax overlaps the
 // other group's MMAs.  The rotated Q / K never leave shared memory.
 //
@@ -30,17 +32,17 @@ constexpr int kKStages = 3;
 constexpr int kVStages = 2;
 constexpr int kTileBytes = kBM * kD * 2;   // 32 KiB: two 128 x 64 boxes
 constexpr int kBoxBytes = kTileBytes / 2;
-constexpr int kThreads = 768;          // six warpgroups: control (TMA K, TMA V, MMA, spare) | rotation | softmax of Q0 (2 groups) | of Q1 (2 groups)
+constexpr int kThreads = 896;          // seven warpgroups: control (TMA K, TMA V, MMA, spare) | rotation (2) | softmax of Q0 (2) | of Q1 (2)
 constexpr int kMmaWarp = 2;
 constexpr int kRotWarp0 = 4;
-constexpr int kSmxWarp0 = 8;
+constexpr int kSmxWarp0 = 12;
 // setmaxnreg only moves registers inside the CTA's own launch allocation (512 threads x 128): the sum must not exceed it
-constexpr int kLaunchRegs = 80;        // 65536 / 768 rounded down to a multiple of 8
-constexpr int kRegsCtl = 40, kRegsRot = 112, kRegsSmx = 80;    // 128 * (40 + 112 + 4 * 80) = 60416 <= 768 * 80
-static_assert(128 * (kRegsCtl + kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
+constexpr int kLaunchRegs = 72;        // 65536 / 896 rounded down to a multiple of 8; the rotation groups keep this count
+constexpr int kRegsCtl = 40, kRegsRot = 72, kRegsSmx = 80;     // 128 * (40 + 2 * 72 + 4 * 80) = 64512 = 896 * 72
+static_assert(128 * (kRegsCtl + 2 * kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 8;
 constexpr int kItemSlots = 4;
-constexpr int kItemReaders = 1 + 1 + 4 + 16;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
+constexpr int kItemReaders = 1 + 1 + 8 + 16;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
 
 enum Bar {
     Q_FULL = 0,                        // +i
@@ -69,7 +71,7 @@ static_assert(kSmemBytes <= 232448, "shared memory budget");  // + alignment sla
 
 // bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
 __device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
-    constexpr int kIters = kTileBytes / (16 * 128);   // 16 vectors of 16 bytes per thread, 8 in flight at a time
+    constexpr int kIters = kTileBytes / 2 / (16 * 128);   // half a tile per group of 128 threads: 8 vectors of 16 bytes per thread
 #pragma unroll
     for (int h = 0; h < kIters; h += 8) {
         uint4 x[8];
@@ -170,7 +172,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         *abort_flag = 0;
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars[Q_FULL + i], 1);
-            mbar_init(&bars[Q_ROT + i], 4);
+            mbar_init(&bars[Q_ROT + i], 8);
             mbar_init(&bars[Q_EMPTY + i], 1);
             mbar_init(&bars[S_FULL + i], 1);
             mbar_init(&bars[P_FULL + i], 8);
@@ -183,12 +185,12 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&bars[K_FULL + s], 1);
-            mbar_init(&bars[K_ROT + s], 4);
+            mbar_init(&bars[K_ROT + s], 8);
             mbar_init(&bars[K_EMPTY + s], 1);
         }
         for (int s = 0; s < kVStages; ++s) {
             mbar_init(&bars[V_FULL + s], 1);
-            mbar_init(&bars[V_READY + s], 4);
+            mbar_init(&bars[V_READY + s], 8);
             mbar_init(&bars[V_EMPTY + s], 1);
         }
         fence_mbar_init();
@@ -346,11 +348,14 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             __syncwarp();
         }
     } else if (warp < kSmxWarp0) {
-        // ------------------------------------------------------------------ rotation group
-        reg_alloc<kRegsRot>();
-        const int tid = threadIdx.x - kRotWarp0 * 32;
+        // ------------------------------------------------------------------ rotation groups
+        // Two groups of 128 threads; group r rotates rows [64 r, 64 r + 64) of every tile (Q0, Q1 once per item, every
+        // K tile).  They stay at the launch register count.
+        const int rg = (warp - kRotWarp0) >> 2;
+        const int tid = (threadIdx.x - kRotWarp0 * 32) & 127;
+        constexpr int kHalfRows = kBM / 2;
         bool ok = true;
-        TabRegs<kBM> tr;
+        TabRegs<kHalfRows> tr;
         int gk = 0, gv = 0;
         for (int n = 0; ok; ++n) {
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
@@ -358,27 +363,27 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const WorkItem wi = work_item(w, n_qt, BH);
             const int nk = 2 * wi.t + 2;
             for (int i = 0; i < 2 && ok; ++i) {
-                load_table_regs<kBM>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM) * (kD / 2), tid);
+                load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM + rg * kHalfRows) * (kD / 2), tid);
                 if (!(ok = mbar_wait_warp(&bars[Q_FULL + i], n & 1, p.status, Q_FULL, abort_flag))) break;
-                rotate_tile_regs<T, kBM>(sQ + i * kTileBytes, tr, tid, p.sm_scale * kLog2e);
+                rotate_tile_regs<T, kHalfRows, kBoxBytes, 2>(sQ + i * kTileBytes + rg * kHalfRows * 128, tr, tid, p.sm_scale * kLog2e);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
             if (!ok) break;
-            load_table_regs<kBM>(tr, p.packed_tab, tid);
+            load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
             for (int j = 0; j < nk; ++j, ++gk, ++gv) {
                 const int ks = gk % kKStages, vs = gv % kVStages;
                 if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
 #ifndef COROPE_KO_ROT
-                rotate_tile_regs<T, kBN>(sK + ks * kTileBytes, tr, tid, 1.0f);
+                rotate_tile_regs<T, kHalfRows, kBoxBytes, 2>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
 #endif
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT + ks], lane);
-                if (j + 1 < nk) load_table_regs<kBN>(tr, p.packed_tab + (size_t)((j + 1) * kBN) * (kD / 2), tid);  // in flight during the V pass
+                if (j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
                 if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
                 if (kConvertV) {
 #ifndef COROPE_KO_ROT
-                    convert_tile_bf16_to_f16(sV + vs * kTileBytes, tid);
+                    convert_tile_bf16_to_f16(sV + vs * kTileBytes + rg * (kTileBytes / 2), tid);
 #endif
                     fence_proxy_async();
                 }
