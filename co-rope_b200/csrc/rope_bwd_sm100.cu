@@ -14,10 +14,10 @@
 // dS^T is written once to shared memory (fp16, 128-byte swizzle) and is read both as the K-major A operand of
 // dK~ and as the MN-major B operand of dQ~^T; K~, Q~ and dO likewise serve two MMAs each from one buffer.
 //
-// Warp roles (640 threads = 5 warpgroups, registers re-divided with setmaxnreg): warp 0 TMA producer; warp 1 MMA
-// issuer + TMEM owner (warps 2-3 spare); warps 4-7 rotation group (K block once, every Q tile); warps 8-11 / 12-15
-// two softmax groups taking alternate steps; warps 16-19 drain dQ~^T from TMEM and add it to the fp32 accumulator
-// with reductions.  After the sweep the softmax groups write
+// Warp roles (768 threads = 6 warpgroups, registers re-divided with setmaxnreg): warp 0 TMA producer; warp 1 MMA
+// issuer + TMEM owner (warps 2-3 spare); warps 4-11 two rotation groups (half of the K block once, half of every Q
+// tile); warps 12-15 / 16-19 two softmax groups, each taking 32 of the 64 query columns of every step; warps 20-23
+// drain dQ~^T from TMEM and add it to the fp32 accumulator with reductions.  After the sweep the softmax groups write
 // dV and dK (inverse rotation and the ln2 factor applied in registers).
 // TMEM columns: S^T/P^T buffers [0,64) [64,128) (P^T of queries 0-31 in columns 0-15, of queries 32-63 in columns 32-47); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
 // A separate small kernel turns the fp32 dQ~ accumulator into dQ (inverse rotation, * sm_scale).
@@ -43,13 +43,14 @@ constexpr int kKVBox = kKVBytes / 2;
 constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
 constexpr int kQBox = kQBytes / 2;
 constexpr int kDsBytes = kBK * kBQ * 2;  // 16 KiB
-constexpr int kThreads = 640;             // five warpgroups: control (TMA, MMA, 2 spare) | rotation | softmax A | softmax B | dQ drain
+constexpr int kThreads = 768;             // six warpgroups: control (TMA, MMA, 2 spare) | rotation (2) | softmax A | softmax B | dQ drain
 constexpr int kMmaWarp = 1;
-constexpr int kRotWarp0 = 4, kSmxWarp0 = 8, kDrainWarp0 = 16;
-// setmaxnreg only moves registers inside the CTA's own launch allocation (640 threads x 96): what the softmax groups
-// gain must be released by the others first, or their setmaxnreg.inc waits forever.  128 * (48 + 96 + 2 * 128 + 80) = 640 * 96.
-constexpr int kRegsCtl = 48, kRegsRot = 96, kRegsSmx = 128, kRegsDrain = 80;
-static_assert(128 * (kRegsCtl + kRegsRot + 2 * kRegsSmx + kRegsDrain) <= kThreads * 96, "register budget");
+constexpr int kRotWarp0 = 4, kSmxWarp0 = 12, kDrainWarp0 = 20;
+// setmaxnreg only moves registers inside the CTA's own launch allocation (768 threads x 80): what the softmax groups
+// gain must be released by the others first, or their setmaxnreg.inc waits forever.  128 * (48 + 2 * 72 + 2 * 104 + 80) = 768 * 80.
+constexpr int kLaunchRegs = 80;
+constexpr int kRegsCtl = 48, kRegsRot = 72, kRegsSmx = 104, kRegsDrain = 80;
+static_assert(128 * (kRegsCtl + 2 * kRegsRot + 2 * kRegsSmx + kRegsDrain) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 4;
 
 enum Bar {
@@ -116,10 +117,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         *abort_flag = 0;
         mbar_init(&bars[K_FULL], 1);
         mbar_init(&bars[V_FULL], 1);
-        mbar_init(&bars[K_ROT], 4);
+        mbar_init(&bars[K_ROT], 8);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(&bars[QDO_FULL + s], 1);
-            mbar_init(&bars[Q_ROT + s], 4);
+            mbar_init(&bars[Q_ROT + s], 8);
             mbar_init(&bars[QDO_EMPTY + s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -282,47 +283,36 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     } else if (warp < kRotWarp0) {
         reg_dealloc<kRegsCtl>();   // spare warps of the control group
     } else if (warp < kSmxWarp0) {
-        // ------------------------------------------------------------------ rotation group
-        const int tid = threadIdx.x - kRotWarp0 * 32;
+        // ------------------------------------------------------------------ rotation groups
+        // Two groups of 128 threads: group r rotates rows [64 r, 64 r + 64) of the K block once, then rows
+        // [32 r, 32 r + 32) of every Q tile.
+        reg_dealloc<kRegsRot>();
+        const int rg = (warp - kRotWarp0) >> 2;
+        const int tid = (threadIdx.x - kRotWarp0 * 32) & 127;
+        constexpr int kQHalf = kBQ / 2;
         bool ok;
-        TabRegs<kBQ> tr;
-        {   // the K block, once: two halves of 64 rows so that the same 32 table registers serve
-            load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(jb * kBK) * (kD / 2), tid);
+        {
+            TabRegs<kBQ> trk;
+            load_table_regs<kBQ>(trk, p.packed_tab + (size_t)(jb * kBK + rg * kBQ) * (kD / 2), tid);
             ok = mbar_wait_warp(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
             if (ok) {
-                rotate_tile_regs<T, kBQ, kKVBox>(sK, tr, tid, 1.0f);
-                load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(jb * kBK + kBQ) * (kD / 2), tid);
-                rotate_tile_regs<T, kBQ, kKVBox>(sK + kBQ * 128, tr, tid, 1.0f);
+                rotate_tile_regs<T, kBQ, kKVBox, 2>(sK + rg * kBQ * 128, trk, tid, 1.0f);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT], lane);
             }
         }
-        load_table_regs<kBQ>(tr, p.packed_tab + (size_t)q_first * (kD / 2), tid);
-#ifdef COROPE_PROFILE
-        long long rw = 0, rc = 0, rt0;
-#endif
+        TabRegs<kQHalf> tr;
+        load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
         for (int s = 0; ok && s < n_steps; ++s) {
             const int st = s % kStages;
-#ifdef COROPE_PROFILE
-            rt0 = clock64();
-#endif
             if (!mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
-#ifdef COROPE_PROFILE
-            rw += clock64() - rt0; rt0 = clock64();
-#endif
 #ifndef COROPE_KO_ROT
-            rotate_tile_regs<T, kBQ>(sQ + st * kQBytes, tr, tid, p.sm_scale * kLog2e);
+            rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
 #endif
             fence_proxy_async();
             mbar_arrive_warp(&bars[Q_ROT + st], lane);
-            if (s + 1 < n_steps) load_table_regs<kBQ>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ) * (kD / 2), tid);
-#ifdef COROPE_PROFILE
-            rc += clock64() - rt0;
-#endif
+            if (s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
         }
-#ifdef COROPE_PROFILE
-        if (p.prof && blockIdx.x < 64 && tid == 0) { p.prof[blockIdx.x * 16 + 7] = rw; p.prof[blockIdx.x * 16 + 8] = rc; }
-#endif
     } else if (warp < kDrainWarp0) {
         // ------------------------------------------------------------------ softmax groups (each takes half the query columns of every step)
         reg_alloc<kRegsSmx>();
@@ -453,7 +443,6 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tc_fence_before();
     } else {
         // ------------------------------------------------------------------ dQ~^T drain: TMEM -> global fp32 reductions
-        reg_dealloc<kRegsDrain>();
         const int quad = warp & 3;
         const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
