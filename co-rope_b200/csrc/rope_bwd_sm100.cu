@@ -34,15 +34,15 @@ constexpr int kBQ = 64;                  // query rows per step
 #ifdef COROPE_STAGES
 constexpr int kStages = COROPE_STAGES;
 #else
-constexpr int kStages = 4;               // Q / dO ring.  The sweep is latency-bound on this ring (stage free -> TMA -> rotation ->
-                                         // MMAs -> stage free): measured 1.56 / 1.08 ms with 2 / 3 stages, so it is as deep as
-                                         // shared memory allows
+constexpr int kStages = 3;               // Q / dO ring.  With 2 stages the sweep is latency-bound on this ring (1.56 ms against 1.08 ms
+                                         // with 3); a 4th stage gave nothing, so its 32 KiB stage the dQ~ tile for the bulk reduce instead
 #endif
 constexpr int kKVBytes = kBK * kD * 2;   // 32 KiB
 constexpr int kKVBox = kKVBytes / 2;
 constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
 constexpr int kQBox = kQBytes / 2;
 constexpr int kDsBytes = kBK * kBQ * 2;  // 16 KiB
+constexpr int kDqBytes = kBQ * kD * 4;   // 32 KiB: dQ~ tile [64 queries][128] fp32, dense, staged for the bulk reduce-add
 constexpr int kThreads = 768;             // six warpgroups: control (TMA, MMA, 2 spare) | rotation (2) | softmax A | softmax B | dQ drain
 constexpr int kMmaWarp = 1;
 constexpr int kRotWarp0 = 4, kSmxWarp0 = 12, kDrainWarp0 = 20;
@@ -67,7 +67,7 @@ enum Bar {
     NUM_BARS = DQ_DONE + 2
 };
 
-constexpr size_t kSmemData = 2 * kKVBytes + kStages * 2 * kQBytes + 2 * kDsBytes + kStages * 2 * kBQ * sizeof(float);
+constexpr size_t kSmemData = 2 * kKVBytes + kStages * 2 * kQBytes + 2 * kDsBytes + kDqBytes + kStages * 2 * kBQ * sizeof(float);
 constexpr size_t kSmemSlack = 512;       // room to round the dynamic shared memory base up to 1024 bytes (checked at run time)
 constexpr size_t kSmemBytes = kSmemData + NUM_BARS * 8 + 64 + kSmemSlack;
 static_assert(kSmemBytes <= 232448, "shared memory budget");
@@ -77,7 +77,8 @@ constexpr uint32_t TS0 = 0, TD0 = 128, TDV = 256, TDK = 384;
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO, RopeParams p) {
+                      const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                      const __grid_constant__ CUtensorMap mapDQ, RopeParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sK = sm;
@@ -85,7 +86,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint8_t* sQ = sV + kKVBytes;                       // [stage] Q tile
     uint8_t* sDO = sQ + kStages * kQBytes;             // [stage] dO tile
     uint8_t* sDS = sDO + kStages * kQBytes;            // [2] dS^T
-    float* sLD = reinterpret_cast<float*>(sDS + 2 * kDsBytes);  // [stage][lse 64 | delta 64]
+    float* sDQ = reinterpret_cast<float*>(sDS + 2 * kDsBytes);  // dQ~ staging tile
+    float* sLD = sDQ + kDqBytes / 4;                            // [stage][lse 64 | delta 64]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sLD + kStages * 2 * kBQ);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -136,6 +138,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         tma_prefetch_desc(&mapK);
         tma_prefetch_desc(&mapV);
         tma_prefetch_desc(&mapDO);
+        tma_prefetch_desc(&mapDQ);
     }
     __syncthreads();
     if (warp == 1) {
@@ -467,16 +470,25 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive_warp(&bars[DQ_EMPTY + b], lane);
-            float* dst = p.dq_acc + ((size_t)row_base + q_first + s * kBQ) * kD + dcol;
 #ifndef COROPE_KO_DRAIN
+            // stage the tile as [query][head dim] (lanes = consecutive head-dim indices: conflict-free), then one thread
+            // adds it to the fp32 accumulator with a single bulk reduce instead of 8192 scalar reductions
+            if (threadIdx.x == kDrainWarp0 * 32) bulk_wait_group_read0();   // the previous reduce has finished reading the tile
+            named_bar_sync(1, 128);
+            float* tile = sDQ + dcol;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)i * kD, __uint_as_float(r0[i]));
+            for (int i = 0; i < 32; ++i) tile[i * kD] = __uint_as_float(r0[i]);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) atomicAdd(dst + (size_t)(32 + i) * kD, __uint_as_float(r1[i]));
-#else
-            if (__uint_as_float(r0[0]) == 123.456f && __uint_as_float(r1[3]) == 1.f) dst[0] = 0.f;
+            for (int i = 0; i < 32; ++i) tile[(32 + i) * kD] = __uint_as_float(r1[i]);
+            fence_proxy_async();
+            named_bar_sync(1, 128);
+            if (threadIdx.x == kDrainWarp0 * 32) {
+                tma_reduce_add_2d(&mapDQ, 0, row_base + q_first + s * kBQ, sDQ);
+                bulk_commit_group();
+            }
 #endif
         }
+        if (threadIdx.x == kDrainWarp0 * 32) bulk_wait_group0();   // all reduces have landed before the CTA exits
     }
     __syncthreads();
     if (warp == 1) {
@@ -519,19 +531,20 @@ __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __
 
 template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
-    CUtensorMap mq, mk, mv, mdo;
+    CUtensorMap mq, mk, mv, mdo, mdq;
     const uint64_t rows = (uint64_t)p.B * p.H * p.N;
     if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mdo, p.d_o, rows, kD, kBQ, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_f32(&mdq, p.dq_acc, rows, kD, kBQ, kD)) return e;
     cudaError_t e = cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
     auto kern = rope_bwd_sm100_kernel<T>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     const unsigned grid = (unsigned)((p.N / kBK) * p.B * p.H);
-    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, p); count_launch();
+    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, mdq, p); count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     const size_t n = rows * 16;
