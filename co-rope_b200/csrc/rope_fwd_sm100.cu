@@ -37,8 +37,10 @@ constexpr int kMmaWarp = 2;
 constexpr int kRotWarp0 = 4;
 constexpr int kSmxWarp0 = 12;
 // setmaxnreg only moves registers inside the CTA's own launch allocation (512 threads x 128): the sum must not exceed it
-constexpr int kLaunchRegs = 72;        // 65536 / 896 rounded down to a multiple of 8; the rotation groups keep this count
-constexpr int kRegsCtl = 40, kRegsRot = 72, kRegsSmx = 80;     // 128 * (40 + 2 * 72 + 4 * 80) = 64512 = 896 * 72
+constexpr int kLaunchRegs = 72;        // 65536 / 896 rounded down to a multiple of 8
+// 128 * (40 + 2 * 72 + 4 * 80) = 64512 = 896 * 72.  Measured against 40 / 56 / 88 (which leaves 8 instead of 64 bytes of
+// spill, all in the softmax groups): 0.437 ms against 0.456 ms at the Llama-7B-4K shape -- the rotation groups need the room.
+constexpr int kRegsCtl = 40, kRegsRot = 72, kRegsSmx = 80;
 static_assert(128 * (kRegsCtl + 2 * kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 8;
 constexpr int kItemSlots = 4;
@@ -365,7 +367,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             for (int i = 0; i < 2 && ok; ++i) {
                 load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM + rg * kHalfRows) * (kD / 2), tid);
                 if (!(ok = mbar_wait_warp(&bars[Q_FULL + i], n & 1, p.status, Q_FULL, abort_flag))) break;
-                rotate_tile_regs<T, kHalfRows, kBoxBytes, 2>(sQ + i * kTileBytes + rg * kHalfRows * 128, tr, tid, p.sm_scale * kLog2e);
+                rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sQ + i * kTileBytes + rg * kHalfRows * 128, tr, tid, p.sm_scale * kLog2e);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
@@ -375,7 +377,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const int ks = gk % kKStages, vs = gv % kVStages;
                 if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
 #ifndef COROPE_KO_ROT
-                rotate_tile_regs<T, kHalfRows, kBoxBytes, 2>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
+                rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
 #endif
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT + ks], lane);
