@@ -15,7 +15,7 @@ constexpr size_t kAlign = 256;
 bool head_dim_ok(int D) { return D == 32 || D == 64 || D == 128; }
 
 struct RopeWorkspace {
-    size_t packed_tab, delta, dq_acc, total;
+    size_t packed_tab, rot, delta, dq_acc, total;
 };
 
 RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dtype) {
@@ -23,6 +23,8 @@ RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dt
     size_t off = 0;
     w.packed_tab = off;
     off += align_up((size_t)N * (D / 2) * sizeof(uint32_t) + 64, kAlign);   // + the work counter behind the table
+    w.rot = off;   // tensor-core kernels: fp16 copy of the rotated K (forward) / rotated and scaled Q (backward)
+    if (dtype != COROPE_DTYPE_F32 && D == 128) off += align_up((size_t)B * H * N * D * 2, kAlign);
     if (bwd) {
         w.delta = off;
         off += align_up((size_t)B * H * N * sizeof(float), kAlign);
@@ -139,6 +141,9 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));
+        void* k_rot = (char*)workspace + w.rot;
+        if (int e = launch_rope_prerotate(k, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
+        p.k_rot = k_rot;
         g_last_family[COROPE_OP_ROPE_FWD] = 1;
         return launch_rope_fwd_tc(p, dtype, s);
     }

@@ -61,6 +61,8 @@ struct RopeParams {
     float sm_scale;
     int* status;
     int* sched_counter; // zeroed word in the workspace: next work item of the persistent forward kernel
+    const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
+    const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
     long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise
 };
 
@@ -319,6 +321,42 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
+// Packed pairs of fp32 in one 64-bit register: add / mul / fma on both lanes with one instruction (one issue slot for
+// two results; the pipe runs them at half the warp rate of the scalar forms, so the gain is in issue slots).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_sub(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 // volatile variant: keeps its program order relative to the TMEM loads / stores, which bounds how far the compiler
 // can hoist the exponentials of later chunks (and with them the register pressure of the softmax loop)
 __device__ __forceinline__ float fast_exp2_ordered(float x) {
@@ -392,6 +430,28 @@ __device__ __forceinline__ void load_table_regs(TabRegs<ROWS>& tr, const uint32_
     }
 }
 
+// Rotation of 8 (x1, x2) pairs held as two 16-byte vectors of T (x1: columns d..d+7, x2: columns d+64..d+71) by the 8
+// packed table entries t0, t1; k1 / k0 are the table's decode constants with the output scale folded in.  The result
+// is fp16 whatever T.  x1' = x1 c - x2 s,  x2' = x2 c + x1 s  (the reference's rotation, fused_rope_attn.py:96-99).
+template <typename T>
+__device__ __forceinline__ void rotate_vec8(uint4& x1, uint4& x2, const uint4& t0, const uint4& t1, float k1, float k0) {
+    uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w};
+    uint32_t b[4] = {x2.x, x2.y, x2.z, x2.w};
+    const uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
+        const float c0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7410)), k1, k0);
+        const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
+        const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
+        const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
+        a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
+        b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
+    }
+    x1 = make_uint4(a[0], a[1], a[2], a[3]);
+    x2 = make_uint4(b[0], b[1], b[2], b[3]);
+}
+
 template <typename T, int ROWS, int BOX_BYTES = ROWS * 128, int BATCH = 4>
 __device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<ROWS>& tr, int tid, float scale) {
     constexpr int kBoxBytes = BOX_BYTES;   // distance between the [0,64) and [64,128) column boxes (ROWS may be part of a taller tile)
@@ -409,22 +469,7 @@ __device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<RO
         }
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
-            const uint4 t0 = tr.t[2 * (h + u)], t1 = tr.t[2 * (h + u) + 1];
-            uint32_t a[4] = {x1[u].x, x1[u].y, x1[u].z, x1[u].w};
-            uint32_t b[4] = {x2[u].x, x2[u].y, x2[u].z, x2[u].w};
-            const uint32_t cs[8] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 fa = unpack2<T>(a[i]), fb = unpack2<T>(b[i]);
-                const float c0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7410)), k1, k0);
-                const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
-                const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
-                const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
-                a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
-                b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
-            }
-            x1[u] = make_uint4(a[0], a[1], a[2], a[3]);
-            x2[u] = make_uint4(b[0], b[1], b[2], b[3]);
+            rotate_vec8<T>(x1[u], x2[u], tr.t[2 * (h + u)], tr.t[2 * (h + u) + 1], k1, k0);
         }
 #pragma unroll
         for (int u = 0; u < kBatch; ++u) {
@@ -476,6 +521,8 @@ int launch_rope_fwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s);
+int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
+                          cudaStream_t s);
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);

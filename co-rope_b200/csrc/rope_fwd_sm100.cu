@@ -372,16 +372,19 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
             if (!ok) break;
-            load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
+            const bool k_pre = p.k_rot != nullptr;   // K tiles arrive rotated (pre-pass): only pass the barriers on
+            if (!k_pre) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
             for (int j = 0; j < nk; ++j, ++gk, ++gv) {
                 const int ks = gk % kKStages, vs = gv % kVStages;
                 if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
 #ifndef COROPE_KO_ROT
-                rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
+                if (!k_pre) {
+                    rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
+                    fence_proxy_async();
+                }
 #endif
-                fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT + ks], lane);
-                if (j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
+                if (!k_pre && j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
                 if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
                 if (kConvertV) {
 #ifndef COROPE_KO_ROT
@@ -451,29 +454,33 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const bool need = m_new > m + 8.f;   // lazy rescale: tolerate P up to 2^8 before moving the reference max
                 const float m_old = m;
                 m = need ? m_new : m;
-                float l0 = 0.f, l1 = 0.f;
+                // two elements per instruction for the subtraction of the reference max and for the row sum
+                const uint64_t neg_m = f2_pack(-m, -m);
+                uint64_t la = 0, lb = 0;   // two packed accumulators (bit pattern 0 = +0.0f twice)
 #define COROPE_EXP_CHUNK(sx, cidx)                                                           \
                 {                                                                            \
                     uint32_t pk[16];                                                         \
                     _Pragma("unroll") for (int i = 0; i < 16; ++i) {                         \
-                        const float p0 = fast_exp2(__uint_as_float(sx[2 * i]) - m);          \
-                        const float p1 = fast_exp2(__uint_as_float(sx[2 * i + 1]) - m);      \
-                        if (kPBf16) {                                                        \
+                        float d0, d1;                                                        \
+                        f2_unpack(f2_add(f2_pack_bits(sx[2 * i], sx[2 * i + 1]), neg_m), d0, d1); \
+                        const float p0 = fast_exp2(d0), p1 = fast_exp2(d1);                  \
+                        uint64_t pr;                                                         \
+                        if (kPBf16) {   /* row sums from the rounded P */                    \
                             pk[i] = pack_bf162(p0, p1);                                      \
-                            const float2 pr = unpack_bf162(pk[i]);                           \
-                            l0 += pr.x;                                                      \
-                            l1 += pr.y;                                                      \
+                            pr = f2_pack_bits(pk[i] << 16, pk[i] & 0xffff0000u);             \
                         } else {                                                             \
-                            l0 += p0;                                                        \
-                            l1 += p1;                                                        \
                             pk[i] = pack_half2(p0, p1);                                      \
+                            pr = f2_pack(p0, p1);                                            \
                         }                                                                    \
+                        if (i & 1) lb = f2_add(lb, pr); else la = f2_add(la, pr);            \
                     }                                                                        \
                     COROPE_TMEM_ST16(tS + (cidx) * 16, pk);                                  \
                 }
                 COROPE_EXP_CHUNK(s0, 0)
                 COROPE_EXP_CHUNK(s1, 1)
 #undef COROPE_EXP_CHUNK
+                float l0, l1;
+                f2_unpack(f2_add(la, lb), l0, l1);
                 // The rescale of O (this group's 64 columns) comes after P is written so that S is no longer live.
                 if (j > 0 && __any_sync(0xffffffffu, need)) {
                     if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
@@ -537,7 +544,9 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv;
     const uint64_t rows = (uint64_t)p.B * p.H * p.N;
     if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBM, 64, dtype)) return e;
-    if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBN, 64, dtype)) return e;
+    if (int e = p.k_rot ? encode_tensor_map_2d_sw128(&mk, p.k_rot, rows, kD, kBN, 64, COROPE_DTYPE_F16)
+                        : encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBN, 64, dtype))
+        return e;
     if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBN, 64, dtype)) return e;
     auto kern = rope_fwd_sm100_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);

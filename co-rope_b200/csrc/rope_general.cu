@@ -375,6 +375,29 @@ __global__ void pack_tables_kernel(const float* __restrict__ cosT, const float* 
     out[idx] = pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]);
 }
 
+// Rotation as a pass of its own, for the tensor-core kernels at D = 128: out[r, :] = rot(x[r, :]) * scale as fp16, with the
+// same packed table and the same arithmetic as the in-kernel rotation (rotate_vec8), so both give identical bits.  The
+// forward uses it for K (every K tile is consumed by up to N/256 work items; rotating it once here instead of once per
+// consumer removes the rotation from the forward's inner loop), the backward for Q (consumed by every key block below
+// its diagonal).  One thread = 8 pairs of one row: two 16-byte loads, 32 bytes of table, two 16-byte stores.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_prerotate_d128_kernel(const T* __restrict__ x, __half* __restrict__ out,
+                                                                   const uint32_t* __restrict__ tab, size_t rows, int N, float scale) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * 8) return;
+    const size_t row = idx >> 3;
+    const int c = (int)(idx & 7) * 8;
+    const int n = (int)(row % (size_t)N);
+    const uint4* src = reinterpret_cast<const uint4*>(x + row * 128 + c);
+    uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
+    const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
+    const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+    rotate_vec8<T>(x1, x2, t0, t1, scale * (1.f / 32768.f), -257.f * scale);
+    uint4* dst = reinterpret_cast<uint4*>(out + row * 128 + c);
+    dst[0] = x1;
+    dst[8] = x2;
+}
+
 template <typename T, int D>
 int launch_fwd_t(const RopeParams& p, cudaStream_t s) {
     size_t smem = sizeof(float) * (kRows * D + kTile * (D + 1) + kTile * D);
@@ -464,6 +487,18 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
             break;
         default: return COROPE_ERR_BAD_DTYPE;
     }
+    return (int)cudaGetLastError();
+}
+
+int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
+                          cudaStream_t s) {
+    const size_t rows = (size_t)B * H * N;
+    const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
+    if (dtype == COROPE_DTYPE_BF16)
+        rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale);
+    else
+        rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale);
+    count_launch();
     return (int)cudaGetLastError();
 }
 
