@@ -172,6 +172,9 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
+        void* q_rot = (char*)workspace + w.rot;
+        if (int e = launch_rope_prerotate(q, q_rot, tab, B, H, N, sm_scale * kLog2e, dtype, s)) return e;
+        p.q_rot = q_rot;
         g_last_family[COROPE_OP_ROPE_BWD] = 1;
         return launch_rope_bwd_tc(p, dtype, s);
     }

@@ -305,16 +305,19 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             }
         }
         TabRegs<kQHalf> tr;
-        load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
+        const bool q_pre = p.q_rot != nullptr;   // Q tiles arrive rotated and scaled (pre-pass): only pass the barrier on
+        if (!q_pre) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
         for (int s = 0; ok && s < n_steps; ++s) {
             const int st = s % kStages;
             if (!mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
 #ifndef COROPE_KO_ROT
-            rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
+            if (!q_pre) {
+                rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
+                fence_proxy_async();
+            }
 #endif
-            fence_proxy_async();
             mbar_arrive_warp(&bars[Q_ROT + st], lane);
-            if (s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
+            if (!q_pre && s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
         }
     } else if (warp < kDrainWarp0) {
         // ------------------------------------------------------------------ softmax groups (each takes half the query columns of every step)
@@ -533,7 +536,9 @@ template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv, mdo, mdq;
     const uint64_t rows = (uint64_t)p.B * p.H * p.N;
-    if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype)) return e;
+    if (int e = p.q_rot ? encode_tensor_map_2d_sw128(&mq, p.q_rot, rows, kD, kBQ, 64, COROPE_DTYPE_F16)
+                        : encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype))
+        return e;
     if (int e = encode_tensor_map_2d_sw128(&mdo, p.d_o, rows, kD, kBQ, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBK, 64, dtype)) return e;
