@@ -57,7 +57,9 @@ int corope_abi_version(void);
 const char* corope_status_string(int status);
 
 /* Bytes of caller-provided scratch (device memory, 256-byte aligned) an op needs.  Contents
- * need not be initialised by the caller.  For MHA pass Hkv == Hq. */
+ * need not be initialised by the caller.  For MHA pass Hkv == Hq.  For 16-bit inputs at D = 128 the
+ * fused-RoPE ops keep a rotated fp16 copy of K (forward) or Q (backward) there, so the size grows
+ * with B*H*N*D (forward: 2 bytes per element of k; backward: 6 bytes per element of q). */
 size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int dtype);
 
 /*
