@@ -197,6 +197,10 @@ int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* 
     GqaParams p{};
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2; p.a_diag = a_diag;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
+    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype)) {
+        g_last_family[COROPE_OP_GQA_FWD] = 1;
+        return launch_gqa_fwd_mma(p, dtype, (cudaStream_t)stream);
+    }
     g_last_family[COROPE_OP_GQA_FWD] = 0;
     return launch_gqa_fwd_general(p, dtype, (cudaStream_t)stream);
 }

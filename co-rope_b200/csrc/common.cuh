@@ -527,6 +527,8 @@ bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_bwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
+bool gqa_fwd_mma_supported(int N, int D, int dtype);
+int launch_gqa_fwd_mma(const GqaParams& p, int dtype, cudaStream_t s);
 int launch_gqa_fwd_general(const GqaParams& p, int dtype, cudaStream_t s);
 int launch_gqa_bwd_general(const GqaParams& p, int dtype, cudaStream_t s);
 

@@ -1,0 +1,312 @@
+// Co-RoPE GQA attention forward for 16-bit inputs at D = 128: the per-(i, j, d) rotation of the key stays on the
+// CUDA cores (it cannot be factored: the phase Delta_ij * w_d depends on query, key and frequency), every dot
+// product over d moves to the tensor cores (mma.sync m16n8k16, fp16 operands, fp32 accumulators).
+//
+// Definition (corope-exp/corope_attn_gqa_pytorch.py:56-124), one KV head and its G query heads, leader = first head:
+//     z_ik = sigmoid(s * qL_i . k_k)    Delta_ij = sum_{k=j+1..i} z_ik
+//     S_hij = s * sum_p ( q1_hip K'1_ijp + q2_hip K'2_ijp ),  K'1 = k1 cos + k2 sin,  K'2 = k2 cos - k1 sin,  angle = Delta_ij w_p
+// One CTA = 8 consecutive query rows of one (batch, KV head), one warp per row; keys in tiles of 64, swept downward
+// from the diagonal so that Delta is a running suffix sum (as in the general kernel).  Per tile:
+//   1. leader scores of the CTA's 8 rows against the 64 keys: warp w takes keys 8w..8w+7 (8 MMAs, rows of the A
+//      operand = the 8 query rows), sigmoid, causal mask -> z in shared memory;
+//   2. each warp turns its row of z into Delta (suffix sums inside the tile + carry from the tiles above);
+//   3. for every block of 8 keys: lane (key = lane/4, c = lane%4) rotates the 16 (k1, k2) pairs p = c mod 4 of its key
+//      by Delta_ij w_p -- these are exactly the B-operand registers of 8 MMAs whose A operand holds the G heads of
+//      the row (rows >= G are zero) -> S[h][key];
+//   4. online softmax per head (log2 domain), P as fp16 A operand, V through ldmatrix.trans, O in registers.
+// The K dimension of the score MMAs is ordered (pair, component): index 2p is the first half of pair p, 2p+1 the
+// second; Q and K use the same order, so dot products are unchanged.  Shared-memory rows of K / leader Q are stored
+// permuted so that a lane's 16 pairs are four 16-byte loads without bank conflicts (see perm_slot).
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace corope {
+namespace {
+
+constexpr int kRows = 8;            // query rows (= warps) per CTA
+constexpr int kThreads = kRows * 32;
+constexpr int kKT = 64;             // keys per tile
+constexpr int kD = 128;
+constexpr int kPairs = kD / 2;
+constexpr int kKRow = 80;           // u32 per K row: 64 pairs + 16 of padding (rows of a quarter-warp land in distinct bank groups)
+constexpr int kVRowBytes = 272;     // bytes per V row: 128 halves + 16 bytes of padding (conflict-free ldmatrix)
+
+// Position (u32 index within a row) of pair p.  MMA k-step t = p / 8 covers pairs 8t..8t+7; lane c = (p % 8) % 4 holds
+// pair 8t + c in b0 / a0 and pair 8t + c + 4 in b1 / a2.  The 16 pairs of lane c are stored as four 16-byte chunks
+// (chunk index 4s + c for s = t / 2), each holding (t = 2s: b0, b1; t = 2s + 1: b0, b1).
+__device__ __forceinline__ int perm_slot(int p) {
+    const int t = p >> 3, r = p & 7, c = r & 3, u = r >> 2, s = t >> 1, tt = t & 1;
+    return ((4 * s + c) << 2) + tt * 2 + u;
+}
+// the pair held in slot (s, e) of lane c: e = 0..3 as stored in the 16-byte chunk
+__device__ __forceinline__ int lane_pair(int c, int s, int e) { return 8 * (2 * s + (e >> 1)) + c + 4 * (e & 1); }
+
+__device__ __forceinline__ void mma16816(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1, float c0, float c1) {
+    float x2, x3;   // rows 8..15 of the A operand are zero: their results are discarded
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d0), "=f"(d1), "=f"(x2), "=f"(x3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(c0), "f"(c1), "f"(0.f), "f"(0.f));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(smem_u32(smem_row)));
+}
+
+__device__ __forceinline__ void sincos_fast(float x, float* s, float* c, bool direct) {
+    if (direct) {
+        // phases up to a few thousand radians (N <= 8192): the hardware approximations alone
+        __sincosf(x, s, c);
+    } else {
+        // two-constant reduction to [-pi, pi], then the hardware approximations
+        float kf = rintf(x * 0.15915494309189535f);
+        float r = fmaf(kf, -6.28318548202514648f, x);
+        r = fmaf(kf, 1.7484555e-7f, r);
+        __sincosf(r, s, c);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t to_half2(T a, T b) {
+    return pack_half2(Elem<T>::to_f32(a), Elem<T>::to_f32(b));
+}
+
+template <typename T, int G>
+__global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p) {
+    __shared__ __align__(16) uint32_t ks[kKT * kKRow];            // K tile, (k1, k2) fp16 pairs, permuted rows
+    __shared__ __align__(16) uint8_t vs[kKT * kVRowBytes];        // V tile, fp16 row-major
+    __shared__ __align__(16) uint32_t qls[kRows * kPairs];        // leader rows of the CTA's queries, permuted like K
+    __shared__ float zs[kRows * kKT];
+    __shared__ float dl[kRows * kKT];
+    __shared__ __align__(16) float ws[kPairs];   // inverse frequencies, permuted like K: the 16 of lane c are contiguous
+
+    const int N = p.N;
+    const int bg = blockIdx.y;
+    const int b = bg / p.Hkv, g = bg % p.Hkv;
+    const int i0 = (gridDim.x - 1 - blockIdx.x) * kRows;   // heavy (late) rows first
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = lane >> 2, c = lane & 3;
+    const int i = i0 + warp;
+    const size_t q_head0 = (size_t)b * p.Hq + (size_t)g * G;
+    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bg * N * kD;
+    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bg * N * kD;
+    const T* QL = reinterpret_cast<const T*>(p.q) + q_head0 * N * kD;
+
+    for (int idx = tid; idx < kRows * kPairs; idx += kThreads) {
+        const int r = idx >> 6, pp = idx & 63;
+        const T* row = QL + (size_t)(i0 + r) * kD;
+        qls[r * kPairs + perm_slot(pp)] = to_half2<T>(row[pp], row[pp + kPairs]);
+    }
+    for (int d = tid; d < kPairs; d += kThreads) {
+        const int cc = (d & 7) & 3, s = d >> 4, e = ((d >> 3) & 1) * 2 + ((d & 7) >> 2);
+        ws[cc * 16 + s * 4 + e] = 1.0f / powf(p.theta, (float)(2 * d) / (float)kD);
+    }
+    __syncthreads();
+
+    // per-lane constants: the 16 pairs of this lane (p = c mod 4), their frequencies, and the query operand of head h
+    uint32_t aq[16];
+    {
+        const T* qrow = reinterpret_cast<const T*>(p.q) + ((q_head0 + (h < G ? h : 0)) * N + i) * kD;
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int pp = lane_pair(c, s, e);
+                aq[s * 4 + e] = (h < G) ? to_half2<T>(qrow[pp], qrow[pp + kPairs]) : 0u;
+            }
+    }
+
+    float m = -INFINITY, l = 0.f;   // of head h (the 4 lanes of a head agree on m; l is a per-lane partial sum)
+    float o[16][2];
+#pragma unroll
+    for (int db = 0; db < 16; ++db) o[db][0] = o[db][1] = 0.f;
+    float carry = 0.f;              // sum of z_ik over the keys of the tiles already swept
+    const float sc2 = p.sm_scale * kLog2e;
+    const bool direct = N <= 8192;
+
+    for (int j0 = ((i0 + kRows - 1) / kKT) * kKT; j0 >= 0; j0 -= kKT) {
+        __syncthreads();
+        // K tile: 16 bytes of each half per thread -> 8 pairs
+        for (int idx = tid; idx < kKT * 8; idx += kThreads) {
+            const int r = idx >> 3, ch = idx & 7;
+            const T* src = K + (size_t)(j0 + r) * kD + ch * 8;
+            const uint4 x1 = *reinterpret_cast<const uint4*>(src);
+            const uint4 x2 = *reinterpret_cast<const uint4*>(src + kPairs);
+            const uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w}, bb[4] = {x2.x, x2.y, x2.z, x2.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f1 = unpack2<T>(a[e]), f2 = unpack2<T>(bb[e]);
+                ks[r * kKRow + perm_slot(ch * 8 + 2 * e)] = pack_half2(f1.x, f2.x);
+                ks[r * kKRow + perm_slot(ch * 8 + 2 * e + 1)] = pack_half2(f1.y, f2.y);
+            }
+        }
+        // V tile: row-major fp16
+        for (int idx = tid; idx < kKT * 16; idx += kThreads) {
+            const int r = idx >> 4, ch = idx & 15;
+            uint4 x = *reinterpret_cast<const uint4*>(V + (size_t)(j0 + r) * kD + ch * 8);
+            if (Elem<T>::kDtype == COROPE_DTYPE_BF16) {
+                uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf162(w4[e]);
+                    w4[e] = pack_half2_sat(f.x, f.y);
+                }
+                x = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+            *reinterpret_cast<uint4*>(vs + r * kVRowBytes + ch * 16) = x;
+        }
+        __syncthreads();
+
+        // 1. leader gates: rows of A = the CTA's 8 query rows, warp w takes keys 8w .. 8w+7 (B = raw K pairs)
+        {
+            const uint4* kp = reinterpret_cast<const uint4*>(ks + (warp * 8 + h) * kKRow) + c;
+            const uint4* qp = reinterpret_cast<const uint4*>(qls + h * kPairs) + c;
+            float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 kv = kp[4 * s], qv = qp[4 * s];
+                mma16816(z0, z1, qv.x, qv.y, kv.x, kv.y, z0, z1);
+                mma16816(z0, z1, qv.z, qv.w, kv.z, kv.w, z0, z1);
+            }
+            // result: row h (query i0 + h), keys j0 + 8 warp + 2c, + 1
+            const int key = j0 + warp * 8 + 2 * c;
+            const int qi = i0 + h;
+            zs[h * kKT + warp * 8 + 2 * c] = key <= qi ? 1.f / (1.f + __expf(-z0 * p.sm_scale)) : 0.f;
+            zs[h * kKT + warp * 8 + 2 * c + 1] = key + 1 <= qi ? 1.f / (1.f + __expf(-z1 * p.sm_scale)) : 0.f;
+        }
+        __syncthreads();
+        // 2. Delta of this warp's row: Delta_j = carry + sum of z over the keys of the tile above j
+        {
+            const float za = zs[warp * kKT + 2 * lane], zb = zs[warp * kKT + 2 * lane + 1];
+            float suf = za + zb;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const float t = __shfl_down_sync(0xffffffffu, suf, off);
+                if (lane + off < 32) suf += t;
+            }
+            const float above = carry + suf - (za + zb);   // keys beyond this lane's pair
+            dl[warp * kKT + 2 * lane + 1] = above;
+            dl[warp * kKT + 2 * lane] = above + zb;
+            carry += __shfl_sync(0xffffffffu, suf, 0);
+        }
+        __syncwarp();
+
+        // 3. scores of the G heads for this row, 8 keys at a time
+        float sc[8][2];
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+            sc[nb][0] = sc[nb][1] = -INFINITY;
+            if (j0 + nb * 8 > i) continue;   // every key of the block is above the diagonal (warp-uniform)
+            const float delta = dl[warp * kKT + nb * 8 + h];
+            const uint4* kp = reinterpret_cast<const uint4*>(ks + (nb * 8 + h) * kKRow) + c;
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 kv = kp[4 * s];
+                const float4 wv = *reinterpret_cast<const float4*>(ws + c * 16 + s * 4);
+                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+                const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
+                uint32_t bf[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sn, cs;
+                    sincos_fast(delta * wq[e], &sn, &cs, direct);
+                    const float2 kk = unpack_half2(kw[e]);
+                    bf[e] = pack_half2(fmaf(kk.x, cs, kk.y * sn), fmaf(kk.y, cs, -kk.x * sn));
+                }
+                mma16816(s0, s1, aq[s * 4 + 0], aq[s * 4 + 1], bf[0], bf[1], s0, s1);
+                mma16816(s0, s1, aq[s * 4 + 2], aq[s * 4 + 3], bf[2], bf[3], s0, s1);
+            }
+            const int key = j0 + nb * 8 + 2 * c;
+            sc[nb][0] = key <= i ? s0 * sc2 : -INFINITY;
+            sc[nb][1] = key + 1 <= i ? s1 * sc2 : -INFINITY;
+        }
+
+        // 4. online softmax of head h (lanes 4h .. 4h+3 hold its 64 scores), then O += P V
+        float mx = m;
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) mx = fmax3(mx, sc[nb][0], sc[nb][1]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float alpha = fast_exp2(m - mx);   // the first tile holds the diagonal, so mx is finite
+        m = mx;
+        float psum = 0.f;
+        uint32_t pa[8];
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+            const float p0 = fast_exp2(sc[nb][0] - mx), p1 = fast_exp2(sc[nb][1] - mx);
+            pa[nb] = pack_half2(p0, p1);
+            const float2 pr = unpack_half2(pa[nb]);   // row sums from the rounded P
+            psum += pr.x + pr.y;
+        }
+        l = l * alpha + psum;
+#pragma unroll
+        for (int db = 0; db < 16; ++db) {
+            o[db][0] *= alpha;
+            o[db][1] *= alpha;
+        }
+        const int n_kc = min(4, (i - j0) / 16 + 1);   // 16-key chunks that hold visible keys (warp-uniform)
+#pragma unroll
+        for (int kc = 0; kc < 4; ++kc) {
+            if (kc >= n_kc) break;
+            const uint8_t* vrow = vs + (kc * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kVRowBytes + (lane >> 4) * 16;
+#pragma unroll
+            for (int dp = 0; dp < 8; ++dp) {
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4_trans(r0, r1, r2, r3, vrow + dp * 32);
+                mma16816(o[2 * dp][0], o[2 * dp][1], pa[2 * kc], pa[2 * kc + 1], r0, r1, o[2 * dp][0], o[2 * dp][1]);
+                mma16816(o[2 * dp + 1][0], o[2 * dp + 1][1], pa[2 * kc], pa[2 * kc + 1], r2, r3, o[2 * dp + 1][0], o[2 * dp + 1][1]);
+            }
+        }
+    }
+
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (h < G) {
+        const float inv = 1.f / l;
+        T* O = reinterpret_cast<T*>(p.out_o) + ((q_head0 + h) * N + i) * kD;
+#pragma unroll
+        for (int db = 0; db < 16; ++db)
+            *reinterpret_cast<uint32_t*>(O + db * 8 + 2 * c) = pack2<T>(o[db][0] * inv, o[db][1] * inv);
+        if (c == 0) p.lse2[(q_head0 + h) * N + i] = m + log2f(l);
+    }
+    if (lane == 0) p.a_diag[(size_t)bg * N + i] = carry;
+}
+
+template <typename T, int G>
+int launch_g(const GqaParams& p, cudaStream_t s) {
+    dim3 grid(p.N / kRows, p.B * p.Hkv);
+    corope_fwd_mma_kernel<T, G><<<grid, kThreads, 0, s>>>(p);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int dispatch(const GqaParams& p, cudaStream_t s) {
+    switch (p.G) {
+        case 1: return launch_g<T, 1>(p, s);
+        case 2: return launch_g<T, 2>(p, s);
+        case 3: return launch_g<T, 3>(p, s);
+        case 4: return launch_g<T, 4>(p, s);
+        case 5: return launch_g<T, 5>(p, s);
+        case 6: return launch_g<T, 6>(p, s);
+        case 7: return launch_g<T, 7>(p, s);
+        case 8: return launch_g<T, 8>(p, s);
+        default: return COROPE_ERR_BAD_GROUP;
+    }
+}
+
+}  // namespace
+
+bool gqa_fwd_mma_supported(int N, int D, int dtype) {
+    return D == kD && N % kKT == 0 && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16);
+}
+
+int launch_gqa_fwd_mma(const GqaParams& p, int dtype, cudaStream_t s) {
+    if (dtype == COROPE_DTYPE_BF16) return dispatch<__nv_bfloat16>(p, s);
+    return dispatch<__half>(p, s);
+}
+
+}  // namespace corope
