@@ -36,12 +36,18 @@ RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dt
 }
 
 struct GqaWorkspace {
-    size_t delta, dk_acc, dv_acc, total;
+    size_t delta, dk_acc, dv_acc, k_pairs, v_half, total;
 };
 
-GqaWorkspace gqa_workspace_layout(bool bwd, int B, int Hq, int Hkv, int N, int D) {
+GqaWorkspace gqa_workspace_layout(bool bwd, int B, int Hq, int Hkv, int N, int D, int dtype) {
     GqaWorkspace w{};
     size_t off = 0;
+    if (!bwd && gqa_fwd_mma_supported(N, D, dtype)) {   // fp16 operand copies of K (pair order) and V for the tensor-core forward
+        w.k_pairs = off;
+        off += align_up((size_t)B * Hkv * N * D * 2, kAlign);
+        w.v_half = off;
+        off += align_up((size_t)B * Hkv * N * D * 2, kAlign);
+    }
     if (bwd) {
         w.delta = off;
         off += align_up((size_t)B * Hq * N * sizeof(float), kAlign);
@@ -103,8 +109,8 @@ size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int 
     switch (op) {
         case COROPE_OP_ROPE_FWD: return rope_workspace_layout(false, B, Hq, N, D, dtype).total;
         case COROPE_OP_ROPE_BWD: return rope_workspace_layout(true, B, Hq, N, D, dtype).total;
-        case COROPE_OP_GQA_FWD: return gqa_workspace_layout(false, B, Hq, Hkv, N, D).total;
-        case COROPE_OP_GQA_BWD: return gqa_workspace_layout(true, B, Hq, Hkv, N, D).total;
+        case COROPE_OP_GQA_FWD: return gqa_workspace_layout(false, B, Hq, Hkv, N, D, dtype).total;
+        case COROPE_OP_GQA_BWD: return gqa_workspace_layout(true, B, Hq, Hkv, N, D, dtype).total;
         default: return 0;
     }
 }
@@ -192,12 +198,14 @@ int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* 
                    int dtype, float sm_scale, float theta, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
     if (!q || !k || !v || !o || !lse2 || !a_diag) return COROPE_ERR_NULL_POINTER;
     if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
-    GqaWorkspace w = gqa_workspace_layout(false, B, Hq, Hkv, N, D);
+    GqaWorkspace w = gqa_workspace_layout(false, B, Hq, Hkv, N, D, dtype);
     if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
     GqaParams p{};
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2; p.a_diag = a_diag;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
     if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype)) {
+        p.k_pairs = reinterpret_cast<uint32_t*>((char*)workspace + w.k_pairs);
+        p.v_half = reinterpret_cast<__half*>((char*)workspace + w.v_half);
         g_last_family[COROPE_OP_GQA_FWD] = 1;
         return launch_gqa_fwd_mma(p, dtype, (cudaStream_t)stream);
     }
@@ -210,7 +218,7 @@ int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, c
                    void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
     if (!q || !k || !v || !o || !d_o || !lse2 || !a_diag || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
     if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
-    GqaWorkspace w = gqa_workspace_layout(true, B, Hq, Hkv, N, D);
+    GqaWorkspace w = gqa_workspace_layout(true, B, Hq, Hkv, N, D, dtype);
     if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
     GqaParams p{};
     p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.dq = dq; p.dk = dk; p.dv = dv;

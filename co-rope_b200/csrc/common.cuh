@@ -81,6 +81,8 @@ struct GqaParams {
     float* delta;    // [B,Hq,N]
     float* dk_acc;   // [B,Hkv,N,D] fp32
     float* dv_acc;   // [B,Hkv,N,D] fp32
+    uint32_t* k_pairs;  // tensor-core forward: [B,Hkv,N,D/2] fp16 (k1, k2) pairs in MMA operand order (workspace)
+    __half* v_half;     // tensor-core forward: [B,Hkv,N,D] fp16 copy of V (workspace)
     int B, Hq, Hkv, G, N, D;
     float sm_scale;
     float theta;

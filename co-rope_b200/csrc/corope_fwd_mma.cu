@@ -30,6 +30,7 @@ constexpr int kKT = 64;             // keys per tile
 constexpr int kD = 128;
 constexpr int kPairs = kD / 2;
 constexpr int kKRow = 80;           // u32 per K row: 64 pairs + 16 of padding (rows of a quarter-warp land in distinct bank groups)
+constexpr int kWStride = 20;        // floats between the frequency blocks of the 4 lane classes (16 + 4: distinct banks)
 constexpr int kVRowBytes = 272;     // bytes per V row: 128 halves + 16 bytes of padding (conflict-free ldmatrix)
 
 // Position (u32 index within a row) of pair p.  MMA k-step t = p / 8 covers pairs 8t..8t+7; lane c = (p % 8) % 4 holds
@@ -55,8 +56,9 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t& r0, uint32_t& r1, ui
                  : "r"(smem_u32(smem_row)));
 }
 
-__device__ __forceinline__ void sincos_fast(float x, float* s, float* c, bool direct) {
-    if (direct) {
+template <bool DIRECT>
+__device__ __forceinline__ void sincos_fast(float x, float* s, float* c) {
+    if (DIRECT) {
         // phases up to a few thousand radians (N <= 8192): the hardware approximations alone
         __sincosf(x, s, c);
     } else {
@@ -73,14 +75,65 @@ __device__ __forceinline__ uint32_t to_half2(T a, T b) {
     return pack_half2(Elem<T>::to_f32(a), Elem<T>::to_f32(b));
 }
 
-template <typename T, int G>
+// Pre-pass: K -> fp16 (k1, k2) pairs in the permuted row order (64 u32 per key), V -> fp16 row-major.  The main kernel
+// then brings tiles in with 16-byte asynchronous copies, two tiles in flight, instead of converting and scattering
+// every tile once per 8 query rows.
+template <typename T>
+__global__ void __launch_bounds__(256) gqa_pack_kv_kernel(const T* __restrict__ K, const T* __restrict__ V, uint32_t* __restrict__ kp,
+                                                          __half* __restrict__ vh, size_t rows) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16: 8 K chunks + 8 V double-chunks
+    if (idx >= rows * 16) return;
+    const size_t r = idx >> 4;
+    const int ch = (int)(idx & 15);
+    if (ch < 8) {
+        const T* src = K + r * kD + ch * 8;
+        const uint4 x1 = *reinterpret_cast<const uint4*>(src);
+        const uint4 x2 = *reinterpret_cast<const uint4*>(src + kPairs);
+        const uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w}, bb[4] = {x2.x, x2.y, x2.z, x2.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f1 = unpack2<T>(a[e]), f2 = unpack2<T>(bb[e]);
+            kp[r * kPairs + perm_slot(ch * 8 + 2 * e)] = pack_half2_sat(f1.x, f2.x);
+            kp[r * kPairs + perm_slot(ch * 8 + 2 * e + 1)] = pack_half2_sat(f1.y, f2.y);
+        }
+    } else {
+        const int c2 = ch - 8;   // 16 elements of V
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            uint4 x = *reinterpret_cast<const uint4*>(V + r * kD + c2 * 16 + u * 8);
+            if (Elem<T>::kDtype == COROPE_DTYPE_BF16) {
+                uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float2 f = unpack_bf162(w4[e]);
+                    w4[e] = pack_half2_sat(f.x, f.y);
+                }
+                x = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
+            *reinterpret_cast<uint4*>(vh + r * kD + c2 * 16 + u * 8) = x;
+        }
+    }
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+constexpr int kKTileBytes = kKT * kKRow * 4;
+constexpr int kVTileBytes = kKT * kVRowBytes;
+constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4;
+
+template <typename T, int G, bool DIRECT>
 __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p) {
-    __shared__ __align__(16) uint32_t ks[kKT * kKRow];            // K tile, (k1, k2) fp16 pairs, permuted rows
-    __shared__ __align__(16) uint8_t vs[kKT * kVRowBytes];        // V tile, fp16 row-major
-    __shared__ __align__(16) uint32_t qls[kRows * kPairs];        // leader rows of the CTA's queries, permuted like K
-    __shared__ float zs[kRows * kKT];
-    __shared__ float dl[kRows * kKT];
-    __shared__ __align__(16) float ws[kPairs];   // inverse frequencies, permuted like K: the 16 of lane c are contiguous
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    uint8_t* ks_base = smem_dyn;                                        // 2 x K tile, (k1, k2) fp16 pairs, permuted rows
+    uint8_t* vs_base = ks_base + 2 * kKTileBytes;                       // 2 x V tile, fp16 row-major
+    uint32_t* qls = reinterpret_cast<uint32_t*>(vs_base + 2 * kVTileBytes);   // leader rows of the CTA's queries, permuted like K
+    float* zs = reinterpret_cast<float*>(qls + kRows * kPairs);
+    float* dl = zs + kRows * kKT;
+    float* ws = dl + kRows * kKT;   // inverse frequencies, permuted like K: the 16 of lane c are contiguous (stride kWStride)
 
     const int N = p.N;
     const int bg = blockIdx.y;
@@ -90,8 +143,20 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     const int h = lane >> 2, c = lane & 3;
     const int i = i0 + warp;
     const size_t q_head0 = (size_t)b * p.Hq + (size_t)g * G;
-    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bg * N * kD;
-    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bg * N * kD;
+    const uint32_t* Kp = p.k_pairs + (size_t)bg * N * kPairs;
+    const __half* Vh = p.v_half + (size_t)bg * N * kD;
+    // asynchronous copy of one tile into buffer `buf`: 64 keys x (16 chunks of K pairs + 16 chunks of V), 8 chunks per thread
+    auto load_tile = [&](int j0, int buf) {
+        uint8_t* kd = ks_base + buf * kKTileBytes;
+        uint8_t* vd = vs_base + buf * kVTileBytes;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * kThreads, r = idx >> 4, ch = idx & 15;
+            cp_async16(kd + r * (kKRow * 4) + ch * 16, Kp + (size_t)(j0 + r) * kPairs + ch * 4);
+            cp_async16(vd + r * kVRowBytes + ch * 16, Vh + (size_t)(j0 + r) * kD + ch * 8);
+        }
+        cp_async_commit();
+    };
     const T* QL = reinterpret_cast<const T*>(p.q) + q_head0 * N * kD;
 
     for (int idx = tid; idx < kRows * kPairs; idx += kThreads) {
@@ -101,7 +166,7 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     }
     for (int d = tid; d < kPairs; d += kThreads) {
         const int cc = (d & 7) & 3, s = d >> 4, e = ((d >> 3) & 1) * 2 + ((d & 7) >> 2);
-        ws[cc * 16 + s * 4 + e] = 1.0f / powf(p.theta, (float)(2 * d) / (float)kD);
+        ws[cc * kWStride + s * 4 + e] = 1.0f / powf(p.theta, (float)(2 * d) / (float)kD);
     }
     __syncthreads();
 
@@ -124,40 +189,16 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     for (int db = 0; db < 16; ++db) o[db][0] = o[db][1] = 0.f;
     float carry = 0.f;              // sum of z_ik over the keys of the tiles already swept
     const float sc2 = p.sm_scale * kLog2e;
-    const bool direct = N <= 8192;
 
-    for (int j0 = ((i0 + kRows - 1) / kKT) * kKT; j0 >= 0; j0 -= kKT) {
-        __syncthreads();
-        // K tile: 16 bytes of each half per thread -> 8 pairs
-        for (int idx = tid; idx < kKT * 8; idx += kThreads) {
-            const int r = idx >> 3, ch = idx & 7;
-            const T* src = K + (size_t)(j0 + r) * kD + ch * 8;
-            const uint4 x1 = *reinterpret_cast<const uint4*>(src);
-            const uint4 x2 = *reinterpret_cast<const uint4*>(src + kPairs);
-            const uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w}, bb[4] = {x2.x, x2.y, x2.z, x2.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float2 f1 = unpack2<T>(a[e]), f2 = unpack2<T>(bb[e]);
-                ks[r * kKRow + perm_slot(ch * 8 + 2 * e)] = pack_half2(f1.x, f2.x);
-                ks[r * kKRow + perm_slot(ch * 8 + 2 * e + 1)] = pack_half2(f1.y, f2.y);
-            }
-        }
-        // V tile: row-major fp16
-        for (int idx = tid; idx < kKT * 16; idx += kThreads) {
-            const int r = idx >> 4, ch = idx & 15;
-            uint4 x = *reinterpret_cast<const uint4*>(V + (size_t)(j0 + r) * kD + ch * 8);
-            if (Elem<T>::kDtype == COROPE_DTYPE_BF16) {
-                uint32_t w4[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float2 f = unpack_bf162(w4[e]);
-                    w4[e] = pack_half2_sat(f.x, f.y);
-                }
-                x = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-            }
-            *reinterpret_cast<uint4*>(vs + r * kVRowBytes + ch * 16) = x;
-        }
-        __syncthreads();
+    const int j_first = ((i0 + kRows - 1) / kKT) * kKT;
+    load_tile(j_first, 0);
+    int buf = 0;
+    for (int j0 = j_first; j0 >= 0; j0 -= kKT, buf ^= 1) {
+        cp_async_wait_all();
+        __syncthreads();   // this tile has landed for every thread, and every warp is done with the previous tile
+        if (j0 >= kKT) load_tile(j0 - kKT, buf ^ 1);
+        const uint32_t* ks = reinterpret_cast<const uint32_t*>(ks_base + buf * kKTileBytes);
+        const uint8_t* vs = vs_base + buf * kVTileBytes;
 
         // 1. leader gates: rows of A = the CTA's 8 query rows, warp w takes keys 8w .. 8w+7 (B = raw K pairs)
         {
@@ -205,14 +246,14 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
                 const uint4 kv = kp[4 * s];
-                const float4 wv = *reinterpret_cast<const float4*>(ws + c * 16 + s * 4);
+                const float4 wv = *reinterpret_cast<const float4*>(ws + c * kWStride + s * 4);
                 const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
                 const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
                 uint32_t bf[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float sn, cs;
-                    sincos_fast(delta * wq[e], &sn, &cs, direct);
+                    sincos_fast<DIRECT>(delta * wq[e], &sn, &cs);
                     const float2 kk = unpack_half2(kw[e]);
                     bf[e] = pack_half2(fmaf(kk.x, cs, kk.y * sn), fmaf(kk.y, cs, -kk.x * sn));
                 }
@@ -278,7 +319,21 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
 template <typename T, int G>
 int launch_g(const GqaParams& p, cudaStream_t s) {
     dim3 grid(p.N / kRows, p.B * p.Hkv);
-    corope_fwd_mma_kernel<T, G><<<grid, kThreads, 0, s>>>(p);
+    const size_t rows = (size_t)p.B * p.Hkv * p.N;
+    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    // phases up to a few thousand radians (N <= 8192) go to the hardware sin / cos directly
+    if (p.N <= 8192) {
+        auto kern = corope_fwd_mma_kernel<T, G, true>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)) != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, kSmemBytes, s>>>(p);
+    } else {
+        auto kern = corope_fwd_mma_kernel<T, G, false>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)) != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, kSmemBytes, s>>>(p);
+    }
     count_launch();
     return (int)cudaGetLastError();
 }
