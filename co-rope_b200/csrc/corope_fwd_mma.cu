@@ -123,7 +123,8 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 constexpr int kKTileBytes = kKT * kKRow * 4;
 constexpr int kVTileBytes = kKT * kVRowBytes;
-constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4;
+constexpr int kAqBytes = kThreads * 16 * 4;   // the query operand of every lane (16 registers' worth), re-read per key block
+constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + kAqBytes;
 
 template <typename T, int G, bool DIRECT>
 __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p) {
@@ -134,6 +135,8 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     float* zs = reinterpret_cast<float*>(qls + kRows * kPairs);
     float* dl = zs + kRows * kKT;
     float* ws = dl + kRows * kKT;   // inverse frequencies, permuted like K: the 16 of lane c are contiguous (stride kWStride)
+    // query operands (A fragments of head lane/4 for the 16 pairs of lane%4): chunk s of lane l at [warp][s][l], so that a
+    // warp's 16-byte loads are contiguous
 
     const int N = p.N;
     const int bg = blockIdx.y;
@@ -142,6 +145,7 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = lane >> 2, c = lane & 3;
     const int i = i0 + warp;
+    uint4* aqs = reinterpret_cast<uint4*>(ws + 4 * kWStride) + warp * 128;
     const size_t q_head0 = (size_t)b * p.Hq + (size_t)g * G;
     const uint32_t* Kp = p.k_pairs + (size_t)bg * N * kPairs;
     const __half* Vh = p.v_half + (size_t)bg * N * kD;
@@ -171,8 +175,8 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     __syncthreads();
 
     // per-lane constants: the 16 pairs of this lane (p = c mod 4), their frequencies, and the query operand of head h
-    uint32_t aq[16];
     {
+        uint32_t aq[16];
         const T* qrow = reinterpret_cast<const T*>(p.q) + ((q_head0 + (h < G ? h : 0)) * N + i) * kD;
 #pragma unroll
         for (int s = 0; s < 4; ++s)
@@ -181,6 +185,9 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
                 const int pp = lane_pair(c, s, e);
                 aq[s * 4 + e] = (h < G) ? to_half2<T>(qrow[pp], qrow[pp + kPairs]) : 0u;
             }
+#pragma unroll
+        for (int s = 0; s < 4; ++s) aqs[s * 32 + lane] = make_uint4(aq[s * 4], aq[s * 4 + 1], aq[s * 4 + 2], aq[s * 4 + 3]);
+        __syncwarp();
     }
 
     float m = -INFINITY, l = 0.f;   // of head h (the 4 lanes of a head agree on m; l is a per-lane partial sum)
@@ -242,7 +249,7 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
             if (j0 + nb * 8 > i) continue;   // every key of the block is above the diagonal (warp-uniform)
             const float delta = dl[warp * kKT + nb * 8 + h];
             const uint4* kp = reinterpret_cast<const uint4*>(ks + (nb * 8 + h) * kKRow) + c;
-            float s0 = 0.f, s1 = 0.f;
+            float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
                 const uint4 kv = kp[4 * s];
@@ -254,15 +261,20 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
                 for (int e = 0; e < 4; ++e) {
                     float sn, cs;
                     sincos_fast<DIRECT>(delta * wq[e], &sn, &cs);
-                    const float2 kk = unpack_half2(kw[e]);
-                    bf[e] = pack_half2(fmaf(kk.x, cs, kk.y * sn), fmaf(kk.y, cs, -kk.x * sn));
+                    // (K'1, K'2) = (k1, k2) (c, c) + (k2, k1) (s, -s) in packed fp16 arithmetic
+                    const __half2 kk = *reinterpret_cast<const __half2*>(&kw[e]);
+                    const uint32_t sw = __byte_perm(kw[e], 0, 0x1032);
+                    const __half2 ksw = *reinterpret_cast<const __half2*>(&sw);
+                    const __half2 r = __hfma2(kk, __floats2half2_rn(cs, cs), __hmul2(ksw, __floats2half2_rn(sn, -sn)));
+                    bf[e] = *reinterpret_cast<const uint32_t*>(&r);
                 }
-                mma16816(s0, s1, aq[s * 4 + 0], aq[s * 4 + 1], bf[0], bf[1], s0, s1);
-                mma16816(s0, s1, aq[s * 4 + 2], aq[s * 4 + 3], bf[2], bf[3], s0, s1);
+                const uint4 av = aqs[s * 32 + lane];
+                mma16816(s0, s1, av.x, av.y, bf[0], bf[1], s0, s1);
+                mma16816(t0, t1, av.z, av.w, bf[2], bf[3], t0, t1);   // two accumulator chains
             }
             const int key = j0 + nb * 8 + 2 * c;
-            sc[nb][0] = key <= i ? s0 * sc2 : -INFINITY;
-            sc[nb][1] = key + 1 <= i ? s1 * sc2 : -INFINITY;
+            sc[nb][0] = key <= i ? (s0 + t0) * sc2 : -INFINITY;
+            sc[nb][1] = key + 1 <= i ? (s1 + t1) * sc2 : -INFINITY;
         }
 
         // 4. online softmax of head h (lanes 4h .. 4h+3 hold its 64 scores), then O += P V
