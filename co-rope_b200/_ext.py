@@ -16,7 +16,7 @@ _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcorope_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "corope_b200.h")
 
-SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu", "corope_fwd_mma.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu", "corope_fwd_mma.cu", "corope_bwd_mma.cu", "noalloc.cu"]
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 OP_ROPE_FWD, OP_ROPE_BWD, OP_GQA_FWD, OP_GQA_BWD = 0, 1, 2, 3

@@ -42,7 +42,7 @@ struct GqaWorkspace {
 GqaWorkspace gqa_workspace_layout(bool bwd, int B, int Hq, int Hkv, int N, int D, int dtype) {
     GqaWorkspace w{};
     size_t off = 0;
-    if (!bwd && gqa_fwd_mma_supported(N, D, dtype)) {   // fp16 operand copies of K (pair order) and V for the tensor-core forward
+    if (gqa_fwd_mma_supported(N, D, dtype)) {   // fp16 operand copies of K (pair order) and V for the tensor-core kernels
         w.k_pairs = off;
         off += align_up((size_t)B * Hkv * N * D * 2, kAlign);
         w.v_half = off;
@@ -227,7 +227,12 @@ int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, c
     p.dk_acc = reinterpret_cast<float*>((char*)workspace + w.dk_acc);
     p.dv_acc = reinterpret_cast<float*>((char*)workspace + w.dv_acc);
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
-    g_last_family[COROPE_OP_GQA_BWD] = 0;
+    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype)) {
+        p.k_pairs = reinterpret_cast<uint32_t*>((char*)workspace + w.k_pairs);
+        p.v_half = reinterpret_cast<__half*>((char*)workspace + w.v_half);
+        p.use_mma = 1;
+    }
+    g_last_family[COROPE_OP_GQA_BWD] = p.use_mma;
     return launch_gqa_bwd_general(p, dtype, (cudaStream_t)stream);
 }
 

@@ -83,6 +83,7 @@ struct GqaParams {
     float* dv_acc;   // [B,Hkv,N,D] fp32
     uint32_t* k_pairs;  // tensor-core forward: [B,Hkv,N,D/2] fp16 (k1, k2) pairs in MMA operand order (workspace)
     __half* v_half;     // tensor-core forward: [B,Hkv,N,D] fp16 copy of V (workspace)
+    int use_mma;        // backward: 1 = tensor-core main kernel (k_pairs / v_half are set), 0 = general kernel
     int B, Hq, Hkv, G, N, D;
     float sm_scale;
     float theta;
@@ -530,6 +531,7 @@ int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_bwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool gqa_fwd_mma_supported(int N, int D, int dtype);
+int launch_gqa_bwd_mma(const GqaParams& p, int dtype, cudaStream_t s);
 int launch_gqa_fwd_mma(const GqaParams& p, int dtype, cudaStream_t s);
 int launch_gqa_fwd_general(const GqaParams& p, int dtype, cudaStream_t s);
 int launch_gqa_bwd_general(const GqaParams& p, int dtype, cudaStream_t s);

@@ -1,0 +1,416 @@
+// Co-RoPE GQA attention backward for 16-bit inputs at D = 128, tensor-core version: as in the forward, the only work
+// left on the CUDA cores is what depends on query, key and frequency together (the rotation by Delta_ij w_p and its
+// inverse); every contraction is an mma.sync m16n8k16 (fp16 operands, fp32 accumulators).
+//
+// Math (corope-exp/corope_attn_gqa_pytorch.py:182-298), one KV head, its G query heads h, leader = first head, s = sm_scale:
+//     z_ik = sigmoid(s qL_i.k_k)   Delta_ij = a_ii - sum_{k<=j} z_ik   K'_ij = R(Delta_ij w) k_j   S_hij = s q_hi.K'_ij
+//     P = exp(S - lse)   g_hij = s P_hij (dO_hi.V_j - delta_hi)
+//     dV_j   += sum_{i,h} P_hij dO_hi
+//     dq_hi  += sum_j g_hij K'_ij                                   (per pair p: components 1 and 2)
+//     u_ij    = sum_h g_hij q_hi        dk_j += R(-Delta_ij w) u_ij
+//     gD_ij   = - sum_h g_hij sum_p w_p (q2 K'1 - q1 K'2)           (mileage gradient)
+//     gz_ik   = sum_{j<k} gD_ij   graw_ik = gz_ik z_ik (1 - z_ik) s    dqL_i += sum_k graw_ik k_k    dk_k += sum_i graw_ik qL_i
+// One CTA = 8 consecutive query rows of one (batch, KV head), one warp per row, key tiles of 64 swept upward (gz is a
+// prefix sum in j).  Per block of 8 keys a warp runs, with lane = (key or head: lane / 4, c = lane % 4):
+//   K' for the lane's 16 pairs (B operand)            -> S (A = q pairs) and the mileage term (A = w (q2, -q1))
+//   dO.V (A = dO of the row, B = V via ldmatrix)      -> P, g, gD (summed over heads with shuffles), gz, graw
+//   u = g^T q (A = g transposed with movmatrix)       -> inverse rotation on the CUDA cores, added to a shared dK tile
+//   dq += g K'^T, dqL += graw k^T (B = movmatrix of the K' / k registers): accumulators in registers for the whole row
+// dV is summed over the CTA's rows by the tensor cores at the end of each tile (K dimension = (row, head)) and goes
+// to the fp32 global accumulator with vector reductions, as does the shared dK tile.
+#include "corope_mma.cuh"
+
+namespace corope {
+namespace {
+
+using namespace gqa_mma;
+
+constexpr int kKTileBytes = kKT * kKRow * 4;
+constexpr int kVTileBytes = kKT * kVRowBytes;
+constexpr int kTabBytes = kThreads * 16 * 4;    // one per-lane operand table: 16 registers' worth for each of the 256 threads
+constexpr int kPsRowBytes = 144;                // P rows (64 keys fp16) + 16 bytes of padding
+constexpr int kDkStride = 132;                  // floats per row of the shared dK tile (128 + 4: conflict-free reductions)
+constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + 4 * kTabBytes +
+                              64 * kPsRowBytes + 64 * kVRowBytes + kKT * kDkStride * 4;
+static_assert(kSmemBytes <= 232448 - 1024, "shared memory budget");
+
+__device__ __forceinline__ void mma16816_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(smem_u32(smem_row)));
+}
+// transpose of an 8x8 matrix of 16-bit values held one register per lane (row = lane / 4, columns 2 (lane % 4), +1)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void red_add_v2(float* gptr, float a, float b) {
+    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(gptr), "f"(a), "f"(b) : "memory");
+}
+
+template <typename T, int G, bool DIRECT>
+__global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p) {
+    constexpr int kKG = 8 * G;                        // (row, head) pairs of the CTA: K dimension of the dV product
+    constexpr int kKSteps = (kKG + 15) / 16;
+    extern __shared__ __align__(16) uint8_t smem_dyn[];
+    uint8_t* ks_base = smem_dyn;
+    uint8_t* vs_base = ks_base + 2 * kKTileBytes;
+    uint32_t* qls = reinterpret_cast<uint32_t*>(vs_base + 2 * kVTileBytes);   // leader rows, permuted like K
+    float* zs = reinterpret_cast<float*>(qls + kRows * kPairs);
+    float* dl = zs + kRows * kKT;
+    float* ws = dl + kRows * kKT;
+    uint4* tab = reinterpret_cast<uint4*>(ws + 4 * kWStride);                  // 4 tables x [warp][chunk s][lane]
+    uint8_t* ps = reinterpret_cast<uint8_t*>(tab) + 4 * kTabBytes;             // P of the tile: [(row, head)][key] fp16
+    uint8_t* dos = ps + 64 * kPsRowBytes;                                      // dO of the CTA's rows: [(row, head)][d] fp16
+    float* dk_t = reinterpret_cast<float*>(dos + 64 * kVRowBytes);             // [key][d] fp32, reduced into by all warps
+
+    const int N = p.N;
+    const int bg = blockIdx.y;
+    const int b = bg / p.Hkv, g = bg % p.Hkv;
+    const int i0 = (gridDim.x - 1 - blockIdx.x) * kRows;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = lane >> 2, c = lane & 3;
+    const int i = i0 + warp;
+    const size_t q_head0 = (size_t)b * p.Hq + (size_t)g * G;
+    const uint32_t* Kp = p.k_pairs + (size_t)bg * N * kPairs;
+    const __half* Vh = p.v_half + (size_t)bg * N * kD;
+    const T* Q = reinterpret_cast<const T*>(p.q);
+    const T* DO = reinterpret_cast<const T*>(p.d_o);
+    float* dk_acc = p.dk_acc + (size_t)bg * N * kD;
+    float* dv_acc = p.dv_acc + (size_t)bg * N * kD;
+    uint4* aqs = tab + warp * 128;             // (q1, q2) pairs of head h for the lane's 16 pairs: A operand of S
+    uint4* aws = aqs + kThreads * 4;           // w (q2, -q1): A operand of the mileage term
+    uint4* ados = aws + kThreads * 4;          // dO of head h, all d: A operand of dO.V
+    uint4* bqs = ados + kThreads * 4;          // q of heads 2c, 2c+1 at the pair component lane/4 selects: B operand of u = g^T q
+
+    auto load_tile = [&](int j0, int buf) {
+        uint8_t* kd = ks_base + buf * kKTileBytes;
+        uint8_t* vd = vs_base + buf * kVTileBytes;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int idx = tid + it * kThreads, r = idx >> 4, ch = idx & 15;
+            cp_async16(kd + r * (kKRow * 4) + ch * 16, Kp + (size_t)(j0 + r) * kPairs + ch * 4);
+            cp_async16(vd + r * kVRowBytes + ch * 16, Vh + (size_t)(j0 + r) * kD + ch * 8);
+        }
+        cp_async_commit();
+    };
+    load_tile(0, 0);
+
+    // ---- per-CTA and per-lane constants
+    for (int idx = tid; idx < kRows * kPairs; idx += kThreads) {
+        const int r = idx >> 6, pp = idx & 63;
+        const T* row = Q + (q_head0 * N + i0 + r) * kD;
+        qls[r * kPairs + perm_slot(pp)] = to_half2<T>(row[pp], row[pp + kPairs]);
+    }
+    for (int d = tid; d < kPairs; d += kThreads) {
+        const int cc = (d & 7) & 3, s = d >> 4, e = ((d >> 3) & 1) * 2 + ((d & 7) >> 2);
+        ws[cc * kWStride + s * 4 + e] = 1.0f / powf(p.theta, (float)(2 * d) / (float)kD);
+    }
+    for (int idx = tid; idx < 64 * (kPsRowBytes / 4); idx += kThreads) reinterpret_cast<uint32_t*>(ps)[idx] = 0u;
+    for (int idx = tid; idx < 64 * 64; idx += kThreads) {   // dO rows of the CTA as fp16, rows beyond 8 G stay zero
+        const int r = idx >> 6, d2 = idx & 63;
+        uint32_t val = 0u;
+        if (r < kKG) {
+            const T* row = DO + ((q_head0 + r % G) * N + i0 + r / G) * kD;
+            val = to_half2<T>(row[2 * d2], row[2 * d2 + 1]);
+        }
+        *reinterpret_cast<uint32_t*>(dos + r * kVRowBytes + d2 * 4) = val;
+    }
+    for (int idx = tid; idx < kKT * kDkStride; idx += kThreads) dk_t[idx] = 0.f;
+    __syncthreads();
+    {
+        const bool valid = h < G;
+        const T* qrow = Q + ((q_head0 + (valid ? h : 0)) * N + i) * kD;
+        const T* dorow = DO + ((q_head0 + (valid ? h : 0)) * N + i) * kD;
+        const int ha = 2 * c, hb = 2 * c + 1;   // the two heads of the lane's B-operand entries
+        const T* qa = Q + ((q_head0 + (ha < G ? ha : 0)) * N + i) * kD;
+        const T* qb = Q + ((q_head0 + (hb < G ? hb : 0)) * N + i) * kD;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+            uint32_t a[4], aw[4], ad[4], bq[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int pp = lane_pair(c, s, e);
+                const float w = ws[c * kWStride + s * 4 + e];
+                const float q1 = Elem<T>::to_f32(qrow[pp]), q2 = Elem<T>::to_f32(qrow[pp + kPairs]);
+                a[e] = valid ? pack_half2(q1, q2) : 0u;
+                aw[e] = valid ? pack_half2(w * q2, -w * q1) : 0u;
+                // dO operand: k-step t = 2 s + e / 2, register e % 2 (0: d = 16 t + 2c, +1;  1: d = 16 t + 8 + 2c, +1)
+                const int d0 = 16 * (2 * s + (e >> 1)) + 8 * (e & 1) + 2 * c;
+                ad[e] = valid ? to_half2<T>(dorow[d0], dorow[d0 + 1]) : 0u;
+                // B operand of u-MMA x = 4 s + e = 2 t + u: column n = lane / 4 is pair 8 t + n / 2 + 4 u, component n % 2
+                const int t = 2 * s + (e >> 1), u = e & 1;
+                const int col = 8 * t + (h >> 1) + 4 * u + kPairs * (h & 1);
+                bq[e] = pack_half2(ha < G ? Elem<T>::to_f32(qa[col]) : 0.f, hb < G ? Elem<T>::to_f32(qb[col]) : 0.f);
+            }
+            aqs[s * 32 + lane] = make_uint4(a[0], a[1], a[2], a[3]);
+            aws[s * 32 + lane] = make_uint4(aw[0], aw[1], aw[2], aw[3]);
+            ados[s * 32 + lane] = make_uint4(ad[0], ad[1], ad[2], ad[3]);
+            bqs[s * 32 + lane] = make_uint4(bq[0], bq[1], bq[2], bq[3]);
+        }
+        __syncwarp();
+    }
+    const bool valid = h < G;
+    const float lse = valid ? p.lse2[(q_head0 + h) * N + i] : 0.f;
+    const float dlt = valid ? p.delta[(q_head0 + h) * N + i] : 0.f;
+    const float a_ii = p.a_diag[(size_t)bg * N + i];
+    const float sc2 = p.sm_scale * kLog2e;
+    float dq[16][2];
+#pragma unroll
+    for (int x = 0; x < 16; ++x) dq[x][0] = dq[x][1] = 0.f;
+    float carry_a = 0.f, carry_g = 0.f;
+
+    const int j_last = ((i0 + kRows - 1) / kKT) * kKT;
+    int buf = 0;
+    for (int j0 = 0; j0 <= j_last; j0 += kKT, buf ^= 1) {
+        cp_async_wait_all();
+        __syncthreads();   // tile landed; the previous tile's dV / dK flush is complete
+        if (j0 + kKT <= j_last) load_tile(j0 + kKT, buf ^ 1);
+        const uint32_t* ks = reinterpret_cast<const uint32_t*>(ks_base + buf * kKTileBytes);
+        const uint8_t* vs = vs_base + buf * kVTileBytes;
+
+        // 1. leader gates (rows of A = the CTA's 8 query rows; warp w takes keys 8w .. 8w+7)
+        {
+            const uint4* kp = reinterpret_cast<const uint4*>(ks + (warp * 8 + h) * kKRow) + c;
+            const uint4* qp = reinterpret_cast<const uint4*>(qls + h * kPairs) + c;
+            float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 kv = kp[4 * s], qv = qp[4 * s];
+                mma16816(z0, z1, qv.x, qv.y, kv.x, kv.y, z0, z1);
+                mma16816(z0, z1, qv.z, qv.w, kv.z, kv.w, z0, z1);
+            }
+            const int key = j0 + warp * 8 + 2 * c;
+            const int qi = i0 + h;
+            zs[h * kKT + warp * 8 + 2 * c] = key <= qi ? 1.f / (1.f + __expf(-z0 * p.sm_scale)) : 0.f;
+            zs[h * kKT + warp * 8 + 2 * c + 1] = key + 1 <= qi ? 1.f / (1.f + __expf(-z1 * p.sm_scale)) : 0.f;
+        }
+        __syncthreads();
+        // 2. Delta_ij = a_ii - sum_{k <= j} z_ik
+        {
+            const float za = zs[warp * kKT + 2 * lane], zb = zs[warp * kKT + 2 * lane + 1];
+            float pre = za + zb;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, pre, off);
+                if (lane >= off) pre += t;
+            }
+            dl[warp * kKT + 2 * lane] = a_ii - (carry_a + pre - zb);
+            dl[warp * kKT + 2 * lane + 1] = a_ii - (carry_a + pre);
+            carry_a += __shfl_sync(0xffffffffu, pre, 31);
+        }
+        __syncwarp();
+
+        // 3. blocks of 8 keys
+#pragma unroll 1
+        for (int nb = 0; nb < 8; ++nb) {
+            uint32_t* ps_out = reinterpret_cast<uint32_t*>(ps + (warp * G + h) * kPsRowBytes + (nb * 8 + 2 * c) * 2);
+            if (j0 + nb * 8 > i) {   // every key of the block is above the diagonal (warp-uniform)
+                if (valid) *ps_out = 0u;
+                continue;
+            }
+            const float delta = dl[warp * kKT + nb * 8 + h];
+            const uint4* kp = reinterpret_cast<const uint4*>(ks + (nb * 8 + h) * kKRow) + c;
+            uint32_t kpr[16], csr[16];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 kv = kp[4 * s];
+                const float4 wv = *reinterpret_cast<const float4*>(ws + c * kWStride + s * 4);
+                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+                const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float sn, cs;
+                    sincos_fast<DIRECT>(delta * wq[e], &sn, &cs);
+                    const __half2 kk = *reinterpret_cast<const __half2*>(&kw[e]);
+                    const uint32_t sw = __byte_perm(kw[e], 0, 0x1032);
+                    const __half2 ksw = *reinterpret_cast<const __half2*>(&sw);
+                    const __half2 r = __hfma2(kk, __floats2half2_rn(cs, cs), __hmul2(ksw, __floats2half2_rn(sn, -sn)));
+                    kpr[s * 4 + e] = *reinterpret_cast<const uint32_t*>(&r);
+                    csr[s * 4 + e] = pack_half2(cs, sn);
+                }
+            }
+            // S, the mileage term and dO.V
+            float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f, m0 = 0.f, m1 = 0.f, n0 = 0.f, n1 = 0.f, dp0 = 0.f, dp1 = 0.f, e0 = 0.f, e1 = 0.f;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 av = aqs[s * 32 + lane], aw = aws[s * 32 + lane], ad = ados[s * 32 + lane];
+                mma16816(s0, s1, av.x, av.y, kpr[4 * s], kpr[4 * s + 1], s0, s1);
+                mma16816(t0, t1, av.z, av.w, kpr[4 * s + 2], kpr[4 * s + 3], t0, t1);
+                mma16816(m0, m1, aw.x, aw.y, kpr[4 * s], kpr[4 * s + 1], m0, m1);
+                mma16816(n0, n1, aw.z, aw.w, kpr[4 * s + 2], kpr[4 * s + 3], n0, n1);
+                uint32_t r0, r1, r2, r3;   // V[key][d]: k-steps 2s and 2s+1 (16 d each)
+                ldmatrix_x4(r0, r1, r2, r3, vs + (nb * 8 + (lane & 7)) * kVRowBytes + s * 64 + (lane >> 3) * 16);
+                mma16816(dp0, dp1, ad.x, ad.y, r0, r1, dp0, dp1);
+                mma16816(e0, e1, ad.z, ad.w, r2, r3, e0, e1);
+            }
+            // P, g, gD (rows = heads, columns = keys 2c, 2c+1 of the block)
+            const int key = j0 + nb * 8 + 2 * c;
+            const bool vis0 = valid && key <= i, vis1 = valid && key + 1 <= i;
+            const float p0 = vis0 ? fast_exp2((s0 + t0) * sc2 - lse) : 0.f;
+            const float p1 = vis1 ? fast_exp2((s1 + t1) * sc2 - lse) : 0.f;
+            const float g0 = p0 * (dp0 + e0 - dlt) * p.sm_scale, g1 = p1 * (dp1 + e1 - dlt) * p.sm_scale;
+            if (valid) *ps_out = pack_half2(p0, p1);
+            const uint32_t gp = pack_half2(g0, g1);
+            float gd0 = -g0 * (m0 + n0), gd1 = -g1 * (m1 + n1);
+#pragma unroll
+            for (int off = 4; off < 32; off <<= 1) {   // sum over the heads
+                gd0 += __shfl_xor_sync(0xffffffffu, gd0, off);
+                gd1 += __shfl_xor_sync(0xffffffffu, gd1, off);
+            }
+            // gz: exclusive prefix over the keys of the row (keys 2c, 2c+1 in lane c of every head group)
+            float incl = gd0 + gd1;
+            {
+                float t = __shfl_up_sync(0xffffffffu, incl, 1);
+                if (c >= 1) incl += t;
+                t = __shfl_up_sync(0xffffffffu, incl, 2);
+                if (c >= 2) incl += t;
+            }
+            const float gz0 = carry_g + incl - (gd0 + gd1), gz1 = gz0 + gd0;
+            carry_g += __shfl_sync(0xffffffffu, incl, lane | 3);
+            const float z0 = zs[warp * kKT + nb * 8 + 2 * c], z1 = zs[warp * kKT + nb * 8 + 2 * c + 1];
+            const float gr0 = key <= i ? gz0 * z0 * (1.f - z0) * p.sm_scale : 0.f;
+            const float gr1 = key + 1 <= i ? gz1 * z1 * (1.f - z1) * p.sm_scale : 0.f;
+            // graw of the key this lane holds in the B-operand layout (key = lane / 4)
+            const int src = (lane & ~3) | (h >> 1);
+            const float gra = __shfl_sync(0xffffffffu, gr0, src), grb = __shfl_sync(0xffffffffu, gr1, src);
+            const float gk = (h & 1) ? grb : gra;
+
+            // u = g^T q per pair, inverse rotation, leader term, into the shared dK tile
+            const uint32_t gT = movmatrix_trans(gp);
+            float* dkrow = dk_t + (nb * 8 + h) * kDkStride;
+            const uint4* qlp = reinterpret_cast<const uint4*>(qls + warp * kPairs) + c;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 bv = bqs[s * 32 + lane], qv = qlp[4 * s];
+                const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w}, ql[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float u1 = 0.f, u2 = 0.f;
+                    mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
+                    const float2 cs = unpack_half2(csr[s * 4 + e]);
+                    const float2 qq = unpack_half2(ql[e]);
+                    const int pp = lane_pair(c, s, e);
+                    atomicAdd(dkrow + pp, fmaf(u1, cs.x, fmaf(-u2, cs.y, gk * qq.x)));
+                    atomicAdd(dkrow + pp + kPairs, fmaf(u2, cs.x, fmaf(u1, cs.y, gk * qq.y)));
+                }
+            }
+            // dq += g K'^T and, for the leader (row 0 of A), graw k^T
+            const uint32_t ga = h == 0 ? pack_half2(gr0, gr1) : 0u;
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const uint4 kv = kp[4 * s];
+                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int x = s * 4 + e;
+                    mma16816(dq[x][0], dq[x][1], gp, 0u, movmatrix_trans(kpr[x]), 0u, dq[x][0], dq[x][1]);
+                    mma16816(dq[x][0], dq[x][1], ga, 0u, movmatrix_trans(kw[e]), 0u, dq[x][0], dq[x][1]);
+                }
+            }
+        }
+        __syncthreads();
+
+        // 4. dV of the tile: [key][d] = sum over (row, head) of P^T dO; warp w takes keys 16 (w / 2) .. +15 and d 64 (w % 2) .. +63
+        {
+            const int mb = warp >> 1, nh = warp & 1;
+            float acc[8][4];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < kKSteps; ++kk) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a[0], a[1], a[2], a[3],
+                                  ps + (kk * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * kPsRowBytes + (mb * 16 + ((lane >> 3) & 1) * 8) * 2);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4_trans(r0, r1, r2, r3,
+                                      dos + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kVRowBytes + (nh * 64 + np * 16 + (lane >> 4) * 8) * 2);
+                    mma16816_full(acc[2 * np], a, r0, r1);
+                    mma16816_full(acc[2 * np + 1], a, r2, r3);
+                }
+            }
+            const int i_last = i0 + kRows - 1;
+            const int ka = j0 + mb * 16 + h, kb = ka + 8;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const int d = nh * 64 + n * 8 + 2 * c;
+                if (ka <= i_last) red_add_v2(dv_acc + (size_t)ka * kD + d, acc[n][0], acc[n][1]);
+                if (kb <= i_last) red_add_v2(dv_acc + (size_t)kb * kD + d, acc[n][2], acc[n][3]);
+            }
+            // the shared dK tile goes to the global accumulator and is cleared for the next tile
+            for (int idx = tid; idx < kKT * 64; idx += kThreads) {
+                const int r = idx >> 6, d2 = (idx & 63) * 2;
+                float* src = dk_t + r * kDkStride + d2;
+                if (j0 + r <= i_last) red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, src[0], src[1]);
+                src[0] = 0.f;
+                src[1] = 0.f;
+            }
+        }
+    }
+
+    if (valid) {
+        T* DQ = reinterpret_cast<T*>(p.dq) + ((q_head0 + h) * N + i) * kD;
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int pp = lane_pair(c, s, e);
+                DQ[pp] = Elem<T>::from_f32(dq[s * 4 + e][0]);
+                DQ[pp + kPairs] = Elem<T>::from_f32(dq[s * 4 + e][1]);
+            }
+    }
+}
+
+template <typename T, int G>
+int launch_g(const GqaParams& p, cudaStream_t s) {
+    dim3 grid(p.N / kRows, p.B * p.Hkv);
+    const size_t rows = (size_t)p.B * p.Hkv * p.N;
+    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (p.N <= 8192) {
+        auto kern = corope_bwd_mma_kernel<T, G, true>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)) != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, kSmemBytes, s>>>(p);
+    } else {
+        auto kern = corope_bwd_mma_kernel<T, G, false>;
+        if ((e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)) != cudaSuccess) return (int)e;
+        kern<<<grid, kThreads, kSmemBytes, s>>>(p);
+    }
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+template <typename T>
+int dispatch(const GqaParams& p, cudaStream_t s) {
+    switch (p.G) {
+        case 1: return launch_g<T, 1>(p, s);
+        case 2: return launch_g<T, 2>(p, s);
+        case 3: return launch_g<T, 3>(p, s);
+        case 4: return launch_g<T, 4>(p, s);
+        case 5: return launch_g<T, 5>(p, s);
+        case 6: return launch_g<T, 6>(p, s);
+        case 7: return launch_g<T, 7>(p, s);
+        case 8: return launch_g<T, 8>(p, s);
+        default: return COROPE_ERR_BAD_GROUP;
+    }
+}
+
+}  // namespace
+
+// The main backward kernel only (delta, the zeroing of the fp32 dK / dV accumulators and their conversion are the caller's).
+int launch_gqa_bwd_mma(const GqaParams& p, int dtype, cudaStream_t s) {
+    if (dtype == COROPE_DTYPE_BF16) return dispatch<__nv_bfloat16>(p, s);
+    return dispatch<__half>(p, s);
+}
+
+}  // namespace corope

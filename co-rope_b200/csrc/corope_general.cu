@@ -506,7 +506,7 @@ int bwd_all(const GqaParams& p, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dk_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dv_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
-    if (int r = dispatch_gd<T>(p, s, true)) return r;
+    if (int r = p.use_mma ? launch_gqa_bwd_mma(p, Elem<T>::kDtype, s) : dispatch_gd<T>(p, s, true)) return r;
     gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dk_acc, (T*)p.dk, kv_elems); count_launch();
     gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dv_acc, (T*)p.dv, kv_elems); count_launch();
     return (int)cudaGetLastError();

@@ -227,17 +227,22 @@ def test_corope_config4_unit_bf16():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("cfg", [(1, 1, 1, 128), (1, 2, 1, 192), (1, 3, 1, 64), (2, 8, 2, 256), (1, 8, 1, 320), (1, 5, 1, 128)])
-def test_corope_tensor_core_forward_groups(dtype, cfg):
-    # the mma forward (16-bit, D = 128, N % 64 == 0) for every group-size path, against the oracle on the same values
+def test_corope_tensor_core_groups(dtype, cfg):
+    # the mma kernels (16-bit, D = 128, N % 64 == 0) for every group-size path, forward and all gradients, against the
+    # oracle on the same values
     B, Hq, Hkv, N = cfg
     D = 128
     q = draw((B, Hq, N, D), 31, dtype)
     k = draw((B, Hkv, N, D), 32, dtype)
     v = draw((B, Hkv, N, D), 33, dtype)
-    o, _, _, _ = run_corope(q, k, v, None, D ** -0.5, 10000.0)
+    do = draw((B, Hq, N, D), 34, dtype)
+    o, dq, dk, dv = run_corope(q, k, v, do, D ** -0.5, 10000.0)
     assert ext.lib().corope_last_kernel_family(ext.OP_GQA_FWD) == 1
+    assert ext.lib().corope_last_kernel_family(ext.OP_GQA_BWD) == 1
     ro = oracle.corope_gqa_fwd(q, k, v, True, D ** -0.5, 10000.0)
     assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.corope_gqa_bwd(q, k, v, do, True, D ** -0.5, 10000.0)):
+        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
 
 
 def test_fused_rope_tensor_core_results_are_reproducible():
