@@ -29,7 +29,15 @@ constexpr int kKTileBytes = kKT * kKRow * 4;
 constexpr int kVTileBytes = kKT * kVRowBytes;
 constexpr int kTabBytes = kThreads * 16 * 4;    // one per-lane operand table: 16 registers' worth for each of the 256 threads
 constexpr int kPsRowBytes = 144;                // P rows (64 keys fp16) + 16 bytes of padding
-constexpr int kDkStride = 132;                  // floats per row of the shared dK tile (128 + 4: conflict-free reductions)
+constexpr int kDkStride = 132;                  // words per row of the shared dK tile (128 + 4: conflict-free reductions)
+// The shared dK tile is summed in 32-bit fixed point (2^-14 units): integer shared-memory atomics are single
+// instructions, fp32 ones are compare-and-swap loops, and the sum no longer depends on the order of the warps.  One
+// contribution is below 256 in magnitude by a wide margin (|g| |q| G); its rounding error of 3e-5 is far below the
+// 16-bit output resolution.  x * 2^14 + 1.5 * 2^23 holds round(x * 2^14) in its low mantissa bits.
+constexpr float kDkScale = 16384.f, kDkMagic = 12582912.f;
+__device__ __forceinline__ void dk_add(int* slot, float x) {
+    atomicAdd(slot, __float_as_int(fmaf(x, kDkScale, kDkMagic)) - 0x4B400000);
+}
 constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + 4 * kTabBytes +
                               64 * kPsRowBytes + 64 * kVRowBytes + kKT * kDkStride * 4;
 static_assert(kSmemBytes <= 232448 - 1024, "shared memory budget");
@@ -68,7 +76,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
     uint4* tab = reinterpret_cast<uint4*>(ws + 4 * kWStride);                  // 4 tables x [warp][chunk s][lane]
     uint8_t* ps = reinterpret_cast<uint8_t*>(tab) + 4 * kTabBytes;             // P of the tile: [(row, head)][key] fp16
     uint8_t* dos = ps + 64 * kPsRowBytes;                                      // dO of the CTA's rows: [(row, head)][d] fp16
-    float* dk_t = reinterpret_cast<float*>(dos + 64 * kVRowBytes);             // [key][d] fp32, reduced into by all warps
+    int* dk_t = reinterpret_cast<int*>(dos + 64 * kVRowBytes);                 // [key][d] fixed point, reduced into by all warps
 
     const int N = p.N;
     const int bg = blockIdx.y;
@@ -122,7 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         }
         *reinterpret_cast<uint32_t*>(dos + r * kVRowBytes + d2 * 4) = val;
     }
-    for (int idx = tid; idx < kKT * kDkStride; idx += kThreads) dk_t[idx] = 0.f;
+    for (int idx = tid; idx < kKT * kDkStride; idx += kThreads) dk_t[idx] = 0;
     __syncthreads();
     {
         const bool valid = h < G;
@@ -155,6 +163,13 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             bqs[s * 32 + lane] = make_uint4(bq[0], bq[1], bq[2], bq[3]);
         }
         __syncwarp();
+    }
+    uint32_t aq[16], aw[16];   // A operands of S and of the mileage term stay in registers for the whole row
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint4 a = aqs[s * 32 + lane], w4 = aws[s * 32 + lane];
+        aq[4 * s] = a.x; aq[4 * s + 1] = a.y; aq[4 * s + 2] = a.z; aq[4 * s + 3] = a.w;
+        aw[4 * s] = w4.x; aw[4 * s + 1] = w4.y; aw[4 * s + 2] = w4.z; aw[4 * s + 3] = w4.w;
     }
     const bool valid = h < G;
     const float lse = valid ? p.lse2[(q_head0 + h) * N + i] : 0.f;
@@ -240,11 +255,11 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f, m0 = 0.f, m1 = 0.f, n0 = 0.f, n1 = 0.f, dp0 = 0.f, dp1 = 0.f, e0 = 0.f, e1 = 0.f;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                const uint4 av = aqs[s * 32 + lane], aw = aws[s * 32 + lane], ad = ados[s * 32 + lane];
-                mma16816(s0, s1, av.x, av.y, kpr[4 * s], kpr[4 * s + 1], s0, s1);
-                mma16816(t0, t1, av.z, av.w, kpr[4 * s + 2], kpr[4 * s + 3], t0, t1);
-                mma16816(m0, m1, aw.x, aw.y, kpr[4 * s], kpr[4 * s + 1], m0, m1);
-                mma16816(n0, n1, aw.z, aw.w, kpr[4 * s + 2], kpr[4 * s + 3], n0, n1);
+                const uint4 ad = ados[s * 32 + lane];
+                mma16816(s0, s1, aq[4 * s], aq[4 * s + 1], kpr[4 * s], kpr[4 * s + 1], s0, s1);
+                mma16816(t0, t1, aq[4 * s + 2], aq[4 * s + 3], kpr[4 * s + 2], kpr[4 * s + 3], t0, t1);
+                mma16816(m0, m1, aw[4 * s], aw[4 * s + 1], kpr[4 * s], kpr[4 * s + 1], m0, m1);
+                mma16816(n0, n1, aw[4 * s + 2], aw[4 * s + 3], kpr[4 * s + 2], kpr[4 * s + 3], n0, n1);
                 uint32_t r0, r1, r2, r3;   // V[key][d]: k-steps 2s and 2s+1 (16 d each)
                 ldmatrix_x4(r0, r1, r2, r3, vs + (nb * 8 + (lane & 7)) * kVRowBytes + s * 64 + (lane >> 3) * 16);
                 mma16816(dp0, dp1, ad.x, ad.y, r0, r1, dp0, dp1);
@@ -284,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
 
             // u = g^T q per pair, inverse rotation, leader term, into the shared dK tile
             const uint32_t gT = movmatrix_trans(gp);
-            float* dkrow = dk_t + (nb * 8 + h) * kDkStride;
+            int* dkrow = dk_t + (nb * 8 + h) * kDkStride;
             const uint4* qlp = reinterpret_cast<const uint4*>(qls + warp * kPairs) + c;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
@@ -297,8 +312,8 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                     const float2 cs = unpack_half2(csr[s * 4 + e]);
                     const float2 qq = unpack_half2(ql[e]);
                     const int pp = lane_pair(c, s, e);
-                    atomicAdd(dkrow + pp, fmaf(u1, cs.x, fmaf(-u2, cs.y, gk * qq.x)));
-                    atomicAdd(dkrow + pp + kPairs, fmaf(u2, cs.x, fmaf(u1, cs.y, gk * qq.y)));
+                    dk_add(dkrow + pp, fmaf(u1, cs.x, fmaf(-u2, cs.y, gk * qq.x)));
+                    dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, fmaf(u1, cs.y, gk * qq.y)));
                 }
             }
             // dq += g K'^T and, for the leader (row 0 of A), graw k^T
@@ -348,10 +363,10 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             // the shared dK tile goes to the global accumulator and is cleared for the next tile
             for (int idx = tid; idx < kKT * 64; idx += kThreads) {
                 const int r = idx >> 6, d2 = (idx & 63) * 2;
-                float* src = dk_t + r * kDkStride + d2;
-                if (j0 + r <= i_last) red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, src[0], src[1]);
-                src[0] = 0.f;
-                src[1] = 0.f;
+                int* src = dk_t + r * kDkStride + d2;
+                if (j0 + r <= i_last) red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, (float)src[0] * (1.f / kDkScale), (float)src[1] * (1.f / kDkScale));
+                src[0] = 0;
+                src[1] = 0;
             }
         }
     }
