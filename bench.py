@@ -321,10 +321,10 @@ def main():
 
     peaks = load_peaks()
     dom_is_bwd = bwd_ms >= fwd_ms
-    fam = lib.corope_last_kernel_family(1 if dom_is_bwd else 0) if kind == "rope" else 0
+    fam = lib.corope_last_kernel_family((1 if dom_is_bwd else 0) + (0 if kind == "rope" else 2))
     roofline = {
         "bound": "tensor", "kernel": ("fused_rope_bwd" if dom_is_bwd else "fused_rope_fwd") if kind == "rope" else ("corope_bwd" if dom_is_bwd else "corope_fwd"),
-        "kernel_family": "tcgen05" if fam == 1 else "cuda-core fp32",
+        "kernel_family": ("tcgen05" if kind == "rope" else "mma.sync contractions + cuda-core rotation") if fam == 1 else "cuda-core fp32",
         "achieved": bwd_tf if dom_is_bwd else fwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops"], "peak_source": peaks["source"] + " cuBLAS bf16 burst",
         "frac_of_sustained": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops_sustained"],

@@ -115,6 +115,8 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
  * the math is that of corope-exp/corope_attn_gqa_pytorch.py:56-124.
  *   q, o   : [B,Hq,N,D];  k, v : [B,Hkv,N,D];  Hq % Hkv == 0, Hq/Hkv <= 8.
  *   lse2   : [B,Hq,N] fp32 (log2 domain);  a_diag : [B,Hkv,N] fp32, the leader mileage a_ii.
+ * For 16-bit inputs at D = 128 and N % 64 == 0 the workspace holds fp16 operand copies of K and V
+ * (4 bytes per element of k); otherwise the forward needs none (corope_workspace_bytes returns the 256-byte minimum).
  */
 int corope_gqa_fwd(const void* q, const void* k, const void* v,
                    void* o, float* lse2, float* a_diag,
