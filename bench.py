@@ -192,6 +192,7 @@ def main():
     ap.add_argument("--ref-units", type=int, default=4, help="(batch, head) units per step of the CPU reference arm")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-chunks", type=int, default=16, help="chunks of (batch, KV head) units in the host-to-host pipeline of the e2e figure")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -288,16 +289,13 @@ def main():
     # end to end: pinned host buffers -> device, forward + backward, results back to pinned host buffers
     e2e = None
     if not args.no_e2e:
-        ho = torch.empty_like(hq)
-        hdq, hdk, hdv = torch.empty_like(hq), torch.empty_like(hk), torch.empty_like(hv)
-        def e2e_step():
-            a, b_, c, d_ = (h.to(dev, non_blocking=True) for h in (hq, hk, hv, hdo))
-            o, (gq, gk, gv) = step(a, b_, c, d_)
-            ho.copy_(o.detach(), non_blocking=True)
-            hdq.copy_(gq, non_blocking=True)
-            hdk.copy_(gk, non_blocking=True)
-            hdv.copy_(gv, non_blocking=True)
-        for _ in range(max(1, args.warmup // 2)):
+        ho, hdq, hdk, hdv = (torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv))   # empty_like alone is pageable
+        def e2e_step():   # the package's call for host tensors: chunks of (batch, KV head) units through copy-in / kernel / copy-out streams
+            if kind == "rope":
+                pkg.attention_fwd_bwd_host(hq, hk, hv, hdo, sm_scale, freqs_cos=cos, freqs_sin=sin, out=(ho, hdq, hdk, hdv), chunks=args.e2e_chunks)
+            else:
+                pkg.attention_fwd_bwd_host(hq, hk, hv, hdo, sm_scale, theta=THETA, out=(ho, hdq, hdk, hdv), chunks=args.e2e_chunks)
+        for _ in range(max(3, args.warmup)):
             e2e_step()
         sync_all()
         e0.record()
@@ -312,7 +310,8 @@ def main():
             e2e_ms = t.item()
         nb = lambda *ts: int(sum(t.numel() * t.element_size() for t in ts))
         e2e = {"value": world * 3.5 * F / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": nb(hq, hk, hv, hdo), "d2h_bytes_per_step": nb(ho, hdq, hdk, hdv)}
+               "h2d_bytes_per_step": nb(hq, hk, hv, hdo), "d2h_bytes_per_step": nb(ho, hdq, hdk, hdv),
+               "api": "attention_fwd_bwd_host", "chunks": args.e2e_chunks}
 
     if rank != 0:
         if world > 1:

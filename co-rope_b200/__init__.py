@@ -7,4 +7,5 @@ from . import _ext  # noqa: F401
 from .fused_rope_attn import attention as fused_rope_attention  # noqa: F401
 from .flash_attn_co_rope_gqa_triton import attention as corope_gqa_attention  # noqa: F401
 from .sharding import shard_units, unit_range  # noqa: F401
+from .host_pipeline import attention_fwd_bwd_host  # noqa: F401
 from ._ext import build, check_status  # noqa: F401

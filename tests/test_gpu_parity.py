@@ -245,6 +245,33 @@ def test_corope_tensor_core_groups(dtype, cfg):
         assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
 
 
+def test_host_pipeline_matches_direct_call():
+    # the chunked host-to-host call must give what one call on the whole tensors gives (units are independent)
+    import importlib
+    pkg = importlib.import_module("co-rope_b200")
+    B, H, N, D = 2, 6, 512, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=41)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    hq, hk, hv, hdo = (t.pin_memory() for t in (q, k, v, do))
+    ho, hdq, hdk, hdv = pkg.attention_fwd_bwd_host(hq, hk, hv, hdo, D ** -0.5, freqs_cos=cos.cuda(), freqs_sin=sin.cuda(), chunks=5)
+    torch.cuda.synchronize()
+    ext.check_status()
+    assert torch.equal(ho.float(), o) and torch.equal(hdk.float(), dk) and torch.equal(hdv.float(), dv)
+    assert maxdiff(hdq, dq) < 1e-2   # dQ is summed with floating-point reductions in an order that varies
+    # Co-RoPE: groups of query heads stay with their KV head
+    q = draw((2, 8, 128, D), 42, torch.bfloat16)
+    k = draw((2, 2, 128, D), 43, torch.bfloat16)
+    v = draw((2, 2, 128, D), 44, torch.bfloat16)
+    do = draw((2, 8, 128, D), 45, torch.bfloat16)
+    o, dq, dk, dv = run_corope(q, k, v, do, D ** -0.5, 10000.0)
+    outs = pkg.attention_fwd_bwd_host(*(t.pin_memory() for t in (q, k, v, do)), D ** -0.5, theta=10000.0, chunks=3)
+    torch.cuda.synchronize()
+    ext.check_status()
+    for got, ref in zip(outs, (o, dq, dk, dv)):
+        assert maxdiff(got, ref) < 2e-2
+
+
 def test_fused_rope_tensor_core_results_are_reproducible():
     # O, dK and dV are accumulated in a fixed order (TMEM accumulators), so repeated calls must agree bit for bit; a
     # difference means a race between the warp-specialised roles.  dQ is summed with floating-point reductions whose
