@@ -289,6 +289,10 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int kk = 0; kk < kBN / 16; ++kk)
                     if (leader) umma_ts2(d, a + (kk >> 2) * 64 + (kk & 3) * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
             };
+            // "operand ready": straight from the TMA barrier when nothing has to touch the tile in shared memory (K rotated by
+            // the pre-pass, V used in its own format), else from the rotation groups
+            const int kReadyBar = p.k_rot != nullptr ? K_FULL : K_ROT;
+            constexpr int kVReadyBar = kConvertV ? V_READY : V_FULL;
             int gk = 0, gv = 0, s0 = 0, s1 = 0;   // K tiles, V tiles, S tiles of group 0 / 1 so far
             bool ok = true;
             for (int n = 0; ok; ++n) {
@@ -298,7 +302,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const int nk = 2 * wi.t + 2, nk0 = nk - 1;
                 // first K tile of the item: S0 = Q0 K^T, S1 = Q1 K^T
                 if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
-                if (!(ok = mbar_wait_warp(&bars[K_ROT + gk % kKStages], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
+                if (!(ok = mbar_wait_warp(&bars[kReadyBar + gk % kKStages], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
                 tc_fence_after();
                 issue_qk(0, gk % kKStages);
                 if (leader) umma_commit(&bars[S_FULL + 0]);
@@ -313,7 +317,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int vs = gv % kVStages;
                     const int ks1 = gk % kKStages;
                     const bool have_next = j + 1 < nk;
-                    if (!(ok = mbar_wait_warp(&bars[V_READY + vs], (gv / kVStages) & 1, p.status, V_READY, abort_flag))) break;
+                    if (!(ok = mbar_wait_warp(&bars[kVReadyBar + vs], (gv / kVStages) & 1, p.status, V_READY, abort_flag))) break;
                     if (j < nk0) {
                         if (!(ok = mbar_wait_warp(&bars[P_FULL + 0], s0 & 1, p.status, P_FULL, abort_flag))) break;
                         if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 0], (n - 1) & 1, p.status, O_FREE, abort_flag))) break;
@@ -323,7 +327,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                         ++s0;
                     }
                     if (have_next) {
-                        if (!(ok = mbar_wait_warp(&bars[K_ROT + ks1], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
+                        if (!(ok = mbar_wait_warp(&bars[kReadyBar + ks1], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
                         tc_fence_after();
                         if (j + 1 < nk0) {
                             issue_qk(0, ks1);
@@ -372,27 +376,30 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
             if (!ok) break;
-            const bool k_pre = p.k_rot != nullptr;   // K tiles arrive rotated (pre-pass): only pass the barriers on
+            // K and V tiles: only where they have to be touched in shared memory (K when no pre-pass has rotated it, V for
+            // the fp16-P variant); otherwise the MMA warp takes them straight from the TMA barriers
+            const bool k_pre = p.k_rot != nullptr;
+            if (k_pre && !kConvertV) continue;
             if (!k_pre) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
             for (int j = 0; j < nk; ++j, ++gk, ++gv) {
                 const int ks = gk % kKStages, vs = gv % kVStages;
-                if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
-#ifndef COROPE_KO_ROT
                 if (!k_pre) {
+                    if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
+#ifndef COROPE_KO_ROT
                     rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
-                    fence_proxy_async();
-                }
 #endif
-                mbar_arrive_warp(&bars[K_ROT + ks], lane);
-                if (!k_pre && j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
-                if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
+                    fence_proxy_async();
+                    mbar_arrive_warp(&bars[K_ROT + ks], lane);
+                    if (j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
+                }
                 if (kConvertV) {
+                    if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
 #ifndef COROPE_KO_ROT
                     convert_tile_bf16_to_f16(sV + vs * kTileBytes + rg * (kTileBytes / 2), tid);
 #endif
                     fence_proxy_async();
+                    mbar_arrive_warp(&bars[V_READY + vs], lane);
                 }
-                mbar_arrive_warp(&bars[V_READY + vs], lane);
             }
         }
     } else {
