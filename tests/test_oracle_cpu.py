@@ -13,7 +13,9 @@ import torch
 import oracle
 
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-REF = os.environ.get("COROPE_REFERENCE_ROOT", "/root/reference")
+# a checkout of the reference: COROPE_REFERENCE_ROOT, else a directory named "reference" beside this repository
+REF = os.environ.get("COROPE_REFERENCE_ROOT",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 
 
 def _t(a):
