@@ -38,8 +38,9 @@ constexpr float kDkScale = 16384.f, kDkMagic = 12582912.f;
 __device__ __forceinline__ void dk_add(int* slot, float x) {
     atomicAdd(slot, __float_as_int(fmaf(x, kDkScale, kDkMagic)) - 0x4B400000);
 }
+constexpr int kGrRowBytes = 144;                // rows of the leader-term operand graw (64 keys fp16 + padding)
 constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + 4 * kTabBytes +
-                              64 * kPsRowBytes + 64 * kVRowBytes + kKT * kDkStride * 4;
+                              64 * kPsRowBytes + 64 * kVRowBytes + kKT * kDkStride * 4 + kRows * kKT * 4 + 16 * kGrRowBytes + 16 * kVRowBytes;
 static_assert(kSmemBytes <= 232448 - 1024, "shared memory budget");
 
 __device__ __forceinline__ void mma16816_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -77,6 +78,9 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
     uint8_t* ps = reinterpret_cast<uint8_t*>(tab) + 4 * kTabBytes;             // P of the tile: [(row, head)][key] fp16
     uint8_t* dos = ps + 64 * kPsRowBytes;                                      // dO of the CTA's rows: [(row, head)][d] fp16
     int* dk_t = reinterpret_cast<int*>(dos + 64 * kVRowBytes);                 // [key][d] fixed point, reduced into by all warps
+    float* gds = reinterpret_cast<float*>(dk_t + kKT * kDkStride);             // gD of the tile: [row][key]
+    uint8_t* grs = reinterpret_cast<uint8_t*>(gds + kRows * kKT);              // graw of the tile: [16 rows (8 used)][key] fp16
+    uint8_t* qlr = grs + 16 * kGrRowBytes;                                     // leader rows, natural order: [16 rows (8 used)][d] fp16
 
     const int N = p.N;
     const int bg = blockIdx.y;
@@ -131,6 +135,16 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         *reinterpret_cast<uint32_t*>(dos + r * kVRowBytes + d2 * 4) = val;
     }
     for (int idx = tid; idx < kKT * kDkStride; idx += kThreads) dk_t[idx] = 0;
+    for (int idx = tid; idx < 16 * (kGrRowBytes / 4); idx += kThreads) reinterpret_cast<uint32_t*>(grs)[idx] = 0u;
+    for (int idx = tid; idx < 16 * 64; idx += kThreads) {
+        const int r = idx >> 6, d2 = idx & 63;
+        uint32_t val = 0u;
+        if (r < kRows) {
+            const T* row = Q + (q_head0 * N + i0 + r) * kD;
+            val = to_half2<T>(row[2 * d2], row[2 * d2 + 1]);
+        }
+        *reinterpret_cast<uint32_t*>(qlr + r * kVRowBytes + d2 * 4) = val;
+    }
     __syncthreads();
     {
         const bool valid = h < G;
@@ -180,6 +194,9 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
 #pragma unroll
     for (int x = 0; x < 16; ++x) dq[x][0] = dq[x][1] = 0.f;
     float carry_a = 0.f, carry_g = 0.f;
+    float dql[2][4];   // leader-term dq of the CTA's 8 rows, operand-order columns 16 warp .. 16 warp + 15 (summed into dq at the end)
+#pragma unroll
+    for (int n = 0; n < 2; ++n) dql[n][0] = dql[n][1] = dql[n][2] = dql[n][3] = 0.f;
 
     const int j_last = ((i0 + kRows - 1) / kKT) * kKT;
     int buf = 0;
@@ -226,8 +243,10 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
 #pragma unroll 1
         for (int nb = 0; nb < 8; ++nb) {
             uint32_t* ps_out = reinterpret_cast<uint32_t*>(ps + (warp * G + h) * kPsRowBytes + (nb * 8 + 2 * c) * 2);
+            float* gd_out = gds + warp * kKT + nb * 8 + 2 * c;
             if (j0 + nb * 8 > i) {   // every key of the block is above the diagonal (warp-uniform)
                 if (valid) *ps_out = 0u;
+                if (h == 0) gd_out[0] = gd_out[1] = 0.f;
                 continue;
             }
             const float delta = dl[warp * kKT + nb * 8 + h];
@@ -279,56 +298,49 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                 gd0 += __shfl_xor_sync(0xffffffffu, gd0, off);
                 gd1 += __shfl_xor_sync(0xffffffffu, gd1, off);
             }
-            // gz: exclusive prefix over the keys of the row (keys 2c, 2c+1 in lane c of every head group)
-            float incl = gd0 + gd1;
-            {
-                float t = __shfl_up_sync(0xffffffffu, incl, 1);
-                if (c >= 1) incl += t;
-                t = __shfl_up_sync(0xffffffffu, incl, 2);
-                if (c >= 2) incl += t;
+            if (h == 0) {   // the mileage-gradient chain (prefix over the keys, leader terms) runs once per tile, below
+                gd_out[0] = gd0;
+                gd_out[1] = gd1;
             }
-            const float gz0 = carry_g + incl - (gd0 + gd1), gz1 = gz0 + gd0;
-            carry_g += __shfl_sync(0xffffffffu, incl, lane | 3);
-            const float z0 = zs[warp * kKT + nb * 8 + 2 * c], z1 = zs[warp * kKT + nb * 8 + 2 * c + 1];
-            const float gr0 = key <= i ? gz0 * z0 * (1.f - z0) * p.sm_scale : 0.f;
-            const float gr1 = key + 1 <= i ? gz1 * z1 * (1.f - z1) * p.sm_scale : 0.f;
-            // graw of the key this lane holds in the B-operand layout (key = lane / 4)
-            const int src = (lane & ~3) | (h >> 1);
-            const float gra = __shfl_sync(0xffffffffu, gr0, src), grb = __shfl_sync(0xffffffffu, gr1, src);
-            const float gk = (h & 1) ? grb : gra;
 
-            // u = g^T q per pair, inverse rotation, leader term, into the shared dK tile
+            // u = g^T q per pair, inverse rotation, into the shared dK tile
             const uint32_t gT = movmatrix_trans(gp);
             int* dkrow = dk_t + (nb * 8 + h) * kDkStride;
-            const uint4* qlp = reinterpret_cast<const uint4*>(qls + warp * kPairs) + c;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                const uint4 bv = bqs[s * 32 + lane], qv = qlp[4 * s];
-                const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w}, ql[4] = {qv.x, qv.y, qv.z, qv.w};
+                const uint4 bv = bqs[s * 32 + lane];
+                const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float u1 = 0.f, u2 = 0.f;
                     mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
                     const float2 cs = unpack_half2(csr[s * 4 + e]);
-                    const float2 qq = unpack_half2(ql[e]);
                     const int pp = lane_pair(c, s, e);
-                    dk_add(dkrow + pp, fmaf(u1, cs.x, fmaf(-u2, cs.y, gk * qq.x)));
-                    dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, fmaf(u1, cs.y, gk * qq.y)));
+                    dk_add(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y));
+                    dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y));
                 }
             }
-            // dq += g K'^T and, for the leader (row 0 of A), graw k^T
-            const uint32_t ga = h == 0 ? pack_half2(gr0, gr1) : 0u;
+            // dq += g K'^T
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint4 kv = kp[4 * s];
-                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+            for (int x = 0; x < 16; ++x) mma16816(dq[x][0], dq[x][1], gp, 0u, movmatrix_trans(kpr[x]), 0u, dq[x][0], dq[x][1]);
+        }
+        // mileage-gradient chain of this row: gz_k = sum of gD over the keys before k, graw = gz z (1 - z) s
+        {
+            __syncwarp();
+            const float ga = gds[warp * kKT + 2 * lane], gb = gds[warp * kKT + 2 * lane + 1];
+            float pre = ga + gb;
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int x = s * 4 + e;
-                    mma16816(dq[x][0], dq[x][1], gp, 0u, movmatrix_trans(kpr[x]), 0u, dq[x][0], dq[x][1]);
-                    mma16816(dq[x][0], dq[x][1], ga, 0u, movmatrix_trans(kw[e]), 0u, dq[x][0], dq[x][1]);
-                }
+            for (int off = 1; off < 32; off <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, pre, off);
+                if (lane >= off) pre += t;
             }
+            const float gz0 = carry_g + pre - (ga + gb), gz1 = gz0 + ga;
+            carry_g += __shfl_sync(0xffffffffu, pre, 31);
+            const float z0 = zs[warp * kKT + 2 * lane], z1 = zs[warp * kKT + 2 * lane + 1];
+            const int key = j0 + 2 * lane;
+            const float gr0 = key <= i ? gz0 * z0 * (1.f - z0) * p.sm_scale : 0.f;
+            const float gr1 = key + 1 <= i ? gz1 * z1 * (1.f - z1) * p.sm_scale : 0.f;
+            *reinterpret_cast<uint32_t*>(grs + warp * kGrRowBytes + lane * 4) = pack_half2(gr0, gr1);
         }
         __syncthreads();
 
@@ -360,7 +372,42 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                 if (ka <= i_last) red_add_v2(dv_acc + (size_t)ka * kD + d, acc[n][0], acc[n][1]);
                 if (kb <= i_last) red_add_v2(dv_acc + (size_t)kb * kD + d, acc[n][2], acc[n][3]);
             }
+            // leader terms of the tile, summed over the CTA's rows by MMAs (K dimension = row):
+            //   dk[key][d] += sum_i graw_ik qL_i[d]   -- the same (keys, d) block of the output as above
+            {
+                float acc2[8][4];
+#pragma unroll
+                for (int n = 0; n < 8; ++n) acc2[n][0] = acc2[n][1] = acc2[n][2] = acc2[n][3] = 0.f;
+                uint32_t a[4];
+                ldmatrix_x4_trans(a[0], a[1], a[2], a[3], grs + ((lane & 7) + ((lane >> 4) & 1) * 8) * kGrRowBytes + (mb * 16 + ((lane >> 3) & 1) * 8) * 2);
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t r0, r1, r2, r3;
+                    ldmatrix_x4_trans(r0, r1, r2, r3, qlr + ((lane & 7) + ((lane >> 3) & 1) * 8) * kVRowBytes + (nh * 64 + np * 16 + (lane >> 4) * 8) * 2);
+                    mma16816_full(acc2[2 * np], a, r0, r1);
+                    mma16816_full(acc2[2 * np + 1], a, r2, r3);
+                }
+                int* ra = dk_t + (mb * 16 + h) * kDkStride + nh * 64 + 2 * c;   // into the shared dK tile (flushed below)
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    dk_add(ra + n * 8, acc2[n][0]);
+                    dk_add(ra + n * 8 + 1, acc2[n][1]);
+                    dk_add(ra + 8 * kDkStride + n * 8, acc2[n][2]);
+                    dk_add(ra + 8 * kDkStride + n * 8 + 1, acc2[n][3]);
+                }
+            }
+            //   dqL_i += sum_k graw_ik k_k   -- warp w takes the operand-order columns 16 w .. 16 w + 15 of k
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+                uint32_t a[4], r0, r1, r2, r3;
+                ldmatrix_x4(a[0], a[1], a[2], a[3], grs + ((lane & 7) + ((lane >> 3) & 1) * 8) * kGrRowBytes + (kk * 16 + (lane >> 4) * 8) * 2);
+                ldmatrix_x4_trans(r0, r1, r2, r3, reinterpret_cast<const uint8_t*>(ks) + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * (kKRow * 4) +
+                                                      (warp * 16 + (lane >> 4) * 8) * 2);
+                mma16816_full(dql[0], a, r0, r1);
+                mma16816_full(dql[1], a, r2, r3);
+            }
             // the shared dK tile goes to the global accumulator and is cleared for the next tile
+            __syncthreads();
             for (int idx = tid; idx < kKT * 64; idx += kThreads) {
                 const int r = idx >> 6, d2 = (idx & 63) * 2;
                 int* src = dk_t + r * kDkStride + d2;
@@ -371,6 +418,27 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         }
     }
 
+    // leader-term dq: from the per-warp column blocks to the lanes that hold the leader head (h == 0) of each row
+    __syncthreads();
+    {
+        float* xs = reinterpret_cast<float*>(dk_t);   // [row][operand-order column], the dK tile is no longer needed
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            xs[h * kD + warp * 16 + n * 8 + 2 * c] = dql[n][0];
+            xs[h * kD + warp * 16 + n * 8 + 2 * c + 1] = dql[n][1];
+        }
+        __syncthreads();
+        if (h == 0) {
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int slot = perm_slot(lane_pair(c, s, e));
+                    dq[s * 4 + e][0] += xs[warp * kD + 2 * slot];
+                    dq[s * 4 + e][1] += xs[warp * kD + 2 * slot + 1];
+                }
+        }
+    }
     if (valid) {
         T* DQ = reinterpret_cast<T*>(p.dq) + ((q_head0 + h) * N + i) * kD;
 #pragma unroll
