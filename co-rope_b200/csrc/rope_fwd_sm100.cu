@@ -472,12 +472,13 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                         f2_unpack(f2_add(f2_pack_bits(sx[2 * i], sx[2 * i + 1]), neg_m), d0, d1); \
                         const float p0 = fast_exp2(d0), p1 = fast_exp2(d1);                  \
                         uint64_t pr;                                                         \
-                        if (kPBf16) {   /* row sums from the rounded P */                    \
+                        if (kPBf16) {   /* row sums from the rounded P, for both formats */   \
                             pk[i] = pack_bf162(p0, p1);                                      \
                             pr = f2_pack_bits(pk[i] << 16, pk[i] & 0xffff0000u);             \
                         } else {                                                             \
                             pk[i] = pack_half2(p0, p1);                                      \
-                            pr = f2_pack(p0, p1);                                            \
+                            const float2 rr = unpack_half2(pk[i]);                           \
+                            pr = f2_pack(rr.x, rr.y);                                        \
                         }                                                                    \
                         if (i & 1) lb = f2_add(lb, pr); else la = f2_add(la, pr);            \
                     }                                                                        \
