@@ -13,11 +13,12 @@
 // One CTA = 8 consecutive query rows of one (batch, KV head), one warp per row, key tiles of 64 swept upward (gz is a
 // prefix sum in j).  Per block of 8 keys a warp runs, with lane = (key or head: lane / 4, c = lane % 4):
 //   K' for the lane's 16 pairs (B operand)            -> S (A = q pairs) and the mileage term (A = w (q2, -q1))
-//   dO.V (A = dO of the row, B = V via ldmatrix)      -> P, g, gD (summed over heads with shuffles), gz, graw
+//   dO.V (A = dO of the row, B = V via ldmatrix)      -> P, g, gD (summed over heads with shuffles, kept per key)
 //   u = g^T q (A = g transposed with movmatrix)       -> inverse rotation on the CUDA cores, added to a shared dK tile
-//   dq += g K'^T, dqL += graw k^T (B = movmatrix of the K' / k registers): accumulators in registers for the whole row
-// dV is summed over the CTA's rows by the tensor cores at the end of each tile (K dimension = (row, head)) and goes
-// to the fp32 global accumulator with vector reductions, as does the shared dK tile.
+//   dq += g K'^T (B = movmatrix of the K' registers): accumulators in registers for the whole row
+// Once per tile: each warp turns its row of gD into gz (prefix over the keys) and graw; then, summed over the CTA's rows
+// by the tensor cores, dV (K dimension = (row, head)), the leader terms dk += graw^T qL and dqL += graw k (K dimension
+// = row / key); dV and the shared dK tile go to the fp32 global accumulators with vector reductions.
 #include "corope_mma.cuh"
 
 namespace corope {
