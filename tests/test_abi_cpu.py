@@ -37,6 +37,18 @@ def test_host_only_entry_points():
     assert nbytes % 256 == 0
     assert L.corope_workspace_bytes(ext.OP_GQA_BWD, 2, 32, 8, 2048, 128, 1) >= 2 * 2 * 8 * 2048 * 128 * 4
     assert L.corope_workspace_bytes(99, 1, 1, 1, 1, 64, 0) == 0
+    # rotated fp16 operand copies of the tensor-core paths: forward = table + 2 bytes per element of k (16-bit, D = 128 only)
+    elems = 2 * 32 * 4096 * 128
+    fwd16 = L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 128, 1)
+    fwd32 = L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 128, 0)
+    assert fwd16 - fwd32 == 2 * elems and fwd32 < 4096 * 64 * 4 + 1024
+    assert nbytes >= 6 * elems                                                      # backward: fp16 Q copy + fp32 dQ accumulator
+    assert L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 64, 1) < 4096 * 32 * 4 + 1024   # D = 64: general kernels, no copy
+    # Co-RoPE: fp16 copies of K and V for the tensor-core kernels (16-bit, D = 128, N % 64 == 0), none otherwise
+    kv = 2 * 8 * 2048 * 128
+    assert L.corope_workspace_bytes(ext.OP_GQA_FWD, 2, 32, 8, 2048, 128, 1) == 4 * kv
+    assert L.corope_workspace_bytes(ext.OP_GQA_FWD, 2, 32, 8, 2048, 128, 0) == 256
+    assert L.corope_workspace_bytes(ext.OP_GQA_FWD, 2, 32, 8, 2000, 128, 1) == 256
 
 
 def test_argument_validation_happens_on_the_host():
