@@ -327,6 +327,7 @@ def main():
         "achieved": bwd_tf if dom_is_bwd else fwd_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
         "frac": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops"], "peak_source": peaks["source"] + " cuBLAS bf16 burst",
         "frac_of_sustained": (bwd_tf if dom_is_bwd else fwd_tf) / peaks["tflops_sustained"],
+        "frac_of_nominal_2250": (bwd_tf if dom_is_bwd else fwd_tf) / 2250.0,
         "traffic": (NCU_DRAM_PER_TENSOR_BYTE["fused_rope_bwd" if dom_is_bwd else "fused_rope_fwd"] * q.numel() * q.element_size()
                     if (kind == "rope" and fam == 1) else None),
         "traffic_unit": "bytes per launch (ncu capture at N=1024, scaled by tensor bytes)",

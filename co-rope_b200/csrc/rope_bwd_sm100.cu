@@ -1,4 +1,4 @@
-// Fused-RoPE causal flash-attention backward for sm_100a: TMA -> shared memory -> in-place rotation of K
+// Fused-RoPE flash-attention backward (causal or full) for sm_100a: TMA -> shared memory -> in-place rotation of K
 // (once) and of every Q tile -> five tcgen05 MMAs per (K block, Q tile) pair with TMEM accumulators.
 // 16-bit inputs, D = 128, N % 128 == 0.
 //
@@ -105,8 +105,9 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int jb = within / heads_here;
     const int bh = chunk * kHeadChunk + within % heads_here;
     const int row_base = bh * N;
-    const int n_steps = (N - jb * kBK) / kBQ;
-    const int q_first = jb * kBK;                       // first query row this CTA visits
+    const bool causal = p.causal != 0;
+    const int q_first = causal ? jb * kBK : 0;          // first query row this CTA visits (causal: the block's own diagonal)
+    const int n_steps = (N - q_first) / kBQ;
 
     if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
         if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
@@ -352,7 +353,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const float* lse = sLD + st * 2 * kBQ;
             const float* dlt = lse + kBQ;
             const int q0 = q_first + s * kBQ;
-            const bool diag = q0 < jb * kBK + kBK;        // some keys of this block lie above the diagonal for these queries
+            const bool diag = causal && q0 < jb * kBK + kBK;   // some keys of this block lie above the diagonal for these queries
             {
                 const int c = wg;   // this group's 32 query columns
                 uint32_t rs[32], rd[32];
@@ -562,7 +563,8 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
 
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal) {
     (void)B; (void)H;
-    return causal && D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % kBK == 0;
+    (void)causal;
+    return D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % kBK == 0;
 }
 
 int launch_rope_bwd_tc(const RopeParams& p, int dtype, cudaStream_t s) {

@@ -1,4 +1,4 @@
-// Fused-RoPE causal flash-attention forward for sm_100a: TMA -> shared memory -> in-place rotation ->
+// Fused-RoPE flash-attention forward (causal or full) for sm_100a: TMA -> shared memory -> in-place rotation ->
 // tcgen05 MMAs with TMEM accumulators -> online softmax in registers.  16-bit inputs, D = 128.
 //
 // A work item is 256 consecutive query rows (two 128-row tiles, "Q0" and "Q1") of one (batch, head) with the K/V
@@ -156,6 +156,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int BH = p.B * p.H;
     const int n_qt = N / (2 * kBM);
     const int n_items = n_qt * BH;
+    // K tiles an item sees: up to its diagonal (causal: Q0 one tile less than Q1), or all of them
+    const bool causal = p.causal != 0;
+    const int nk_all = N / kBN;
     // Persistent CTAs with a dynamic schedule: the first item of CTA c is c, further ones come from a global counter
     // (heavy items first, so the greedy order balances to a few percent; a static round-robin was 19 % off).  The K
     // producer fetches an item, publishes it in a small shared-memory ring and every other role reads it from there.
@@ -227,7 +230,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     mbar_arrive(&bars[ITEM_FULL + slot]);
                     if (w < 0) break;
                     const WorkItem wi = work_item(w, n_qt, BH);
-                    const int row_base = wi.bh * N, nk = 2 * wi.t + 2;
+                    const int row_base = wi.bh * N, nk = causal ? 2 * wi.t + 2 : nk_all;
                     for (int i = 0; i < 2; ++i) {
                         if (n > 0 && !(ok = mbar_wait(&bars[Q_EMPTY + i], (n - 1) & 1, p.status, Q_EMPTY, abort_flag))) break;
                         const int r = row_base + wi.t * 2 * kBM + i * kBM;
@@ -255,7 +258,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int w = fetch_item(bars, item_ring, n, lane, false, p.status, abort_flag);
                     if (w < 0) break;
                     const WorkItem wi = work_item(w, n_qt, BH);
-                    const int row_base = wi.bh * N, nk = 2 * wi.t + 2;
+                    const int row_base = wi.bh * N, nk = causal ? 2 * wi.t + 2 : nk_all;
                     for (int j = 0; j < nk; ++j, ++gv) {
                         const int r = row_base + j * kBN;
                         const int vs = gv % kVStages;
@@ -299,7 +302,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
                 if (w < 0) break;
                 const WorkItem wi = work_item(w, n_qt, BH);
-                const int nk = 2 * wi.t + 2, nk0 = nk - 1;
+                const int nk = causal ? 2 * wi.t + 2 : nk_all, nk0 = causal ? nk - 1 : nk;
                 // first K tile of the item: S0 = Q0 K^T, S1 = Q1 K^T
                 if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
                 if (!(ok = mbar_wait_warp(&bars[kReadyBar + gk % kKStages], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
@@ -367,7 +370,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
             if (w < 0) break;
             const WorkItem wi = work_item(w, n_qt, BH);
-            const int nk = 2 * wi.t + 2;
+            const int nk = causal ? 2 * wi.t + 2 : nk_all;
             for (int i = 0; i < 2 && ok; ++i) {
                 load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM + rg * kHalfRows) * (kD / 2), tid);
                 if (!(ok = mbar_wait_warp(&bars[Q_FULL + i], n & 1, p.status, Q_FULL, abort_flag))) break;
@@ -427,12 +430,12 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
             if (w < 0) break;
             const WorkItem wi = work_item(w, n_qt, BH);
-            const int nk_i = 2 * wi.t + 1 + wg;
+            const int nk_i = causal ? 2 * wi.t + 1 + wg : nk_all;
             float m = -INFINITY, l = 0.f;
             for (int j = 0; j < nk_i; ++j, ++gs) {
                 if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], gs & 1, p.status, S_FULL + wg, abort_flag))) break;
                 tc_fence_after();
-                const bool diag = (j == nk_i - 1);
+                const bool diag = causal && (j == nk_i - 1);
 #ifdef COROPE_KO_SMX
                 if (j > 0) { tc_fence_before(); mbar_arrive_warp(&bars[P_FULL + wg], lane); continue; }
 #endif
@@ -572,7 +575,8 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
 
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal) {
     (void)B; (void)H;
-    return causal && D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % (2 * kBM) == 0;
+    (void)causal;
+    return D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % (2 * kBM) == 0;
 }
 
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s) {

@@ -123,6 +123,27 @@ def test_fused_rope_tensor_core_backward(dtype, shape):
         assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128), (1, 2, 2048, 128)])
+def test_fused_rope_tensor_core_non_causal(dtype, shape):
+    # full (non-causal) attention on the tensor-core kernels: every Q tile sees every K tile, no mask
+    B, H, N, D = shape
+    q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=6)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, False, D ** -0.5, cos, sin)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    if N <= 1024:
+        ro = oracle.rope_attn_fwd(q, k, v, False, D ** -0.5, cos, sin)
+        refs = oracle.rope_attn_bwd(q, k, v, do, False, D ** -0.5, cos, sin)
+    else:
+        ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, False, D ** -0.5, cos, sin, rows=512)
+        refs = (rdq, rdk, rdv)
+    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), refs):
+        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+
+
 def test_fused_rope_llama7b_4k_heads_bf16():
     # two heads of the Llama-7B-4K configuration at full sequence length, forward and backward
     B, H, N, D = 1, 2, 4096, 128
