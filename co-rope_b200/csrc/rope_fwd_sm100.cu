@@ -154,11 +154,14 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
     const int BH = p.B * p.H;
-    const int n_qt = N / (2 * kBM);
+    // N is a multiple of 128: when it is not a multiple of 256 the last item of a head has only Q0; its Q1 tile (and, causal,
+    // the K tile behind the diagonal) lies beyond the head -- TMA fetches whatever is there (the next head's rows, zeros
+    // behind the tensor), the results are finite and are not stored
+    const int n_qt = (N + 2 * kBM - 1) / (2 * kBM);
     const int n_items = n_qt * BH;
     // K tiles an item sees: up to its diagonal (causal: Q0 one tile less than Q1), or all of them
     const bool causal = p.causal != 0;
-    const int nk_all = N / kBN;
+    const int nk_all = N / kBN;   // full attention: every tile that lies inside the head
     // Persistent CTAs with a dynamic schedule: the first item of CTA c is c, further ones come from a global counter
     // (heavy items first, so the greedy order balances to a few percent; a static round-robin was 19 % off).  The K
     // producer fetches an item, publishes it in a small shared-memory ring and every other role reads it from there.
@@ -523,6 +526,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             if (!(ok = mbar_wait_warp(&bars[O_FULL + wg], (gs - 1) & 1, p.status, O_FULL + wg, abort_flag))) break;
             tc_fence_after();
             const float inv = 1.f / l_tot;
+            const bool in_head = (2 * wi.t + wg) * kBM < N;   // false for the Q1 tile of a head's last, half-empty item
             const size_t grow = (size_t)wi.bh * N + (size_t)(2 * wi.t + wg) * kBM + row;
             T* orow = reinterpret_cast<T*>(p.out_o) + grow * kD + half * 64;
 #pragma unroll
@@ -534,12 +538,14 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pk[i] = pack2<T>(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
                 uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                if (in_head) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                    for (int i = 0; i < 4; ++i) dst[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+                }
             }
             tc_fence_before();
             mbar_arrive_warp(&bars[O_FREE + wg], lane);
-            if (half == 0) p.lse2[grow] = m + log2f(l_tot);
+            if (half == 0 && in_head) p.lse2[grow] = m + log2f(l_tot);
         }
         tc_fence_before();
     }
@@ -562,7 +568,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     auto kern = rope_fwd_sm100_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    const unsigned items = (unsigned)((p.N / (2 * kBM)) * p.B * p.H);
+    const unsigned items = (unsigned)(((p.N + 2 * kBM - 1) / (2 * kBM)) * p.B * p.H);
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
@@ -576,7 +582,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal) {
     (void)B; (void)H;
     (void)causal;
-    return D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % (2 * kBM) == 0;
+    return D == kD && (dtype == COROPE_DTYPE_BF16 || dtype == COROPE_DTYPE_F16) && N % kBM == 0;
 }
 
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s) {

@@ -98,7 +98,7 @@ def test_fused_rope_reference_verification_cases_fp16(shape, causal):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128)])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128), (1, 2, 128, 128), (2, 3, 640, 128)])
 def test_fused_rope_tensor_core_forward(dtype, shape):
     B, H, N, D = shape
     q, k, v, _ = rope_inputs(B, H, N, D, dtype, seed=3)
@@ -116,6 +116,7 @@ def test_fused_rope_tensor_core_backward(dtype, shape):
     q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=5)
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
     o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
     ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
     assert excess(o, ro, TOL_FWD_16, dtype) <= 0
@@ -124,7 +125,7 @@ def test_fused_rope_tensor_core_backward(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128), (1, 2, 2048, 128)])
+@pytest.mark.parametrize("shape", [(1, 2, 256, 128), (2, 3, 1024, 128), (1, 2, 2048, 128), (2, 2, 384, 128)])
 def test_fused_rope_tensor_core_non_causal(dtype, shape):
     # full (non-causal) attention on the tensor-core kernels: every Q tile sees every K tile, no mask
     B, H, N, D = shape
