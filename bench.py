@@ -182,8 +182,57 @@ def run_reference_arm(args, wl, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# The 19 causal shapes of the reference's own comparison script (fused-rope/bench_compare.py:323-350): (B, H, N, D, name).
+SWEEP_SHAPES = [
+    (4, 8, 512, 64, "Small-512"), (4, 8, 1024, 64, "Small-1K"), (2, 8, 2048, 64, "Small-2K"), (2, 8, 4096, 64, "Small-4K"),
+    (1, 8, 8192, 64, "Small-8K"),
+    (4, 32, 512, 128, "Llama7B-512"), (4, 32, 1024, 128, "Llama7B-1K"), (2, 32, 2048, 128, "Llama7B-2K"), (2, 32, 4096, 128, "Llama7B-4K"),
+    (1, 32, 8192, 128, "Llama7B-8K"), (1, 32, 16384, 128, "Llama7B-16K"),
+    (2, 64, 512, 128, "Llama70B-512"), (2, 64, 1024, 128, "Llama70B-1K"), (1, 64, 2048, 128, "Llama70B-2K"), (1, 64, 4096, 128, "Llama70B-4K"),
+    (1, 32, 8192, 128, "Llama70B-8K"),
+    (1, 16, 32768, 128, "Long-32K"), (1, 8, 65536, 128, "Long-64K"), (1, 4, 131072, 128, "Long-128K"),
+]
+
+
+def run_sweep(args):
+    """Forward / backward time and causal-adjusted TFLOP/s for the reference's shape list, one markdown row per shape
+    (same FLOP convention as its report: 4 B H N^2 D / 2 forward, 2.5x that backward).  fp16 like the reference's run."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pkg = importlib.import_module("co-rope_b200")
+    import oracle
+    print("| configuration (B, H, N, D) | forward | backward | kernels |")
+    print("|---|---|---|---|")
+    for B, H, N, D, name in SWEEP_SHAPES:
+        q, k, v, do = (t.to(dev) for t in make_inputs("rope", B, H, H, N, D, torch.float16, 7, dev))
+        cos, sin = oracle.precompute_freqs_cis(D, N, THETA)
+        cos, sin = cos[:, : D // 2].contiguous().to(dev), sin[:, : D // 2].contiguous().to(dev)
+        reps = max(3, min(args.steps, 20))
+        f_ms, b_ms = [], []
+        for it in range(3 + reps):
+            qq, kk, vv = (t.detach().requires_grad_(True) for t in (q, k, v))
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            e[0].record()
+            o = pkg.fused_rope_attention(qq, kk, vv, True, 0.5, cos, sin)
+            e[1].record()
+            torch.autograd.grad(o, (qq, kk, vv), do)
+            e[2].record()
+            torch.cuda.synchronize()
+            if it >= 3:
+                f_ms.append(e[0].elapsed_time(e[1]))
+                b_ms.append(e[1].elapsed_time(e[2]))
+        pkg.check_status()
+        F = flops_fwd(B, H, N, D)
+        f, b = sorted(f_ms)[len(f_ms) // 2], sorted(b_ms)[len(b_ms) // 2]
+        fam = "tcgen05" if pkg._ext.lib().corope_last_kernel_family(0) == 1 else "cuda-core fp32"
+        print("| %s (%d, %d, %d, %d) | %.3f ms (%.1f TFLOP/s) | %.3f ms (%.1f TFLOP/s) | %s |"
+              % (name, B, H, N, D, f, F / f / 1e9, b, 2.5 * F / b / 1e9, fam), flush=True)
+        del q, k, v, do
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--sweep", action="store_true", help="time the reference's 19 benchmark shapes (forward / backward) and print a table")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
@@ -204,6 +253,10 @@ def main():
 
     if args.impl == "reference":
         run_reference_arm(args, wl, rank, world)
+        return
+    if args.sweep:
+        if rank == 0:
+            run_sweep(args)
         return
 
     import torch.distributed as dist
