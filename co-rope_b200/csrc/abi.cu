@@ -15,22 +15,36 @@ constexpr size_t kAlign = 256;
 bool head_dim_ok(int D) { return D == 32 || D == 64 || D == 128; }
 
 struct RopeWorkspace {
-    size_t packed_tab, rot, delta, dq_acc, total;
+    size_t packed_tab, rot, delta, dq_acc, pad[5], total;
 };
+
+// 16-bit problems with D = 64 and N % 128 == 0 run zero-padded to D = 128 on the tensor-core kernels (half of the MMA work
+// is on zeros, which still is an order of magnitude faster than the CUDA-core kernels); the workspace then also holds the
+// padded copies.
+bool rope_d64_padded(int N, int D, int dtype) { return D == 64 && dtype != COROPE_DTYPE_F32 && N % 128 == 0; }
 
 RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dtype) {
     RopeWorkspace w{};
+    const bool padded = rope_d64_padded(N, D, dtype);
+    const int Dk = padded ? 128 : D;                 // head dimension the kernels see
+    const bool tc = dtype != COROPE_DTYPE_F32 && Dk == 128;
+    const size_t elems = (size_t)B * H * N * Dk;
     size_t off = 0;
     w.packed_tab = off;
-    off += align_up((size_t)N * (D / 2) * sizeof(uint32_t) + 64, kAlign);   // + the work counter behind the table
+    off += align_up((size_t)N * (Dk / 2) * sizeof(uint32_t) + 64, kAlign);   // + the work counter behind the table
     w.rot = off;   // tensor-core kernels: fp16 copy of the rotated K (forward) / rotated and scaled Q (backward)
-    if (dtype != COROPE_DTYPE_F32 && D == 128) off += align_up((size_t)B * H * N * D * 2, kAlign);
+    if (tc) off += align_up(elems * 2, kAlign);
     if (bwd) {
         w.delta = off;
         off += align_up((size_t)B * H * N * sizeof(float), kAlign);
         w.dq_acc = off;
-        if (dtype != COROPE_DTYPE_F32 && D == 128) off += align_up((size_t)B * H * N * D * sizeof(float), kAlign);
+        if (tc) off += align_up(elems * sizeof(float), kAlign);
     }
+    if (padded)   // forward: q, v, o (+ k before its rotation shares o's buffer); backward: k, v, dO / dq, dk (+ q before its rotation), dv
+        for (int i = 0; i < (bwd ? 5 : 3); ++i) {
+            w.pad[i] = off;
+            off += align_up(elems * 2, kAlign);
+        }
     w.total = off < kAlign ? kAlign : off;
     return w;
 }
@@ -142,6 +156,27 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
     COROPE_SET_PROF(p);
+    if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
+        // D = 64: zero-padded copies of q, k, v in the layout that keeps the rotation pairs together, the D = 128 kernels, o back
+        const size_t rows = (size_t)B * H * N;
+        uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
+        void* k_rot = (char*)workspace + w.rot;
+        void* qp = (char*)workspace + w.pad[0];
+        void* vp = (char*)workspace + w.pad[1];
+        void* op = (char*)workspace + w.pad[2];   // first the padded k (until it is rotated), then the padded output
+        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, 64, s, 32)) return e;
+        if (int e = launch_pad_d64(q, qp, rows, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, op, rows, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, vp, rows, 0, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(op, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
+        p.q = qp; p.k = op; p.v = vp; p.out_o = op; p.D = 128;
+        p.packed_tab = tab;
+        p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);
+        p.k_rot = k_rot;
+        g_last_family[COROPE_OP_ROPE_FWD] = 1;
+        if (int e = launch_rope_fwd_tc(p, dtype, s)) return e;
+        return launch_unpad_d64(op, o, rows, 0, dtype, s);
+    }
     if (g_policy.load() == 0 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
@@ -173,6 +208,31 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
     COROPE_SET_PROF(p);
     if (int e = launch_rope_delta(p, dtype, s)) return e;
+    if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
+        const size_t rows = (size_t)B * H * N;
+        uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
+        void* q_rot = (char*)workspace + w.rot;
+        void* kp = (char*)workspace + w.pad[0];
+        void* vp = (char*)workspace + w.pad[1];
+        void* dop = (char*)workspace + w.pad[2];   // padded dO; after the main kernel the padded dq (the finalize kernel writes it)
+        void* dkp = (char*)workspace + w.pad[3];   // first the padded q (until it is rotated), then the padded dk
+        void* dvp = (char*)workspace + w.pad[4];
+        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, 64, s, 32)) return e;
+        if (int e = launch_pad_d64(q, dkp, rows, 1, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(dkp, q_rot, tab, B, H, N, sm_scale * kLog2e, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, kp, rows, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, vp, rows, 0, dtype, s)) return e;
+        if (int e = launch_pad_d64(d_o, dop, rows, 0, dtype, s)) return e;
+        p.q = dkp; p.k = kp; p.v = vp; p.d_o = dop; p.dq = dop; p.dk = dkp; p.dv = dvp; p.D = 128;
+        p.packed_tab = tab;
+        p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
+        p.q_rot = q_rot;
+        g_last_family[COROPE_OP_ROPE_BWD] = 1;
+        if (int e = launch_rope_bwd_tc(p, dtype, s)) return e;
+        if (int e = launch_unpad_d64(dop, dq, rows, 1, dtype, s)) return e;
+        if (int e = launch_unpad_d64(dkp, dk, rows, 1, dtype, s)) return e;
+        return launch_unpad_d64(dvp, dv, rows, 0, dtype, s);
+    }
     if (g_policy.load() == 0 && rope_bwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;

@@ -523,7 +523,9 @@ void count_launch(int n = 1);
 int launch_rope_fwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s);
-int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s);
+int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src = -1);
+int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
+int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
 int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
                           cudaStream_t s);
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);

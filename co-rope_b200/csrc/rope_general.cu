@@ -366,13 +366,45 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
 
 // cos/sin fp32 tables -> compact [N][D/2] table of (cos, sin) pairs in 16-bit offset-binary fixed point
 // (see pack_unorm_pair): half the bytes of the fp32 tables with an absolute error of 1.5e-5.
+// half_src < half_d: the caller's tables have half_src columns; the pairs beyond them get the identity rotation (used when
+// a D = 64 problem is run zero-padded on the D = 128 kernels).
 __global__ void pack_tables_kernel(const float* __restrict__ cosT, const float* __restrict__ sinT, int64_t ts, uint32_t* __restrict__ out,
-                                   int N, int half_d) {
+                                   int N, int half_d, int half_src) {
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx == 0) out[(size_t)N * half_d] = 0u;   // the word after the table: work counter of the persistent forward kernel
     if (idx >= (size_t)N * half_d) return;
     int n = (int)(idx / half_d), d = (int)(idx % half_d);
-    out[idx] = pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]);
+    out[idx] = d < half_src ? pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]) : pack_unorm_pair(1.f, 0.f);
+}
+
+// D = 64 <-> D = 128 with zero padding, 16-byte chunks.  "rope" layout keeps the half-layout pairs together for the
+// D = 128 kernels: first half of the row (32 columns) to columns 0..31, second half to columns 64..95; "plain" layout
+// puts the 64 columns first.  Everything else is zero, so dot products and rotations are unchanged.
+template <typename T>
+__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16 output chunks
+    if (idx >= rows * 16) return;
+    const size_t r = idx >> 4;
+    const int c = (int)(idx & 15);
+    int src = -1;
+    if (rope_layout) {
+        if (c < 4) src = c;
+        else if (c >= 8 && c < 12) src = c - 4;
+    } else if (c < 8) {
+        src = c;
+    }
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + r * 64 + src * 8);
+    *reinterpret_cast<uint4*>(out + r * 128 + c * 8) = v;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 8 output chunks
+    if (idx >= rows * 8) return;
+    const size_t r = idx >> 3;
+    const int c = (int)(idx & 7);
+    const int src = rope_layout ? (c < 4 ? c : c + 4) : c;
+    *reinterpret_cast<uint4*>(out + r * 64 + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
 }
 
 // Rotation as a pass of its own, for the tensor-core kernels at D = 128: out[r, :] = rot(x[r, :]) * scale as fp16, with the
@@ -502,9 +534,30 @@ int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, 
     return (int)cudaGetLastError();
 }
 
-int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s) {
+int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src) {
     size_t n = (size_t)N * half_d;
-    pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d); count_launch();
+    pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d, half_src < 0 ? half_d : half_src);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s) {
+    const unsigned grid = (unsigned)((rows * 16 + 255) / 256);
+    if (dtype == COROPE_DTYPE_BF16)
+        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout);
+    else
+        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s) {
+    const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
+    if (dtype == COROPE_DTYPE_BF16)
+        unpad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)xp, (__nv_bfloat16*)out, rows, rope_layout);
+    else
+        unpad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)xp, (__half*)out, rows, rope_layout);
+    count_launch();
     return (int)cudaGetLastError();
 }
 

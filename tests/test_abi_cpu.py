@@ -43,7 +43,10 @@ def test_host_only_entry_points():
     fwd32 = L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 128, 0)
     assert fwd16 - fwd32 == 2 * elems and fwd32 < 4096 * 64 * 4 + 1024
     assert nbytes >= 6 * elems                                                      # backward: fp16 Q copy + fp32 dQ accumulator
-    assert L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 64, 1) < 4096 * 32 * 4 + 1024   # D = 64: general kernels, no copy
+    # D = 64, 16-bit, N % 128 == 0 runs zero-padded to D = 128: rotated K + padded q, v, o (four padded tensors); other D = 64 cases need only the table
+    assert L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 64, 1) >= 4 * elems * 2
+    assert L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4000, 64, 1) < 4000 * 32 * 4 + 1024
+    assert L.corope_workspace_bytes(ext.OP_ROPE_FWD, 2, 32, 32, 4096, 64, 0) < 4096 * 32 * 4 + 1024
     # Co-RoPE: fp16 copies of K and V for the tensor-core kernels (16-bit, D = 128, N % 64 == 0), none otherwise
     kv = 2 * 8 * 2048 * 128
     assert L.corope_workspace_bytes(ext.OP_GQA_FWD, 2, 32, 8, 2048, 128, 1) == 4 * kv

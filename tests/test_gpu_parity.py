@@ -145,6 +145,22 @@ def test_fused_rope_tensor_core_non_causal(dtype, shape):
         assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape,causal", [((2, 3, 256, 64), True), ((1, 2, 1024, 64), True), ((2, 2, 384, 64), False)])
+def test_fused_rope_head_dim_64_on_tensor_cores(dtype, shape, causal):
+    # D = 64 with N % 128 == 0 runs zero-padded to D = 128 on the tensor-core kernels
+    B, H, N, D = shape
+    q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=8)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, causal, D ** -0.5, cos, sin)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    ro = oracle.rope_attn_fwd(q, k, v, causal, D ** -0.5, cos, sin)
+    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, causal, D ** -0.5, cos, sin)):
+        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+
+
 def test_fused_rope_llama7b_4k_heads_bf16():
     # two heads of the Llama-7B-4K configuration at full sequence length, forward and backward
     B, H, N, D = 1, 2, 4096, 128
