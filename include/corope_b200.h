@@ -59,7 +59,9 @@ const char* corope_status_string(int status);
 /* Bytes of caller-provided scratch (device memory, 256-byte aligned) an op needs.  Contents
  * need not be initialised by the caller.  For MHA pass Hkv == Hq.  For 16-bit inputs at D = 128 the
  * fused-RoPE ops keep a rotated fp16 copy of K (forward) or Q (backward) there, so the size grows
- * with B*H*N*D (forward: 2 bytes per element of k; backward: 6 bytes per element of q). */
+ * with B*H*N*D (forward: 2 bytes per element of k; backward: 6 bytes per element of q).  16-bit
+ * inputs at D = 64 with N % 128 == 0 are run zero-padded to D = 128 and also keep their padded copies
+ * there (forward: 16 bytes per element of q; backward: 32).  Always ask this function. */
 size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int dtype);
 
 /*
