@@ -225,6 +225,7 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         if (int e = launch_pad_d64(d_o, dop, rows, 0, dtype, s)) return e;
         p.q = dkp; p.k = kp; p.v = vp; p.d_o = dop; p.dq = dop; p.dk = dkp; p.dv = dvp; p.D = 128;
         p.packed_tab = tab;
+        p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
         p.q_rot = q_rot;
         g_last_family[COROPE_OP_ROPE_BWD] = 1;
@@ -237,6 +238,7 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
+        p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
         void* q_rot = (char*)workspace + w.rot;
         if (int e = launch_rope_prerotate(q, q_rot, tab, B, H, N, sm_scale * kLog2e, dtype, s)) return e;

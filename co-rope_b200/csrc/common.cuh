@@ -60,7 +60,7 @@ struct RopeParams {
     int causal;
     float sm_scale;
     int* status;
-    int* sched_counter; // zeroed word in the workspace: next work item of the persistent forward kernel
+    int* sched_counter; // zeroed word in the workspace: next work item / unit of the persistent tensor-core kernels
     const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
     const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
     long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise

@@ -2,8 +2,13 @@
 // (once) and of every Q tile -> five tcgen05 MMAs per (K block, Q tile) pair with TMEM accumulators.
 // 16-bit inputs, D = 128, N % 128 == 0.
 //
-// One CTA owns one K/V block of 128 keys of one (batch, head) and sweeps the query tiles (64 rows each) at or
-// below the diagonal.  Per step, with everything transposed so that thread = key row:
+// Work unit = one K/V block of 128 keys of one (batch, head): the CTA sweeps the query tiles (64 rows each) at or
+// below the block's diagonal.  CTAs are persistent (one per SM) and take units from a global counter, the first unit
+// of CTA c being c; every role walks the same unit sequence and keeps a running step count, from which ring stages
+// and mbarrier parities follow, so the rings run on across units: Q / dO tiles of the next unit are requested while
+// the last steps of the current one compute, its K / V block as soon as the last MMA of the current one has completed,
+// and that block lands and is rotated while the softmax groups write dV / dK of the current one.
+// Per step, with everything transposed so that thread = key row:
 //     S^T  = K~ Q~^T                      [128 keys x 64 queries]   (Q~ carries sm_scale*log2e)
 //     dP^T = V dO^T                       [128 x 64]
 //     P^T  = exp2(S^T - lse2_i),  dS^T = P^T o (dP^T - delta_i)     (CUDA cores)
@@ -52,6 +57,8 @@ constexpr int kLaunchRegs = 80;
 constexpr int kRegsCtl = 48, kRegsRot = 72, kRegsSmx = 104, kRegsDrain = 80;
 static_assert(128 * (kRegsCtl + 2 * kRegsRot + 2 * kRegsSmx + kRegsDrain) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 4;
+constexpr int kUnitSlots = 4;
+constexpr int kUnitReaders = 1 + 8 + 8 + 4;   // MMA warp, rotation warps, softmax warps, drain warps: one arrival each
 
 enum Bar {
     K_FULL = 0, V_FULL, K_ROT,
@@ -64,8 +71,36 @@ enum Bar {
     DQ_EMPTY = DQ_FULL + 2,
     ACC_FULL = DQ_EMPTY + 2,
     DQ_DONE,                             // + buffer: dQ~^T of the step is in TMEM
-    NUM_BARS = DQ_DONE + 2
+    UNIT_FULL = DQ_DONE + 2,             // + slot: a unit index has been published in the unit ring
+    UNIT_EMPTY = UNIT_FULL + kUnitSlots, // + slot: every role has read it
+    NUM_BARS = UNIT_EMPTY + kUnitSlots
 };
+
+// Unit order: heads in chunks of kHeadChunk (the CTAs at work at one time then share few heads, so their Q / dO tiles
+// and above all the fp32 dQ accumulator rows stay in L2); within a chunk low key blocks first, since they sweep the
+// most query tiles.
+struct Unit {
+    int jb, bh;
+};
+__device__ __forceinline__ Unit unit_of(int w, int n_kb, int BH) {
+    const int chunk_units = kHeadChunk * n_kb;
+    const int chunk = w / chunk_units, within = w % chunk_units;
+    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
+    Unit u;
+    u.jb = within / heads_here;
+    u.bh = chunk * kHeadChunk + within % heads_here;
+    return u;
+}
+
+// Consumer side of the unit ring: the n-th unit of this CTA, or -1 when there is none left (or a wait gave up).
+// Called by all 32 lanes of a warp; one arrival per warp.
+__device__ __forceinline__ int fetch_unit(uint64_t* bars, volatile int* unit_ring, int n, int lane, int* status, volatile int* abort_flag) {
+    const int slot = n % kUnitSlots;
+    if (!mbar_wait_warp(&bars[UNIT_FULL + slot], (n / kUnitSlots) & 1, status, UNIT_FULL, abort_flag)) return -1;
+    const int w = unit_ring[slot];
+    mbar_arrive_warp(&bars[UNIT_EMPTY + slot], lane);
+    return w;
+}
 
 constexpr size_t kSmemData = 2 * kKVBytes + kStages * 2 * kQBytes + 2 * kDsBytes + kDqBytes + kStages * 2 * kBQ * sizeof(float);
 constexpr size_t kSmemSlack = 512;       // room to round the dynamic shared memory base up to 1024 bytes (checked at run time)
@@ -91,23 +126,16 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     uint64_t* bars = reinterpret_cast<uint64_t*>(sLD + kStages * 2 * kBQ);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* unit_ring = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [kUnitSlots]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
     const int BH = p.B * p.H;
-    // CTA order: heads in chunks of kHeadChunk (the CTAs resident at one time then share few heads, so their
-    // Q / dO tiles and above all the fp32 dQ accumulator rows stay in L2); within a chunk low key blocks first,
-    // since they sweep the most query tiles
     const int n_kb = N / kBK;
-    const int chunk_ctas = kHeadChunk * n_kb;
-    const int chunk = (int)blockIdx.x / chunk_ctas, within = (int)blockIdx.x % chunk_ctas;
-    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
-    const int jb = within / heads_here;
-    const int bh = chunk * kHeadChunk + within % heads_here;
-    const int row_base = bh * N;
+    const int n_units = BH * n_kb;
     const bool causal = p.causal != 0;
-    const int q_first = causal ? jb * kBK : 0;          // first query row this CTA visits (causal: the block's own diagonal)
-    const int n_steps = (N - q_first) / kBQ;
+    // per unit (jb, bh): first query row visited q_first = causal ? jb * kBK : 0 (causal: the block's own diagonal) and
+    // n_steps = (N - q_first) / kBQ, which is even, so the two-buffer indices of a unit's first step are always 0
 
     if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
         if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
@@ -134,6 +162,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             mbar_init(&bars[DQ_DONE + b], 1);
         }
         mbar_init(&bars[ACC_FULL], 1);
+        for (int i = 0; i < kUnitSlots; ++i) {
+            mbar_init(&bars[UNIT_FULL + i], 1);
+            mbar_init(&bars[UNIT_EMPTY + i], kUnitReaders);
+        }
         fence_mbar_init();
         tma_prefetch_desc(&mapQ);
         tma_prefetch_desc(&mapK);
@@ -157,24 +189,47 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         // ------------------------------------------------------------------ TMA producer
         reg_dealloc<kRegsCtl>();
         if (lane == 0) {
-            const int kr = row_base + jb * kBK;
-            mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
-            tma_load_2d(sK, &mapK, 0, kr, &bars[K_FULL]);
-            tma_load_2d(sK + kKVBox, &mapK, 64, kr, &bars[K_FULL]);
-            mbar_arrive_expect_tx(&bars[V_FULL], kKVBytes);
-            tma_load_2d(sV, &mapV, 0, kr, &bars[V_FULL]);
-            tma_load_2d(sV + kKVBox, &mapV, 64, kr, &bars[V_FULL]);
-            for (int s = 0; s < n_steps; ++s) {
-                const int st = s % kStages;
-                if (s >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((s / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) break;
-                const int qr = row_base + q_first + s * kBQ;
-                mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
-                tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
-                tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
-                tma_load_2d(sDO + st * kQBytes, &mapDO, 0, qr, &bars[QDO_FULL + st]);
-                tma_load_2d(sDO + st * kQBytes + kQBox, &mapDO, 64, qr, &bars[QDO_FULL + st]);
-                bulk_load_1d(sLD + st * 2 * kBQ, p.lse2 + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
-                bulk_load_1d(sLD + st * 2 * kBQ + kBQ, p.delta + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
+            int g = 0;                   // steps before this unit
+            bool ok = true;
+            for (int n = 0; ok; ++n) {
+                const int slot = n % kUnitSlots;
+                if (n >= kUnitSlots && !(ok = mbar_wait(&bars[UNIT_EMPTY + slot], ((n / kUnitSlots) - 1) & 1, p.status, UNIT_EMPTY, abort_flag))) break;
+                int w = n == 0 ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.sched_counter, 1);
+                if (w >= n_units) w = -1;
+                unit_ring[slot] = w;
+                mbar_arrive(&bars[UNIT_FULL + slot]);
+                if (w < 0) break;
+                const Unit un = unit_of(w, n_kb, BH);
+                const int row_base = un.bh * N;
+                const int q_first = causal ? un.jb * kBK : 0;
+                const int n_steps = (N - q_first) / kBQ;
+                auto load_step = [&](int s) -> bool {
+                    const int gs = g + s, st = gs % kStages;
+                    if (gs >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((gs / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) return false;
+                    const int qr = row_base + q_first + s * kBQ;
+                    mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
+                    tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
+                    tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
+                    tma_load_2d(sDO + st * kQBytes, &mapDO, 0, qr, &bars[QDO_FULL + st]);
+                    tma_load_2d(sDO + st * kQBytes + kQBox, &mapDO, 64, qr, &bars[QDO_FULL + st]);
+                    bulk_load_1d(sLD + st * 2 * kBQ, p.lse2 + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
+                    bulk_load_1d(sLD + st * 2 * kBQ + kBQ, p.delta + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
+                    return true;
+                };
+                // the first two Q / dO tiles only need ring stages, which the last steps of the previous unit free: ask
+                // for them before waiting for that unit's last MMA (n_steps >= 2)
+                if (!(ok = load_step(0) && load_step(1))) break;
+                // K and V are read by MMAs up to the previous unit's last step
+                if (n > 0 && !(ok = mbar_wait(&bars[ACC_FULL], (n - 1) & 1, p.status, ACC_FULL, abort_flag))) break;
+                const int kr = row_base + un.jb * kBK;
+                mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
+                tma_load_2d(sK, &mapK, 0, kr, &bars[K_FULL]);
+                tma_load_2d(sK + kKVBox, &mapK, 64, kr, &bars[K_FULL]);
+                mbar_arrive_expect_tx(&bars[V_FULL], kKVBytes);
+                tma_load_2d(sV, &mapV, 0, kr, &bars[V_FULL]);
+                tma_load_2d(sV + kKVBox, &mapV, 64, kr, &bars[V_FULL]);
+                for (int s = 2; ok && s < n_steps; ++s) ok = load_step(s);
+                g += n_steps;
             }
         }
         __syncwarp();
@@ -226,62 +281,52 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
                     if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
             };
-            bool ok = mbar_wait_warp(&bars[K_ROT], 0, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], 0, p.status, V_FULL, abort_flag) &&
-                      mbar_wait_warp(&bars[Q_ROT + 0], 0, p.status, Q_ROT, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                issue_st(0, 0);
-                issue_dp(0, 0);
-                if (leader) umma_commit(&bars[ST_FULL + 0]);
-            }
-#ifdef COROPE_PROFILE
-            long long pw[5] = {0, 0, 0, 0, 0}, pt;
-            const long long pstart = clock64();
-#define PROF_T0 pt = clock64()
-#define PROF_ACC(i) pw[i] += clock64() - pt
-#else
-#define PROF_T0
-#define PROF_ACC(i)
-#endif
-            for (int s = 0; ok && s < n_steps; ++s) {
-                const int b = s & 1;
-                if (s + 1 < n_steps) {
-                    const int st1 = (s + 1) % kStages, b1 = (s + 1) & 1;
-                    PROF_T0;
-                    if (!mbar_wait_warp(&bars[Q_ROT + st1], ((s + 1) / kStages) & 1, p.status, Q_ROT, abort_flag)) break;
-                    PROF_ACC(0);
+            int g = 0;                   // steps before this unit
+            bool ok = true;
+            for (int n = 0; ok; ++n) {
+                const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
+                if (w < 0) break;
+                const Unit un = unit_of(w, n_kb, BH);
+                const int n_steps = (N - (causal ? un.jb * kBK : 0)) / kBQ;
+                {
+                    const int st0 = g % kStages, b0 = g & 1;
+                    ok = mbar_wait_warp(&bars[K_ROT], n & 1, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], n & 1, p.status, V_FULL, abort_flag) &&
+                         mbar_wait_warp(&bars[Q_ROT + st0], (g / kStages) & 1, p.status, Q_ROT, abort_flag);
+                    if (!ok) break;
                     tc_fence_after();
-                    PROF_T0;
-                    issue_st(st1, b1);       // S^T first: it does not need the dQ~^T buffer, so it runs while that drains
-                    PROF_ACC(3);
-                    PROF_T0;
-                    if (s + 1 >= 2 && !mbar_wait_warp(&bars[DQ_EMPTY + b1], (((s + 1) >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag)) break;
-                    PROF_ACC(1);
+                    issue_st(st0, b0);
+                    // the dQ~^T of two steps ago (previous unit) has left this buffer
+                    if (g >= 2 && !(ok = mbar_wait_warp(&bars[DQ_EMPTY + b0], ((g >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag))) break;
                     tc_fence_after();
-                    PROF_T0;
-                    issue_dp(st1, b1);
-                    if (leader) umma_commit(&bars[ST_FULL + b1]);
-                    PROF_ACC(3);
+                    issue_dp(st0, b0);
+                    if (leader) umma_commit(&bars[ST_FULL + b0]);
                 }
-                PROF_T0;
-                if (!mbar_wait_warp(&bars[P_READY + b], (s >> 1) & 1, p.status, P_READY, abort_flag)) break;
-                PROF_ACC(2);
-                tc_fence_after();
-                PROF_T0;
-                issue_dq(b);                           // first, so that its drain starts as early as possible
-                if (leader) umma_commit(&bars[DQ_DONE + b]);
-                issue_dvdk(s % kStages, b, s > 0);
-                if (leader) umma_commit(&bars[DQ_FULL + b]);      // everything that reads dS^T / P^T of this buffer is done
-                if (leader) umma_commit(&bars[QDO_EMPTY + s % kStages]);
-                PROF_ACC(4);
+                for (int s = 0; s < n_steps; ++s) {
+                    const int gs = g + s, b = gs & 1;
+                    if (s + 1 < n_steps) {
+                        const int g1 = gs + 1, st1 = g1 % kStages, b1 = g1 & 1;
+                        if (!(ok = mbar_wait_warp(&bars[Q_ROT + st1], (g1 / kStages) & 1, p.status, Q_ROT, abort_flag))) break;
+                        tc_fence_after();
+                        issue_st(st1, b1);       // S^T first: it does not need the dQ~^T buffer, so it runs while that drains
+                        if (g1 >= 2 && !(ok = mbar_wait_warp(&bars[DQ_EMPTY + b1], ((g1 >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag))) break;
+                        tc_fence_after();
+                        issue_dp(st1, b1);
+                        if (leader) umma_commit(&bars[ST_FULL + b1]);
+                    }
+                    if (!(ok = mbar_wait_warp(&bars[P_READY + b], (gs >> 1) & 1, p.status, P_READY, abort_flag))) break;
+                    tc_fence_after();
+                    issue_dq(b);                           // first, so that its drain starts as early as possible
+                    if (leader) umma_commit(&bars[DQ_DONE + b]);
+                    // step 0 overwrites dV / dK~: the softmax groups have read the previous unit's out of TMEM before
+                    // they arrive on P_READY for this step
+                    issue_dvdk(gs % kStages, b, s > 0);
+                    if (leader) umma_commit(&bars[DQ_FULL + b]);      // everything that reads dS^T / P^T of this buffer is done
+                    if (leader) umma_commit(&bars[QDO_EMPTY + gs % kStages]);
+                }
+                if (!ok) break;
+                if (leader) umma_commit(&bars[ACC_FULL]);
+                g += n_steps;
             }
-            if (leader) umma_commit(&bars[ACC_FULL]);
-#ifdef COROPE_PROFILE
-            if (leader && p.prof && blockIdx.x < 64) {
-                long long* o = p.prof + blockIdx.x * 16;
-                o[0] = clock64() - pstart; o[1] = pw[0]; o[2] = pw[1]; o[3] = pw[2]; o[4] = pw[3]; o[5] = pw[4]; o[6] = n_steps;
-            }
-#endif
         }
         __syncwarp();
     } else if (warp < kRotWarp0) {
@@ -294,31 +339,36 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int rg = (warp - kRotWarp0) >> 2;
         const int tid = (threadIdx.x - kRotWarp0 * 32) & 127;
         constexpr int kQHalf = kBQ / 2;
-        bool ok;
-        {
-            TabRegs<kBQ> trk;
-            load_table_regs<kBQ>(trk, p.packed_tab + (size_t)(jb * kBK + rg * kBQ) * (kD / 2), tid);
-            ok = mbar_wait_warp(&bars[K_FULL], 0, p.status, K_FULL, abort_flag);
-            if (ok) {
+        const bool q_pre = p.q_rot != nullptr;   // Q tiles arrive rotated and scaled (pre-pass): only pass the barrier on
+        int g = 0;
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+            const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
+            if (w < 0) break;
+            const Unit un = unit_of(w, n_kb, BH);
+            const int q_first = causal ? un.jb * kBK : 0;
+            const int n_steps = (N - q_first) / kBQ;
+            {
+                TabRegs<kBQ> trk;
+                load_table_regs<kBQ>(trk, p.packed_tab + (size_t)(un.jb * kBK + rg * kBQ) * (kD / 2), tid);
+                if (!(ok = mbar_wait_warp(&bars[K_FULL], n & 1, p.status, K_FULL, abort_flag))) break;
                 rotate_tile_regs<T, kBQ, kKVBox, 2>(sK + rg * kBQ * 128, trk, tid, 1.0f);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT], lane);
             }
-        }
-        TabRegs<kQHalf> tr;
-        const bool q_pre = p.q_rot != nullptr;   // Q tiles arrive rotated and scaled (pre-pass): only pass the barrier on
-        if (!q_pre) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
-        for (int s = 0; ok && s < n_steps; ++s) {
-            const int st = s % kStages;
-            if (!mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag)) break;
-#ifndef COROPE_KO_ROT
-            if (!q_pre) {
-                rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
-                fence_proxy_async();
+            TabRegs<kQHalf> tr;
+            if (!q_pre) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
+            for (int s = 0; s < n_steps; ++s) {
+                const int gs = g + s, st = gs % kStages;
+                if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (gs / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
+                if (!q_pre) {
+                    rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
+                    fence_proxy_async();
+                }
+                mbar_arrive_warp(&bars[Q_ROT + st], lane);
+                if (!q_pre && s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
             }
-#endif
-            mbar_arrive_warp(&bars[Q_ROT + st], lane);
-            if (!q_pre && s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
+            g += n_steps;
         }
     } else if (warp < kDrainWarp0) {
         // ------------------------------------------------------------------ softmax groups (each takes half the query columns of every step)
@@ -327,29 +377,25 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int quad = warp & 3;
         const int row = quad * 32 + lane;                 // key row within the block
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-        const int key = jb * kBK + row;
+        int g = 0;
         bool ok = true;
-#ifdef COROPE_PROFILE
-        long long sw = 0, sc = 0, sl = 0, st0;
-#endif
+        for (int n = 0; ok; ++n) {
+        const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
+        if (w < 0) break;
+        const Unit un = unit_of(w, n_kb, BH);
+        const int jb = un.jb, row_base = un.bh * N;
+        const int q_first = causal ? jb * kBK : 0;
+        const int n_steps = (N - q_first) / kBQ;
+        const int key = jb * kBK + row;
         for (int s = 0; s < n_steps; ++s) {
-            const int u = s >> 1, st = s % kStages, b = s & 1;
+            const int gs = g + s, u = gs >> 1, st = gs % kStages, b = gs & 1;
             const uint32_t tS = tmem + lane_base + TS0 + b * 64;
             const uint32_t tD = tmem + lane_base + TD0 + b * 64;
             uint8_t* ds_row = sDS + b * kDsBytes + row * 128;
-#ifdef COROPE_PROFILE
-            st0 = clock64();
-#endif
             if (!(ok = mbar_wait_warp(&bars[ST_FULL + b], u & 1, p.status, ST_FULL + b, abort_flag))) break;
-            if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (s / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
+            if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (gs / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
             if (u > 0 && !(ok = mbar_wait_warp(&bars[DQ_FULL + b], (u - 1) & 1, p.status, DQ_FULL + b, abort_flag))) break;
-#ifdef COROPE_PROFILE
-            sw += clock64() - st0; st0 = clock64();
-#endif
             tc_fence_after();
-#ifdef COROPE_KO_SMX
-            if (s > 1) { fence_proxy_async(); tc_fence_before(); mbar_arrive_warp(&bars[P_READY + b], lane); continue; }
-#endif
             const float* lse = sLD + st * 2 * kBQ;
             const float* dlt = lse + kBQ;
             const int q0 = q_first + s * kBQ;
@@ -357,15 +403,9 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             {
                 const int c = wg;   // this group's 32 query columns
                 uint32_t rs[32], rd[32];
-#ifdef COROPE_PROFILE
-                const long long l0 = clock64();
-#endif
                 COROPE_TMEM_LD32(tS + c * 32, rs);
                 COROPE_TMEM_LD32(tD + c * 32, rd);
                 tmem_wait_ld();
-#ifdef COROPE_PROFILE
-                sl += clock64() - l0;
-#endif
                 uint32_t pp[16], dd[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -392,15 +432,9 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive_warp(&bars[P_READY + b], lane);
-#ifdef COROPE_PROFILE
-            sc += clock64() - st0;
-#endif
         }
-#ifdef COROPE_PROFILE
-        if (p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) { p.prof[blockIdx.x * 16 + 9 + wg * 2] = sw; p.prof[blockIdx.x * 16 + 10 + wg * 2] = sc; if (wg == 0) p.prof[blockIdx.x * 16 + 15] = sl; }
-#endif
         // epilogue: group 0 writes dV, group 1 writes dK (inverse rotation, * ln2 because Q~ carried log2e)
-        if (ok) ok = mbar_wait_warp(&bars[ACC_FULL], 0, p.status, ACC_FULL, abort_flag);
+        if (ok) ok = mbar_wait_warp(&bars[ACC_FULL], n & 1, p.status, ACC_FULL, abort_flag);
         if (ok) {
             tc_fence_after();
             const size_t grow = (size_t)row_base + key;
@@ -447,26 +481,26 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 }
             }
         }
-        tc_fence_before();
+        tc_fence_before();   // the TMEM reads above are ordered before this warp's next P_READY arrival, on which the next unit's first dV / dK~ MMA waits
+        g += n_steps;
+        }
     } else {
         // ------------------------------------------------------------------ dQ~^T drain: TMEM -> global fp32 reductions
         const int quad = warp & 3;
         const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-#ifdef COROPE_PROFILE
-        long long dw = 0, dc = 0, dt0;
-#endif
+        int g = 0;
+        bool ok = true;
+        for (int n = 0; ok; ++n) {
+        const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
+        if (w < 0) break;
+        const Unit un = unit_of(w, n_kb, BH);
+        const int row_base = un.bh * N;
+        const int q_first = causal ? un.jb * kBK : 0;
+        const int n_steps = (N - q_first) / kBQ;
         for (int s = 0; s < n_steps; ++s) {
-            const int b = s & 1;
-#ifdef COROPE_PROFILE
-            if (s > 0) dc += clock64() - dt0;
-            dt0 = clock64();
-#endif
-            if (!mbar_wait_warp(&bars[DQ_DONE + b], (s >> 1) & 1, p.status, DQ_DONE + b, abort_flag)) break;
-#ifdef COROPE_PROFILE
-            dw += clock64() - dt0; dt0 = clock64();
-            if (s == n_steps - 1 && p.prof && blockIdx.x < 64 && (threadIdx.x & 127) == 0) { p.prof[blockIdx.x * 16 + 13] = dw; p.prof[blockIdx.x * 16 + 14] = dc; }
-#endif
+            const int gs = g + s, b = gs & 1;
+            if (!(ok = mbar_wait_warp(&bars[DQ_DONE + b], (gs >> 1) & 1, p.status, DQ_DONE + b, abort_flag))) break;
             tc_fence_after();
             uint32_t r0[32], r1[32];
             COROPE_TMEM_LD32(tmem + lane_base + TD0 + b * 64, r0);
@@ -474,7 +508,6 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive_warp(&bars[DQ_EMPTY + b], lane);
-#ifndef COROPE_KO_DRAIN
             // stage the tile as [query][head dim] (lanes = consecutive head-dim indices: conflict-free), then one thread
             // adds it to the fp32 accumulator with a single bulk reduce instead of 8192 scalar reductions
             if (threadIdx.x == kDrainWarp0 * 32) bulk_wait_group_read0();   // the previous reduce has finished reading the tile
@@ -490,7 +523,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 tma_reduce_add_2d(&mapDQ, 0, row_base + q_first + s * kBQ, sDQ);
                 bulk_commit_group();
             }
-#endif
+        }
+        g += n_steps;
         }
         if (threadIdx.x == kDrainWarp0 * 32) bulk_wait_group0();   // all reduces have landed before the CTA exits
     }
@@ -549,7 +583,11 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     auto kern = rope_bwd_sm100_kernel<T>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
-    const unsigned grid = (unsigned)((p.N / kBK) * p.B * p.H);
+    int dev = 0, sms = 0;
+    if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+    const unsigned units = (unsigned)((p.N / kBK) * p.B * p.H);
+    const unsigned grid = units < (unsigned)sms ? units : (unsigned)sms;   // persistent: one CTA per SM
     kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, mdq, p); count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
