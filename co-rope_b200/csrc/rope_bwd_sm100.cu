@@ -244,12 +244,15 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             const uint32_t id_dv = make_idesc(kTFmt, kTFmt, 0, 1, kBK, kD);      // dV  : P^T (TMEM) x dO (MN-major)
             const uint32_t id_dk = make_idesc(0, 0, 0, 1, kBK, kD);              // dK~ : dS^T (K-major) x Q~ (MN-major)
             const uint32_t id_dq = make_idesc(0, 0, 1, 1, kD, kBQ);              // dQ~^T: K~ (MN-major) x dS^T (MN-major)
-            const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV), q_addr = smem_u32(sQ), do_addr = smem_u32(sDO),
-                           ds_addr = smem_u32(sDS);
             constexpr uint32_t kHi = sdesc_hi(1024);
-            const uint32_t k_lo = sdesc_lo(k_addr, 0), v_lo = sdesc_lo(v_addr, 0), q_lo = sdesc_lo(q_addr, 0), do_lo = sdesc_lo(do_addr, 0);
-            const uint32_t do_mn = sdesc_lo(do_addr, kQBox), q_mn = sdesc_lo(q_addr, kQBox), k_mn = sdesc_lo(k_addr, kKVBox);
-            const uint32_t ds_lo = sdesc_lo(ds_addr, 0);
+            // The buffers follow one another in shared memory (K | V | Q ring | dO ring | dS^T x 2) and the address field of
+            // a descriptor (address >> 4, 14 bits) cannot wrap below 256 KiB, so every descriptor is the one of K plus a
+            // constant: one live register instead of eight in this 48-register warp.
+            const uint32_t k_lo = sdesc_lo(smem_u32(sK), 0);
+            constexpr uint32_t kLboQ = (uint32_t)(kQBox >> 4) << 16, kLboKV = (uint32_t)(kKVBox >> 4) << 16;   // leading-dimension byte offset of the MN-major views
+            const uint32_t v_lo = k_lo + (kKVBytes >> 4), q_lo = k_lo + (2 * kKVBytes >> 4), do_lo = q_lo + (kStages * kQBytes >> 4);
+            const uint32_t ds_lo = do_lo + (kStages * kQBytes >> 4);
+            const uint32_t do_mn = do_lo + kLboQ, q_mn = q_lo + kLboQ, k_mn = k_lo + kLboKV;
             auto issue_st = [&](int st, int b) {      // S^T = K~ Q~^T
                 const uint32_t qb = q_lo + st * (kQBytes >> 4);
 #pragma unroll
@@ -281,6 +284,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
                     if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
             };
+            // Q tiles that arrive rotated (pre-pass) are ready as they land; otherwise the rotation groups pass them on
+            const int q_bar = p.q_rot != nullptr ? QDO_FULL : Q_ROT;
             int g = 0;                   // steps before this unit
             bool ok = true;
             for (int n = 0; ok; ++n) {
@@ -291,7 +296,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 {
                     const int st0 = g % kStages, b0 = g & 1;
                     ok = mbar_wait_warp(&bars[K_ROT], n & 1, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], n & 1, p.status, V_FULL, abort_flag) &&
-                         mbar_wait_warp(&bars[Q_ROT + st0], (g / kStages) & 1, p.status, Q_ROT, abort_flag);
+                         mbar_wait_warp(&bars[q_bar + st0], (g / kStages) & 1, p.status, Q_ROT, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
                     issue_st(st0, b0);
@@ -305,7 +310,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int gs = g + s, b = gs & 1;
                     if (s + 1 < n_steps) {
                         const int g1 = gs + 1, st1 = g1 % kStages, b1 = g1 & 1;
-                        if (!(ok = mbar_wait_warp(&bars[Q_ROT + st1], (g1 / kStages) & 1, p.status, Q_ROT, abort_flag))) break;
+                        if (!(ok = mbar_wait_warp(&bars[q_bar + st1], (g1 / kStages) & 1, p.status, Q_ROT, abort_flag))) break;
                         tc_fence_after();
                         issue_st(st1, b1);       // S^T first: it does not need the dQ~^T buffer, so it runs while that drains
                         if (g1 >= 2 && !(ok = mbar_wait_warp(&bars[DQ_EMPTY + b1], ((g1 >> 1) - 1) & 1, p.status, DQ_EMPTY, abort_flag))) break;
@@ -339,7 +344,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int rg = (warp - kRotWarp0) >> 2;
         const int tid = (threadIdx.x - kRotWarp0 * 32) & 127;
         constexpr int kQHalf = kBQ / 2;
-        const bool q_pre = p.q_rot != nullptr;   // Q tiles arrive rotated and scaled (pre-pass): only pass the barrier on
+        const bool q_pre = p.q_rot != nullptr;   // Q tiles arrive rotated and scaled (pre-pass): nothing to do per step
         int g = 0;
         bool ok = true;
         for (int n = 0; ok; ++n) {
@@ -356,17 +361,16 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[K_ROT], lane);
             }
+            if (q_pre) continue;
             TabRegs<kQHalf> tr;
-            if (!q_pre) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
+            load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + rg * kQHalf) * (kD / 2), tid);
             for (int s = 0; s < n_steps; ++s) {
                 const int gs = g + s, st = gs % kStages;
                 if (!(ok = mbar_wait_warp(&bars[QDO_FULL + st], (gs / kStages) & 1, p.status, QDO_FULL, abort_flag))) break;
-                if (!q_pre) {
-                    rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
-                    fence_proxy_async();
-                }
+                rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
+                fence_proxy_async();
                 mbar_arrive_warp(&bars[Q_ROT + st], lane);
-                if (!q_pre && s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
+                if (s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
             }
             g += n_steps;
         }
