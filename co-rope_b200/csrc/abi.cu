@@ -207,7 +207,9 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
     COROPE_SET_PROF(p);
-    if (int e = launch_rope_delta(p, dtype, s)) return e;
+    const bool tc_direct = g_policy.load() == 0 && !rope_d64_padded(N, D, dtype) && rope_bwd_tc_supported(B, H, N, D, dtype, causal);
+    if (!tc_direct)   // the tensor-core path at D = 128 computes delta in its fused pre-pass
+        if (int e = launch_rope_delta(p, dtype, s)) return e;
     if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
         const size_t rows = (size_t)B * H * N;
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
@@ -234,15 +236,15 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         if (int e = launch_unpad_d64(dkp, dk, rows, 1, dtype, s)) return e;
         return launch_unpad_d64(dvp, dv, rows, 0, dtype, s);
     }
-    if (g_policy.load() == 0 && rope_bwd_tc_supported(B, H, N, D, dtype, causal)) {
+    if (tc_direct) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
-        void* q_rot = (char*)workspace + w.rot;
-        if (int e = launch_rope_prerotate(q, q_rot, tab, B, H, N, sm_scale * kLog2e, dtype, s)) return e;
-        p.q_rot = q_rot;
+        p.q_rot = (char*)workspace + w.rot;
+        if (int e = launch_rope_bwd_prepass(p, dtype, s)) return e;   // delta, rotated Q, cleared dQ accumulator
+        p.dq_acc_zeroed = 1;
         g_last_family[COROPE_OP_ROPE_BWD] = 1;
         return launch_rope_bwd_tc(p, dtype, s);
     }

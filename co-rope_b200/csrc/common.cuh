@@ -63,6 +63,7 @@ struct RopeParams {
     int* sched_counter; // zeroed word in the workspace: next work item / unit of the persistent tensor-core kernels
     const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
     const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
+    int dq_acc_zeroed;  // backward: the pre-pass has already cleared dq_acc (otherwise the launcher of the main kernel does)
     long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise
 };
 
@@ -523,6 +524,9 @@ void count_launch(int n = 1);
 int launch_rope_fwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s);
+// tensor-core backward, D = 128, 16-bit: delta, the rotated fp16 copy of Q (scaled by sm_scale * log2e) into p.q_rot and a
+// zeroed p.dq_acc in one launch; sets nothing in p
+int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src = -1);
 int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
 int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);

@@ -582,7 +582,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_f32(&mdq, p.dq_acc, rows, kD, kBQ, kD)) return e;
-    cudaError_t e = cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
+    cudaError_t e = p.dq_acc_zeroed ? cudaSuccess : cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
     auto kern = rope_bwd_sm100_kernel<T>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);

@@ -430,6 +430,51 @@ __global__ void __launch_bounds__(256) rope_prerotate_d128_kernel(const T* __res
     dst[8] = x2;
 }
 
+// Everything the tensor-core backward needs before its main kernel, in one pass over the rows (16 threads per row):
+// delta = rowsum(O * dO), the rotated and scaled fp16 copy of Q (threads 0-7 of a row: 8 pairs each, same arithmetic as
+// rope_prerotate_d128_kernel) and a zeroed row of the fp32 dQ accumulator (32 bytes per thread).  One launch instead of
+// a memset and two kernels; all three parts are bound by the same HBM traffic.
+template <typename T>
+__global__ void __launch_bounds__(256) rope_bwd_prepass_d128_kernel(const T* __restrict__ q, const T* __restrict__ o, const T* __restrict__ d_o,
+                                                                     const uint32_t* __restrict__ tab, __half* __restrict__ q_rot,
+                                                                     float* __restrict__ delta, float* __restrict__ dq_acc, size_t rows, int N,
+                                                                     float scale) {
+    const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t row = t >> 4;
+    const int part = (int)(t & 15);
+    const bool live = row < rows;
+    float s = 0.f;
+    if (live) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + row * 128) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + row * 128) + part);
+        if (part < 8) {
+            const int c = part * 8;
+            const int n = (int)(row % (size_t)N);
+            const uint4* src = reinterpret_cast<const uint4*>(q + row * 128 + c);
+            uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
+            const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
+            const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
+            rotate_vec8<T>(x1, x2, t0, t1, scale * (1.f / 32768.f), -257.f * scale);
+            uint4* dst = reinterpret_cast<uint4*>(q_rot + row * 128 + c);
+            dst[0] = x1;
+            dst[8] = x2;
+        }
+        uint4* z = reinterpret_cast<uint4*>(dq_acc + row * 128) + part * 2;
+        z[0] = make_uint4(0u, 0u, 0u, 0u);
+        z[1] = make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 fa = unpack2<T>(aw[i]), fb = unpack2<T>(bw[i]);
+            s = fmaf(fa.x, fb.x, s);
+            s = fmaf(fa.y, fb.y, s);
+        }
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (part == 0 && live) delta[row] = s;
+}
+
 template <typename T, int D>
 int launch_fwd_t(const RopeParams& p, cudaStream_t s) {
     size_t smem = sizeof(float) * (kRows * D + kTile * (D + 1) + kTile * D);
@@ -530,6 +575,20 @@ int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, 
         rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale);
     else
         rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s) {
+    const size_t rows = (size_t)p.B * p.H * p.N;
+    const unsigned grid = (unsigned)((rows * 16 + 255) / 256);
+    const float scale = p.sm_scale * kLog2e;
+    if (dtype == COROPE_DTYPE_BF16)
+        rope_bwd_prepass_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)p.q, (const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o,
+                                                                        p.packed_tab, (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale);
+    else
+        rope_bwd_prepass_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)p.q, (const __half*)p.o, (const __half*)p.d_o, p.packed_tab,
+                                                                 (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale);
     count_launch();
     return (int)cudaGetLastError();
 }
