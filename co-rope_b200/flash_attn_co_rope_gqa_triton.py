@@ -17,43 +17,68 @@ except ImportError:
     import _ext
 
 
+def _forward(q, k, v, causal, sm_scale, theta):
+    """Checks + one corope_gqa_fwd call.  Returns what the backward needs: (q, k, v, o, lse2, a_diag)."""
+    # same checks and messages as flash_attn_co_rope_gqa_triton.py:407-425
+    if not causal:
+        raise ValueError("CoRoPE fused kernel supports causal=True only.")
+    if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
+        raise ValueError("Expected q, k, v to have shape (batch, heads, seqlen, dim).")
+    if k.shape != v.shape:
+        raise ValueError("k and v must share the same shape in GQA.")
+    if q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2] or q.shape[3] != k.shape[3]:
+        raise ValueError("k must align with q along batch/sequence/head_dim.")
+    BATCH, H_Q, N_CTX, HEAD_DIM = q.shape
+    H_KV = k.shape[1]
+    if H_Q % H_KV != 0:
+        raise ValueError("Number of query heads must be divisible by KV heads.")
+    group_size = H_Q // H_KV
+    if group_size > 8:
+        raise ValueError(f"CoRoPE backbone currently limits group_size <= 8 (got {group_size}).")
+    if not (q.dtype == k.dtype == v.dtype) or q.dtype not in _ext.DTYPE_CODES:
+        raise ValueError("q, k, v must share one dtype out of float32, bfloat16, float16.")
+    for t in (q, k, v):
+        _ext.require_cuda(t)
+    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(qc)
+    lse2 = torch.empty((BATCH, H_Q, N_CTX), device=q.device, dtype=torch.float32)
+    a_diag = torch.empty((BATCH, H_KV, N_CTX), device=q.device, dtype=torch.float32)
+    ws, ws_bytes = _ext.workspace(_ext.OP_GQA_FWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_gqa_fwd(
+            qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lse2.data_ptr(), a_diag.data_ptr(),
+            BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_gqa_fwd")
+    return qc, kc, vc, o, lse2, a_diag
+
+
+def _backward(q, k, v, o, lse2, a_diag, grad_output, sm_scale, theta):
+    """One corope_gqa_bwd call on what _forward returned.  Returns (dq, dk, dv); dk / dv are summed over each group."""
+    grad_output = grad_output.contiguous()
+    BATCH, H_Q, N_CTX, HEAD_DIM = q.shape
+    H_KV = k.shape[1]
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    ws, ws_bytes = _ext.workspace(_ext.OP_GQA_BWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_gqa_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(), lse2.data_ptr(),
+            a_diag.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_gqa_bwd")
+    return dq, dk, dv
+
+
 class _attention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, causal, sm_scale, theta, warp_specialize=False):
-        # same checks and messages as flash_attn_co_rope_gqa_triton.py:407-425
-        if not causal:
-            raise ValueError("CoRoPE fused kernel supports causal=True only.")
-        if q.ndim != 4 or k.ndim != 4 or v.ndim != 4:
-            raise ValueError("Expected q, k, v to have shape (batch, heads, seqlen, dim).")
-        if k.shape != v.shape:
-            raise ValueError("k and v must share the same shape in GQA.")
-        if q.shape[0] != k.shape[0] or q.shape[2] != k.shape[2] or q.shape[3] != k.shape[3]:
-            raise ValueError("k must align with q along batch/sequence/head_dim.")
-        BATCH, H_Q, N_CTX, HEAD_DIM = q.shape
-        H_KV = k.shape[1]
-        if H_Q % H_KV != 0:
-            raise ValueError("Number of query heads must be divisible by KV heads.")
-        group_size = H_Q // H_KV
-        if group_size > 8:
-            raise ValueError(f"CoRoPE backbone currently limits group_size <= 8 (got {group_size}).")
-        if not (q.dtype == k.dtype == v.dtype) or q.dtype not in _ext.DTYPE_CODES:
-            raise ValueError("q, k, v must share one dtype out of float32, bfloat16, float16.")
-        for t in (q, k, v):
-            _ext.require_cuda(t)
-        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
-        o = torch.empty_like(qc)
-        lse2 = torch.empty((BATCH, H_Q, N_CTX), device=q.device, dtype=torch.float32)
-        a_diag = torch.empty((BATCH, H_KV, N_CTX), device=q.device, dtype=torch.float32)
-        ws, ws_bytes = _ext.workspace(_ext.OP_GQA_FWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
-        with torch.cuda.device(q.device):
-            rc = _ext.lib().corope_gqa_fwd(
-                qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lse2.data_ptr(), a_diag.data_ptr(),
-                BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
-                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
-        _ext.raise_for_status(rc, "corope_gqa_fwd")
+        qc, kc, vc, o, lse2, a_diag = _forward(q, k, v, causal, sm_scale, theta)
         ctx.save_for_backward(qc, kc, vc, o, lse2, a_diag)
-        ctx.group_size = group_size
+        ctx.group_size = q.shape[1] // k.shape[1]
         ctx.sm_scale = sm_scale
         ctx.theta = theta
         ctx.causal = causal
@@ -62,20 +87,7 @@ class _attention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         q, k, v, o, lse2, a_diag = ctx.saved_tensors
-        grad_output = grad_output.contiguous()
-        BATCH, H_Q, N_CTX, HEAD_DIM = q.shape
-        H_KV = k.shape[1]
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(k)
-        dv = torch.empty_like(v)
-        ws, ws_bytes = _ext.workspace(_ext.OP_GQA_BWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
-        with torch.cuda.device(q.device):
-            rc = _ext.lib().corope_gqa_bwd(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(), lse2.data_ptr(),
-                a_diag.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(ctx.sm_scale), float(ctx.theta),
-                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
-        _ext.raise_for_status(rc, "corope_gqa_bwd")
+        dq, dk, dv = _backward(q, k, v, o, lse2, a_diag, grad_output, ctx.sm_scale, ctx.theta)
         return dq, dk, dv, None, None, None, None
 
 

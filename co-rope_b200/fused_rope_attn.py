@@ -34,35 +34,61 @@ def _tables(freqs_cos, freqs_sin, N, D, device):
     return out[0], out[1], out[0].stride(0)
 
 
+def _forward(q, k, v, causal, sm_scale, freqs_cos, freqs_sin):
+    """Checks + one corope_rope_attn_fwd call.  Returns what the backward needs: (q, k, v, o, M, cos, sin, table stride)."""
+    # shape constraints, as fused_rope_attn.py:657-661
+    HEAD_DIM_Q, HEAD_DIM_K = q.shape[-1], k.shape[-1]
+    HEAD_DIM_V = v.shape[-1]
+    assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}
+    assert HEAD_DIM_K in SUPPORTED_HEAD_DIMS, "corope_b200 supports head dims %s" % (SUPPORTED_HEAD_DIMS,)
+    assert q.shape == k.shape == v.shape and q.dim() == 4
+    assert q.dtype == k.dtype == v.dtype and q.dtype in _ext.DTYPE_CODES
+    for t in (q, k, v):
+        _ext.require_cuda(t)
+    B, H, N, D = q.shape
+    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    cos, sin, tstride = _tables(freqs_cos, freqs_sin, N, D, q.device)
+    o = torch.empty_like(qc)
+    M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+    ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD, B, H, H, N, D, q.dtype, q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_rope_attn_fwd(
+            qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), tstride,
+            o.data_ptr(), M.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_rope_attn_fwd")
+    return qc, kc, vc, o, M, cos, sin, tstride
+
+
+def _backward(q, k, v, o, M, cos, sin, tstride, do, causal, sm_scale):
+    """One corope_rope_attn_bwd call on what _forward returned.  Returns (dq, dk, dv)."""
+    # the reference asserts contiguity and N % 128 == 0 (fused_rope_attn.py:727-728, 750); these kernels take any
+    # N, and a non-contiguous dO is made contiguous instead of rejected
+    do = do.contiguous()
+    B, H, N, D = q.shape
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD, B, H, H, N, D, q.dtype, q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_rope_attn_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
+            cos.data_ptr(), sin.data_ptr(), tstride, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+            B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_rope_attn_bwd")
+    return dq, dk, dv
+
+
 class _attention(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, q, k, v, causal, sm_scale, freqs_cos, freqs_sin, warp_specialize=True):
-        # shape constraints, as fused_rope_attn.py:657-661
-        HEAD_DIM_Q, HEAD_DIM_K = q.shape[-1], k.shape[-1]
-        HEAD_DIM_V = v.shape[-1]
-        assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
-        assert HEAD_DIM_K in {16, 32, 64, 128, 256}
-        assert HEAD_DIM_K in SUPPORTED_HEAD_DIMS, "corope_b200 supports head dims %s" % (SUPPORTED_HEAD_DIMS,)
-        assert q.shape == k.shape == v.shape and q.dim() == 4
-        assert q.dtype == k.dtype == v.dtype and q.dtype in _ext.DTYPE_CODES
-        for t in (q, k, v):
-            _ext.require_cuda(t)
-        B, H, N, D = q.shape
-        qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
-        cos, sin, tstride = _tables(freqs_cos, freqs_sin, N, D, q.device)
-        o = torch.empty_like(qc)
-        M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
-        ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD, B, H, H, N, D, q.dtype, q.device)
-        with torch.cuda.device(q.device):
-            rc = _ext.lib().corope_rope_attn_fwd(
-                qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), tstride,
-                o.data_ptr(), M.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
-                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
-        _ext.raise_for_status(rc, "corope_rope_attn_fwd")
+        qc, kc, vc, o, M, cos, sin, tstride = _forward(q, k, v, causal, sm_scale, freqs_cos, freqs_sin)
         ctx.save_for_backward(qc, kc, vc, o, M, cos, sin)
         ctx.sm_scale = sm_scale
-        ctx.HEAD_DIM = D
+        ctx.HEAD_DIM = q.shape[-1]
         ctx.causal = causal
         ctx.tstride = tstride
         return o
@@ -70,21 +96,7 @@ class _attention(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, M, cos, sin = ctx.saved_tensors
-        # the reference asserts contiguity and N % 128 == 0 (fused_rope_attn.py:727-728, 750); these kernels take any
-        # N, and a non-contiguous dO is made contiguous instead of rejected
-        do = do.contiguous()
-        B, H, N, D = q.shape
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(k)
-        dv = torch.empty_like(v)
-        ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD, B, H, H, N, D, q.dtype, q.device)
-        with torch.cuda.device(q.device):
-            rc = _ext.lib().corope_rope_attn_bwd(
-                q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
-                cos.data_ptr(), sin.data_ptr(), ctx.tstride, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(ctx.causal)), float(ctx.sm_scale),
-                ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
-        _ext.raise_for_status(rc, "corope_rope_attn_bwd")
+        dq, dk, dv = _backward(q, k, v, o, M, cos, sin, ctx.tstride, do, ctx.causal, ctx.sm_scale)
         return dq, dk, dv, None, None, None, None, None
 
 

@@ -9,8 +9,8 @@ call costs about one direction's copy time instead of both directions plus the k
 
 import torch
 
-from .fused_rope_attn import attention as _fused_rope_attention
-from .flash_attn_co_rope_gqa_triton import attention as _corope_gqa_attention
+from . import fused_rope_attn as _rope
+from . import flash_attn_co_rope_gqa_triton as _gqa
 
 
 _side_streams = {}   # device index -> (copy-in stream, copy-out stream), created once: the caching allocator keeps one pool
@@ -69,19 +69,21 @@ def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=
         for t in (dq_, dk_, dv_, ddo):
             t.record_stream(cur)
         cur.wait_event(landed)
-        # a chunk is a batch of one with n KV heads
-        qq = dq_.view(1, n * G, N, D).requires_grad_(True)
-        kk = dk_.view(1, n, N, D).requires_grad_(True)
-        vv = dv_.view(1, n, N, D).requires_grad_(True)
+        # a chunk is a batch of one with n KV heads; the two library calls are made directly (same checks as the autograd
+        # entry points, none of the autograd engine's per-call cost, which a 16-chunk call would pay 32 times)
+        qq, kk, vv, dd = dq_.view(1, n * G, N, D), dk_.view(1, n, N, D), dv_.view(1, n, N, D), ddo.view(1, n * G, N, D)
         if theta is None:
-            o = _fused_rope_attention(qq, kk, vv, True, sm_scale, freqs_cos, freqs_sin)
+            saved = _rope._forward(qq, kk, vv, True, sm_scale, freqs_cos, freqs_sin)
+            o = saved[3]
+            gq, gk, gv = _rope._backward(*saved, dd, True, sm_scale)
         else:
-            o = _corope_gqa_attention(qq, kk, vv, True, sm_scale, theta)
-        gq, gk, gv = torch.autograd.grad(o, (qq, kk, vv), ddo.view(1, n * G, N, D))
+            saved = _gqa._forward(qq, kk, vv, True, sm_scale, theta)
+            o = saved[3]
+            gq, gk, gv = _gqa._backward(*saved, dd, sm_scale, theta)
         done = cur.record_event()
         s_out.wait_event(done)
         with torch.cuda.stream(s_out):
-            uo[lo:hi].copy_(o.detach().view(n, G, N, D), non_blocking=True)
+            uo[lo:hi].copy_(o.view(n, G, N, D), non_blocking=True)
             udq[lo:hi].copy_(gq.view(n, G, N, D), non_blocking=True)
             udk[lo:hi].copy_(gk.view(n, 1, N, D), non_blocking=True)
             udv[lo:hi].copy_(gv.view(n, 1, N, D), non_blocking=True)
