@@ -490,6 +490,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
     } else {
         // ------------------------------------------------------------------ dQ~^T drain: TMEM -> global fp32 reductions
+        // stays at the launch count when kRegsDrain equals it; any other share has to be taken or released here, because the
+        // register budget above counts on it and setmaxnreg.inc in another group waits without a time limit
+        if constexpr (kRegsDrain < kLaunchRegs) reg_dealloc<kRegsDrain>();
+        if constexpr (kRegsDrain > kLaunchRegs) reg_alloc<kRegsDrain>();
         const int quad = warp & 3;
         const int dcol = quad * 32 + lane;                // head-dim index held by this thread (TMEM lane)
         const uint32_t lane_base = (uint32_t)(quad * 32) << 16;

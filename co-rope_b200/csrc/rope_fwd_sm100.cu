@@ -38,9 +38,10 @@ constexpr int kRotWarp0 = 4;
 constexpr int kSmxWarp0 = 12;
 // setmaxnreg only moves registers inside the CTA's own launch allocation (512 threads x 128): the sum must not exceed it
 constexpr int kLaunchRegs = 72;        // 65536 / 896 rounded down to a multiple of 8
-// 128 * (40 + 2 * 72 + 4 * 80) = 64512 = 896 * 72.  Measured against 40 / 56 / 88 (which leaves 8 instead of 64 bytes of
-// spill, all in the softmax groups): 0.437 ms against 0.456 ms at the Llama-7B-4K shape -- the rotation groups need the room.
-constexpr int kRegsCtl = 40, kRegsRot = 72, kRegsSmx = 80;
+// 128 * (40 + 2 * 56 + 4 * 88) = 64512 = 896 * 72.  While the rotation groups rotated every K tile in the loop they needed
+// the room (40 / 72 / 80 measured 0.437 ms against 0.456 ms at the Llama-7B-4K shape); with K arriving rotated they only
+// rotate Q once per item and the registers serve the softmax groups better: 0.387 against 0.401 ms.
+constexpr int kRegsCtl = 40, kRegsRot = 56, kRegsSmx = 88;
 static_assert(128 * (kRegsCtl + 2 * kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
 constexpr int kHeadChunk = 8;
 constexpr int kItemSlots = 4;
@@ -362,7 +363,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     } else if (warp < kSmxWarp0) {
         // ------------------------------------------------------------------ rotation groups
         // Two groups of 128 threads; group r rotates rows [64 r, 64 r + 64) of every tile (Q0, Q1 once per item, every
-        // K tile).  They stay at the launch register count.
+        // K tile).  With kRegsRot equal to the launch count they keep what they have; a smaller kRegsRot has to be released
+        // here, or the softmax groups' setmaxnreg.inc (which has no time limit) waits for registers that never come.
+        if constexpr (kRegsRot < kLaunchRegs) reg_dealloc<kRegsRot>();
         const int rg = (warp - kRotWarp0) >> 2;
         const int tid = (threadIdx.x - kRotWarp0 * 32) & 127;
         constexpr int kHalfRows = kBM / 2;
