@@ -41,10 +41,10 @@ DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 THETA = 10000.0
 
 # DRAM bytes per launch of the two tensor-core kernels, from one ncu capture each (dram__bytes_read.sum +
-# dram__bytes_write.sum) at B=2 H=64 N=1024 D=128 bf16 -- 114.4 MB forward, 288.4 MB backward -- expressed per byte of
+# dram__bytes_write.sum) at B=2 H=64 N=1024 D=128 bf16 -- 112.2 MB forward, 288.4 MB backward -- expressed per byte of
 # one [B,H,N,D] bf16 tensor (33.55 MB there).  Traffic of these kernels is proportional to the tensor bytes as long as a
 # head's K/V (and, backward, its fp32 dQ rows) fit in L2, which holds for every workload here.
-NCU_DRAM_PER_TENSOR_BYTE = {"fused_rope_fwd": 114.4 / 33.55, "fused_rope_bwd": 288.4 / 33.55}
+NCU_DRAM_PER_TENSOR_BYTE = {"fused_rope_fwd": 112.2 / 33.55, "fused_rope_bwd": 288.4 / 33.55}
 
 
 def flops_fwd(B, H, N, D):
