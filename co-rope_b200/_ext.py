@@ -15,8 +15,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libcorope_b200.so")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "corope_b200.h")
+DEBUG_HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "corope_b200_debug.h")
 
-SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu", "corope_fwd_mma.cu", "corope_bwd_mma.cu", "noalloc.cu"]
+SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu", "corope_general.cu", "corope_fwd_mma.cu", "corope_bwd_mma.cu", "noalloc.cu",
+           "debug.cu"]
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 OP_ROPE_FWD, OP_ROPE_BWD, OP_GQA_FWD, OP_GQA_BWD = 0, 1, 2, 3
@@ -36,7 +38,7 @@ def _nvcc():
 def build(force=False, verbose=False):
     """Compile csrc/*.cu into libcorope_b200.so for sm_100a (cross-compiles without a GPU)."""
     srcs = [os.path.join(_CSRC, s) for s in SOURCES]
-    deps = srcs + [os.path.join(_CSRC, "common.cuh"), HEADER_PATH]
+    deps = srcs + [os.path.join(_CSRC, "common.cuh"), os.path.join(_CSRC, "corope_mma.cuh"), HEADER_PATH, DEBUG_HEADER_PATH]
     if not force and os.path.exists(LIB_PATH) and all(os.path.getmtime(LIB_PATH) >= os.path.getmtime(d) for d in deps):
         return LIB_PATH
     objs = []
@@ -45,7 +47,7 @@ def build(force=False, verbose=False):
         obj = src[:-3] + ".o"
         objs.append(obj)
         cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
-               "-Xcompiler", "-fPIC", "--use_fast_math" if False else "-DCOROPE_BUILD", "-c", src, "-o", obj]
+               "-Xcompiler", "-fPIC", "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -84,6 +86,9 @@ def lib():
             L.corope_set_kernel_policy.argtypes = [i32]
             L.corope_last_kernel_family.restype = i32
             L.corope_last_kernel_family.argtypes = [i32]
+            if hasattr(L, "corope_debug_expire_wait"):
+                L.corope_debug_expire_wait.restype = i32
+                L.corope_debug_expire_wait.argtypes = [vp, ctypes.c_uint, vp]
             L.corope_rope_attn_fwd.restype = i32
             L.corope_rope_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
             L.corope_rope_attn_fwd_noalloc.restype = i32
@@ -104,25 +109,101 @@ def require_cuda(t):
         raise RuntimeError("corope_b200 runs on CUDA tensors only (got a %s tensor); there is no CPU path." % t.device.type)
 
 
-def status_word(device):
-    """Per-device int32 that kernels set when a bounded wait expires (0 = healthy)."""
+class _DeviceStatus:
+    """The device status word of one GPU with a pinned host mirror that a side stream refreshes after every call."""
+
+    def __init__(self, index):
+        dev = torch.device("cuda", index)
+        self.word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.stream = torch.cuda.Stream(dev)
+        self.event = None
+
+
+def _status(device):
     key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
     with _lock:
-        w = _status_words.get(key)
-        if w is None:
-            w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
-            _status_words[key] = w
-        return w
+        st = _status_words.get(key)
+        if st is None:
+            st = _DeviceStatus(key)
+            _status_words[key] = st
+        return st
+
+
+def status_word(device):
+    """Per-device int32 that kernels set when a bounded wait expires or a value leaves the supported range (0 = healthy)."""
+    return _status(device).word
+
+
+def _status_message(v):
+    if v & 0x2000:
+        return "a gradient term left the value range of the 16-bit Co-RoPE backward and was clamped (results of that call are inaccurate)"
+    return "a bounded device-side wait expired (results of that call and of later calls are undefined)"
+
+
+def pre_call(device):
+    """Called by the attention entry points before they launch: raises if an EARLIER call on this device left the status
+    word set.  Reads only the pinned host mirror (no synchronisation); the mirror is refreshed by post_call(), so the error
+    surfaces at the first call after the failing one has finished on the GPU.  The word is cleared before raising."""
+    if getattr(_batched, "depth", 0) > 0:
+        return
+    st = _status(device)
+    if st.event is not None and st.event.query():
+        v = int(st.mirror[0])
+        if v != 0:
+            st.mirror.zero_()
+            st.word.zero_()
+            st.event = None
+            raise RuntimeError("corope_b200: an earlier kernel reported device status 0x%x: %s" % (v, _status_message(v)))
+
+
+_batched = threading.local()
+
+
+class batched_status:
+    """Context manager for callers that make many library calls in a row (the host pipeline): the per-call look at the
+    mirror and its refresh are done once, on entry and on exit, instead of around every call."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def __enter__(self):
+        pre_call(self.device)
+        _batched.depth = getattr(_batched, "depth", 0) + 1
+        return self
+
+    def __exit__(self, *exc):
+        _batched.depth -= 1
+        if exc[0] is None:
+            post_call(self.device)
+        return False
+
+
+def post_call(device):
+    """Called after a launch: a side stream copies the status word to its pinned mirror once the caller's stream gets there
+    (the caller's stream itself is not delayed)."""
+    if getattr(_batched, "depth", 0) > 0:
+        return
+    st = _status(device)
+    if torch.cuda.is_current_stream_capturing():
+        return
+    done = torch.cuda.current_stream(device).record_event()
+    st.stream.wait_event(done)
+    with torch.cuda.stream(st.stream):
+        st.mirror.copy_(st.word, non_blocking=True)
+        st.event = st.stream.record_event()
 
 
 def check_status(device=None):
-    """Synchronise and raise if any kernel on `device` reported an expired wait."""
+    """Synchronise and raise if any kernel on `device` has set the status word; clears it."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    w = status_word(dev)
-    v = int(w.item())
+    st = _status(dev)
+    v = int(st.word.item())
     if v != 0:
-        w.zero_()
-        raise RuntimeError("corope_b200 kernel reported device status 0x%x (bounded wait expired)" % v)
+        st.word.zero_()
+        st.mirror.zero_()
+        st.event = None
+        raise RuntimeError("corope_b200 kernel reported device status 0x%x: %s" % (v, _status_message(v)))
 
 
 def workspace(op, B, Hq, Hkv, N, D, dtype, device):

@@ -90,6 +90,10 @@ int check_workspace(const void* ws, size_t have, size_t need) {
 }  // namespace
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n); }
+void note_kernel_family(int op, int family) {
+    if (op >= 0 && op < 4) g_last_family[op] = family;
+}
+int kernel_policy() { return g_policy.load(); }
 
 }  // namespace corope
 
@@ -129,14 +133,6 @@ size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int 
     }
 }
 
-#ifdef COROPE_PROFILE
-static long long* g_prof = nullptr;
-void corope_debug_set_profile_buffer(void* ptr) { g_prof = (long long*)ptr; }
-#define COROPE_SET_PROF(p) (p).prof = g_prof
-#else
-#define COROPE_SET_PROF(p) (void)0
-#endif
-
 uint64_t corope_launch_count(void) { return (uint64_t)g_launches.load(); }
 
 int corope_set_kernel_policy(int policy) { return g_policy.exchange(policy); }
@@ -155,7 +151,6 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    COROPE_SET_PROF(p);
     if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
         // D = 64: zero-padded copies of q, k, v in the layout that keeps the rotation pairs together, the D = 128 kernels, o back
         const size_t rows = (size_t)B * H * N;
@@ -177,14 +172,16 @@ int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const floa
         if (int e = launch_rope_fwd_tc(p, dtype, s)) return e;
         return launch_unpad_d64(op, o, rows, 0, dtype, s);
     }
-    if (g_policy.load() == 0 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
+    if (g_policy.load() != 1 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));
-        void* k_rot = (char*)workspace + w.rot;
-        if (int e = launch_rope_prerotate(k, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
-        p.k_rot = k_rot;
+        if (g_policy.load() == 0) {   // policy 2: every K tile is rotated in shared memory by the main kernel, nothing rotated is written to HBM
+            void* k_rot = (char*)workspace + w.rot;
+            if (int e = launch_rope_prerotate(k, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
+            p.k_rot = k_rot;
+        }
         g_last_family[COROPE_OP_ROPE_FWD] = 1;
         return launch_rope_fwd_tc(p, dtype, s);
     }
@@ -206,9 +203,9 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
     p.delta = reinterpret_cast<float*>((char*)workspace + w.delta);
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    COROPE_SET_PROF(p);
-    const bool tc_direct = g_policy.load() == 0 && !rope_d64_padded(N, D, dtype) && rope_bwd_tc_supported(B, H, N, D, dtype, causal);
-    if (!tc_direct)   // the tensor-core path at D = 128 computes delta in its fused pre-pass
+    const int policy = g_policy.load();
+    const bool tc_direct = policy != 1 && !(policy == 0 && rope_d64_padded(N, D, dtype)) && rope_bwd_tc_supported(B, H, N, D, dtype, causal);
+    if (!(tc_direct && policy == 0))   // the tensor-core path at D = 128 computes delta in its fused pre-pass
         if (int e = launch_rope_delta(p, dtype, s)) return e;
     if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
         const size_t rows = (size_t)B * H * N;
@@ -242,9 +239,11 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
-        p.q_rot = (char*)workspace + w.rot;
-        if (int e = launch_rope_bwd_prepass(p, dtype, s)) return e;   // delta, rotated Q, cleared dQ accumulator
-        p.dq_acc_zeroed = 1;
+        if (policy == 0) {   // policy 2: every Q tile is rotated in shared memory by the main kernel, nothing rotated is written to HBM
+            p.q_rot = (char*)workspace + w.rot;
+            if (int e = launch_rope_bwd_prepass(p, dtype, s)) return e;   // delta, rotated Q, cleared dQ accumulator
+            p.dq_acc_zeroed = 1;
+        }
         g_last_family[COROPE_OP_ROPE_BWD] = 1;
         return launch_rope_bwd_tc(p, dtype, s);
     }

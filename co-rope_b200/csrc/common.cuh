@@ -64,7 +64,6 @@ struct RopeParams {
     const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
     const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
     int dq_acc_zeroed;  // backward: the pre-pass has already cleared dq_acc (otherwise the launcher of the main kernel does)
-    long long* prof;    // timing scratch for profiling builds (COROPE_PROFILE); null otherwise
 };
 
 struct GqaParams {
@@ -132,14 +131,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // then leave their loops and fall through to the common exit path.  try_wait itself blocks for
 // a hardware-defined slice, so the limit corresponds to well over a second.
 constexpr uint32_t kWaitLimit = 1u << 20;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kWaitLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag,
+                                                  uint32_t limit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 1023u) == 1023u && *abort_flag) return false;
     }
     *abort_flag = 1;
     if (status) atomicCAS(status, 0, COROPE_DEV_WAIT_EXPIRED | id);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int id, volatile int* abort_flag) {
+    return mbar_wait_limited(bar, parity, status, id, abort_flag, kWaitLimit);
 }
 
 // Non-blocking probe of a phase, and a bounded spin on it.  try_wait parks the thread and wakes it some hundreds of
@@ -379,6 +382,13 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     __half2 h = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&h);
 }
+// two floats -> packed fp16 pair, values beyond the fp16 range saturate to +-65504 instead of becoming inf
+__device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
 __device__ __forceinline__ float2 unpack_half2(uint32_t u) {
     __half2 h = *reinterpret_cast<__half2*>(&u);
     return __half22float2(h);
@@ -449,8 +459,8 @@ __device__ __forceinline__ void rotate_vec8(uint4& x1, uint4& x2, const uint4& t
         const float s0 = fmaf(__uint_as_float(__byte_perm(cs[2 * i], 0x4B000000u, 0x7432)), k1, k0);
         const float c1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7410)), k1, k0);
         const float s1 = fmaf(__uint_as_float(__byte_perm(cs[2 * i + 1], 0x4B000000u, 0x7432)), k1, k0);
-        a[i] = pack_half2(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
-        b[i] = pack_half2(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
+        a[i] = pack_half2_sat(fmaf(fa.x, c0, -fb.x * s0), fmaf(fa.y, c1, -fb.y * s1));
+        b[i] = pack_half2_sat(fmaf(fb.x, c0, fa.x * s0), fmaf(fb.y, c1, fa.y * s1));
     }
     x1 = make_uint4(a[0], a[1], a[2], a[3]);
     x2 = make_uint4(b[0], b[1], b[2], b[3]);
@@ -483,13 +493,6 @@ __device__ __forceinline__ void rotate_tile_regs(uint8_t* tile, const TabRegs<RO
     }
 }
 
-// two floats -> packed fp16 pair, values beyond the fp16 range saturate to +-65504 instead of becoming inf
-__device__ __forceinline__ uint32_t pack_half2_sat(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-
 #endif  // __CUDACC__
 
 // Same for a 2-D row-major fp32 tensor without swizzle (box_cols * 4 bytes a multiple of 16, box_cols <= 256): used for
@@ -517,6 +520,9 @@ inline int encode_tensor_map_2d_f32(CUtensorMap* out, const void* base, uint64_t
 
 // Every kernel launch of the library bumps this counter (read through corope_launch_count()).
 void count_launch(int n = 1);
+// Diagnostics kept by abi.cu (see include/corope_b200_debug.h): which kernel family an op took last, and the policy in force.
+void note_kernel_family(int op, int family);
+int kernel_policy();
 
 // ---------------------------------------------------------------------------------------------
 // host launchers implemented by the kernel translation units (return cudaError_t as int)

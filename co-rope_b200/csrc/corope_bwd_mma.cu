@@ -32,12 +32,21 @@ constexpr int kTabBytes = kThreads * 16 * 4;    // one per-lane operand table: 1
 constexpr int kPsRowBytes = 144;                // P rows (64 keys fp16) + 16 bytes of padding
 constexpr int kDkStride = 132;                  // words per row of the shared dK tile (128 + 4: conflict-free reductions)
 // The shared dK tile is summed in 32-bit fixed point (2^-14 units): integer shared-memory atomics are single
-// instructions, fp32 ones are compare-and-swap loops, and the sum no longer depends on the order of the warps.  One
-// contribution is below 256 in magnitude by a wide margin (|g| |q| G); its rounding error of 3e-5 is far below the
-// 16-bit output resolution.  x * 2^14 + 1.5 * 2^23 holds round(x * 2^14) in its low mantissa bits.
-constexpr float kDkScale = 16384.f, kDkMagic = 12582912.f;
+// instructions, fp32 ones are compare-and-swap loops, and the sum no longer depends on the order of the warps.  The
+// rounding error of one contribution, 3e-5, is far below the 16-bit output resolution.
+// Fast form: x * 2^14 + 1.5 * 2^23 holds round(x * 2^14) in its low mantissa bits -- valid for |x| < 256 only.  Per block
+// of 8 keys a warp therefore bounds its contributions (|x| <= sqrt(2) G max|g| max|q_row|, one vote instruction) and takes
+// the range-safe form when the bound is not below 256: a real float -> int conversion of x clamped to +-4096 (the tile sum
+// of 9 such terms still fits 32 bits).  A contribution that had to be clamped is reported in the status word
+// (COROPE_DEV_RANGE): the result is then inaccurate, never wrapped around.
+constexpr float kDkScale = 16384.f, kDkMagic = 12582912.f, kDkFastLimit = 250.f, kDkClamp = 4096.f;
 __device__ __forceinline__ void dk_add(int* slot, float x) {
     atomicAdd(slot, __float_as_int(fmaf(x, kDkScale, kDkMagic)) - 0x4B400000);
+}
+__device__ __forceinline__ void dk_add_safe(int* slot, float x, bool& clamped) {
+    const float xc = fminf(fmaxf(x, -kDkClamp), kDkClamp);
+    clamped |= xc != x;
+    atomicAdd(slot, __float2int_rn(xc * kDkScale));
 }
 constexpr int kGrRowBytes = 144;                // rows of the leader-term operand graw (64 keys fp16 + padding)
 constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + 4 * kTabBytes +
@@ -187,6 +196,20 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         aw[4 * s] = w4.x; aw[4 * s + 1] = w4.y; aw[4 * s + 2] = w4.z; aw[4 * s + 3] = w4.w;
     }
     const bool valid = h < G;
+    // largest |g| for which every dK contribution of a block stays inside the fast fixed-point form (see dk_add)
+    float g_fast_limit;
+    {
+        float qmax = 0.f;
+#pragma unroll
+        for (int x = 0; x < 16; ++x) {
+            const float2 f = unpack_half2(aq[x]);
+            qmax = fmaxf(qmax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) qmax = fmaxf(qmax, __shfl_xor_sync(0xffffffffu, qmax, off));
+        g_fast_limit = kDkFastLimit / (1.4143f * (float)G * fmaxf(qmax, 1e-20f));
+    }
+    bool range_clamped = false;
     const float lse = valid ? p.lse2[(q_head0 + h) * N + i] : 0.f;
     const float dlt = valid ? p.delta[(q_head0 + h) * N + i] : 0.f;
     const float a_ii = p.a_diag[(size_t)bg * N + i];
@@ -292,7 +315,9 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             const float p1 = vis1 ? fast_exp2((s1 + t1) * sc2 - lse) : 0.f;
             const float g0 = p0 * (dp0 + e0 - dlt) * p.sm_scale, g1 = p1 * (dp1 + e1 - dlt) * p.sm_scale;
             if (valid) *ps_out = pack_half2(p0, p1);
-            const uint32_t gp = pack_half2(g0, g1);
+            const uint32_t gp = pack_half2_sat(g0, g1);
+            const float g_abs = fmaxf(fabsf(g0), fabsf(g1));
+            const bool big = __any_sync(0xffffffffu, g_abs > g_fast_limit);   // warp-uniform: some contribution may leave the fast range
             float gd0 = -g0 * (m0 + n0), gd1 = -g1 * (m1 + n1);
 #pragma unroll
             for (int off = 4; off < 32; off <<= 1) {   // sum over the heads
@@ -307,18 +332,36 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             // u = g^T q per pair, inverse rotation, into the shared dK tile
             const uint32_t gT = movmatrix_trans(gp);
             int* dkrow = dk_t + (nb * 8 + h) * kDkStride;
+            if (!big) {
 #pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                const uint4 bv = bqs[s * 32 + lane];
-                const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
+                for (int s = 0; s < 4; ++s) {
+                    const uint4 bv = bqs[s * 32 + lane];
+                    const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float u1 = 0.f, u2 = 0.f;
-                    mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
-                    const float2 cs = unpack_half2(csr[s * 4 + e]);
-                    const int pp = lane_pair(c, s, e);
-                    dk_add(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y));
-                    dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y));
+                    for (int e = 0; e < 4; ++e) {
+                        float u1 = 0.f, u2 = 0.f;
+                        mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
+                        const float2 cs = unpack_half2(csr[s * 4 + e]);
+                        const int pp = lane_pair(c, s, e);
+                        dk_add(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y));
+                        dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y));
+                    }
+                }
+            } else {
+                range_clamped |= g_abs > 65504.f;   // g itself no longer fits the fp16 operand (it was saturated above)
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint4 bv = bqs[s * 32 + lane];
+                    const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float u1 = 0.f, u2 = 0.f;
+                        mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
+                        const float2 cs = unpack_half2(csr[s * 4 + e]);
+                        const int pp = lane_pair(c, s, e);
+                        dk_add_safe(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y), range_clamped);
+                        dk_add_safe(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y), range_clamped);
+                    }
                 }
             }
             // dq += g K'^T
@@ -341,7 +384,8 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             const int key = j0 + 2 * lane;
             const float gr0 = key <= i ? gz0 * z0 * (1.f - z0) * p.sm_scale : 0.f;
             const float gr1 = key + 1 <= i ? gz1 * z1 * (1.f - z1) * p.sm_scale : 0.f;
-            *reinterpret_cast<uint32_t*>(grs + warp * kGrRowBytes + lane * 4) = pack_half2(gr0, gr1);
+            range_clamped |= fmaxf(fabsf(gr0), fabsf(gr1)) > 65504.f;
+            *reinterpret_cast<uint32_t*>(grs + warp * kGrRowBytes + lane * 4) = pack_half2_sat(gr0, gr1);
         }
         __syncthreads();
 
@@ -391,10 +435,10 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                 int* ra = dk_t + (mb * 16 + h) * kDkStride + nh * 64 + 2 * c;   // into the shared dK tile (flushed below)
 #pragma unroll
                 for (int n = 0; n < 8; ++n) {
-                    dk_add(ra + n * 8, acc2[n][0]);
-                    dk_add(ra + n * 8 + 1, acc2[n][1]);
-                    dk_add(ra + 8 * kDkStride + n * 8, acc2[n][2]);
-                    dk_add(ra + 8 * kDkStride + n * 8 + 1, acc2[n][3]);
+                    dk_add_safe(ra + n * 8, acc2[n][0], range_clamped);   // once per tile: the range-safe form costs nothing here
+                    dk_add_safe(ra + n * 8 + 1, acc2[n][1], range_clamped);
+                    dk_add_safe(ra + 8 * kDkStride + n * 8, acc2[n][2], range_clamped);
+                    dk_add_safe(ra + 8 * kDkStride + n * 8 + 1, acc2[n][3], range_clamped);
                 }
             }
             //   dqL_i += sum_k graw_ik k_k   -- warp w takes the operand-order columns 16 w .. 16 w + 15 of k
@@ -440,6 +484,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                 }
         }
     }
+    if (__any_sync(0xffffffffu, range_clamped) && lane == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_RANGE);
     if (valid) {
         T* DQ = reinterpret_cast<T*>(p.dq) + ((q_head0 + h) * N + i) * kD;
 #pragma unroll

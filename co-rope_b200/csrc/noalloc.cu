@@ -56,14 +56,18 @@ extern "C" int corope_rope_attn_fwd_noalloc(const void* q, const void* k, const 
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    if (rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
+    // the kernel-selection policy of the diagnostics header applies here too: 1 = general kernels; 0 and 2 both mean the
+    // tensor-core kernel with its in-kernel K rotation (this entry point has no room for a rotated copy)
+    if (kernel_policy() != 1 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
         uint32_t* table = nullptr;
         if (int e = scratch_on_current_device(&table)) return e;
         // the table is rebuilt in full for rows [0, N) on every call, so stale contents of an earlier call are never read
         if (int e = launch_pack_tables(cos, sin, table_row_stride, table, N, D / 2, s)) return e;
         p.packed_tab = table;
         p.sched_counter = reinterpret_cast<int*>(table + (size_t)N * (D / 2));
+        note_kernel_family(COROPE_OP_ROPE_FWD, 1);
         return launch_rope_fwd_tc(p, dtype, s);
     }
+    note_kernel_family(COROPE_OP_ROPE_FWD, 0);
     return launch_rope_fwd_general(p, dtype, s);  // the general kernels use no scratch at all
 }

@@ -36,12 +36,8 @@ namespace {
 constexpr int kD = 128;
 constexpr int kBK = 128;                 // keys per CTA
 constexpr int kBQ = 64;                  // query rows per step
-#ifdef COROPE_STAGES
-constexpr int kStages = COROPE_STAGES;
-#else
 constexpr int kStages = 3;               // Q / dO ring.  With 2 stages the sweep is latency-bound on this ring (1.56 ms against 1.08 ms
                                          // with 3); a 4th stage gave nothing, so its 32 KiB stage the dQ~ tile for the bulk reduce instead
-#endif
 constexpr int kKVBytes = kBK * kD * 2;   // 32 KiB
 constexpr int kKVBox = kKVBytes / 2;
 constexpr int kQBytes = kBQ * kD * 2;    // 16 KiB
@@ -423,7 +419,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const float s0 = p0 * (__uint_as_float(rd[2 * i]) - d2.x);
                     const float s1 = p1 * (__uint_as_float(rd[2 * i + 1]) - d2.y);
                     pp[i] = pack2<T>(p0, p1);
-                    dd[i] = pack_half2(s0, s1);
+                    dd[i] = pack_half2_sat(s0, s1);
                 }
                 COROPE_TMEM_ST16(tS + c * 32, pp);   // each group writes P^T over the start of its own 32 S^T columns: the other group's S^T may still be unread
 #pragma unroll
@@ -544,10 +540,11 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 }
 
 // dQ = inverse_rotate(dQ~ accumulator) * sm_scale; one thread per (row, 4 consecutive d < 64): 16-byte loads of the
-// accumulator halves and of the tables, 8-byte stores
+// accumulator halves and of the packed (cos, sin) table the main kernel used (the caller's own tables may be narrower than
+// 64 columns when a D = 64 problem runs zero-padded; the packed table then holds the identity in columns 32..63), 8-byte stores
 template <typename T>
-__global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const float* __restrict__ cosT,
-                                            const float* __restrict__ sinT, int64_t ts, size_t rows, int N, float scale) {
+__global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const uint32_t* __restrict__ packed,
+                                            size_t rows, int N, float scale) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 16) return;
     const size_t row = idx >> 4;
@@ -555,22 +552,14 @@ __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __
     const int pos = (int)(row % (size_t)N);
     const float4 a1 = *reinterpret_cast<const float4*>(acc + row * kD + d);
     const float4 a2 = *reinterpret_cast<const float4*>(acc + row * kD + d + 64);
-    float c[4], sn[4];
-    if ((ts & 3) == 0 && ((reinterpret_cast<uintptr_t>(cosT) | reinterpret_cast<uintptr_t>(sinT)) & 15) == 0) {
-        const float4 c4 = __ldg(reinterpret_cast<const float4*>(cosT + pos * ts + d));
-        const float4 s4 = __ldg(reinterpret_cast<const float4*>(sinT + pos * ts + d));
-        c[0] = c4.x; c[1] = c4.y; c[2] = c4.z; c[3] = c4.w;
-        sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { c[i] = cosT[pos * ts + d + i]; sn[i] = sinT[pos * ts + d + i]; }
-    }
+    const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(packed + (size_t)pos * (kD / 2) + d));
+    const float2 cs[4] = {unpack_unorm_pair(t4.x), unpack_unorm_pair(t4.y), unpack_unorm_pair(t4.z), unpack_unorm_pair(t4.w)};
     const float x1[4] = {a1.x, a1.y, a1.z, a1.w}, x2[4] = {a2.x, a2.y, a2.z, a2.w};
     uint2 o1, o2;
-    o1.x = pack2<T>((x1[0] * c[0] + x2[0] * sn[0]) * scale, (x1[1] * c[1] + x2[1] * sn[1]) * scale);
-    o1.y = pack2<T>((x1[2] * c[2] + x2[2] * sn[2]) * scale, (x1[3] * c[3] + x2[3] * sn[3]) * scale);
-    o2.x = pack2<T>((x2[0] * c[0] - x1[0] * sn[0]) * scale, (x2[1] * c[1] - x1[1] * sn[1]) * scale);
-    o2.y = pack2<T>((x2[2] * c[2] - x1[2] * sn[2]) * scale, (x2[3] * c[3] - x1[3] * sn[3]) * scale);
+    o1.x = pack2<T>((x1[0] * cs[0].x + x2[0] * cs[0].y) * scale, (x1[1] * cs[1].x + x2[1] * cs[1].y) * scale);
+    o1.y = pack2<T>((x1[2] * cs[2].x + x2[2] * cs[2].y) * scale, (x1[3] * cs[3].x + x2[3] * cs[3].y) * scale);
+    o2.x = pack2<T>((x2[0] * cs[0].x - x1[0] * cs[0].y) * scale, (x2[1] * cs[1].x - x1[1] * cs[1].y) * scale);
+    o2.y = pack2<T>((x2[2] * cs[2].x - x1[2] * cs[2].y) * scale, (x2[3] * cs[3].x - x1[3] * cs[3].y) * scale);
     *reinterpret_cast<uint2*>(dq + row * kD + d) = o1;
     *reinterpret_cast<uint2*>(dq + row * kD + d + 64) = o2;
 }
@@ -600,8 +589,8 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     const size_t n = rows * 16;
-    rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.cos, p.sin,
-                                                                              p.table_stride, rows, p.N, p.sm_scale); count_launch();
+    rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.packed_tab, rows, p.N,
+                                                                              p.sm_scale); count_launch();
     return (int)cudaGetLastError();
 }
 

@@ -16,7 +16,13 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_i (16-bit) is written over S_i: keys 0-63 in
 // columns 0-31, keys 64-127 in columns 64-95 (each softmax group writes only over columns it has already read).
 // MMA order per K tile j:  PV0(j) QK0(j+1) | PV1(j) QK1(j+1)  so that one group's softmax overlaps the
-// other group's MMAs.  The rotated Q / K never leave shared memory.
+// other group's MMAs.
+// K tiles come in one of two ways.  By default a pre-pass (rope_prerotate_d128_kernel) has written a rotated fp16 copy
+// of K to the workspace and the K ring loads that copy: every K tile is consumed by up to N/256 work items, and rotating
+// it in shared memory for each of them cost 14 % of the kernel (issue slots and shared-memory port time that the softmax
+// and the MMA operand fetch need), more than the copy's extra HBM traffic.  With p.k_rot == nullptr (kernel policy 2 of
+// the diagnostics header, and the entry point that takes no workspace) the rotation groups rotate every K tile in shared
+// memory as it lands and nothing rotated is ever written to HBM.  Q is always rotated in shared memory, once per item.
 //
 // Replaces _attn_fwd / _attn_fwd_inner of the reference (fused-rope/fused_rope_attn.py:47-138, 219-320):
 // rotation formula :96-99 / :286-287, exp2-domain softmax :103-114, M = m + log2(l) :316.
@@ -54,8 +60,7 @@ enum Bar {
     K_ROT = K_FULL + kKStages,
     K_EMPTY = K_ROT + kKStages,
     V_FULL = K_EMPTY + kKStages,
-    V_READY = V_FULL + kVStages,
-    V_EMPTY = V_READY + kVStages,
+    V_EMPTY = V_FULL + kVStages,
     S_FULL = V_EMPTY + kVStages,       // +i
     P_FULL = S_FULL + 2,
     O_FULL = P_FULL + 2,
@@ -71,27 +76,6 @@ constexpr size_t kXchBytes = 2 * 2 * kBM * sizeof(float);         // half-row ma
 constexpr size_t kSmemSlack = 512;     // room to round the dynamic shared memory base up to 1024 bytes (checked at run time)
 constexpr size_t kSmemBytes = kSmemTiles + kXchBytes + NUM_BARS * 8 + 64 + kSmemSlack;
 static_assert(kSmemBytes <= 232448, "shared memory budget");  // + alignment slack (tmem slot, abort flag and the item ring live in the 64)
-
-// bf16 -> fp16 in place over a whole tile (layout-agnostic).  Values beyond the fp16 range saturate.
-__device__ __forceinline__ void convert_tile_bf16_to_f16(uint8_t* tile, int tid) {
-    constexpr int kIters = kTileBytes / 2 / (16 * 128);   // half a tile per group of 128 threads: 8 vectors of 16 bytes per thread
-#pragma unroll
-    for (int h = 0; h < kIters; h += 8) {
-        uint4 x[8];
-#pragma unroll
-        for (int it = 0; it < 8; ++it) x[it] = reinterpret_cast<uint4*>(tile)[(h + it) * 128 + tid];
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-            uint32_t w[4] = {x[it].x, x[it].y, x[it].z, x[it].w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = unpack_bf162(w[i]);
-                w[i] = pack_half2_sat(f.x, f.y);
-            }
-            reinterpret_cast<uint4*>(tile)[(h + it) * 128 + tid] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-    }
-}
 
 // Work items (one = 256 query rows of one head) in the order CTAs take them: heads in chunks of kHeadChunk so that
 // the items in flight at one time share few heads (their K/V stay in L2), heaviest query blocks first inside a chunk.
@@ -134,13 +118,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     // P is written in the inputs' own 16-bit format so that V can be used as it lands (tcgen05.mma wants both operands in
     // one format).  For bf16 the row sums are taken from the rounded P, which keeps the normalised weights consistent:
     // measured max-abs error of O at the Llama-7B-4K shape is unchanged (0.0080, rounding of the bf16 output itself 0.0077).
-    // COROPE_CONVERT_V restores the older variant (V converted to fp16 in shared memory, fp16 P).
-#ifdef COROPE_CONVERT_V
-    constexpr bool kConvertV = (Elem<T>::kDtype == COROPE_DTYPE_BF16);
-#else
-    constexpr bool kConvertV = false;
-#endif
-    constexpr bool kPBf16 = !kConvertV && Elem<T>::kDtype == COROPE_DTYPE_BF16;
+    constexpr bool kPBf16 = Elem<T>::kDtype == COROPE_DTYPE_BF16;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = sm;
@@ -199,7 +177,6 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         }
         for (int s = 0; s < kVStages; ++s) {
             mbar_init(&bars[V_FULL + s], 1);
-            mbar_init(&bars[V_READY + s], 8);
             mbar_init(&bars[V_EMPTY + s], 1);
         }
         fence_mbar_init();
@@ -277,7 +254,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         } else if (warp == kMmaWarp) {
             // -------------------------------------------------------------- MMA issuer
             const bool leader = elect_one();
-            constexpr int kVFmt = (kConvertV || Elem<T>::kDtype == COROPE_DTYPE_F16) ? 0 : 1;
+            constexpr int kVFmt = Elem<T>::kDtype == COROPE_DTYPE_F16 ? 0 : 1;
             const uint32_t idesc_qk = make_idesc(0, 0, 0, 0, kBM, kBN);
             const uint32_t idesc_pv = make_idesc(kVFmt, kVFmt, 0, 1, kBM, kD);
             constexpr uint32_t kHi = sdesc_hi(1024);
@@ -296,10 +273,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int kk = 0; kk < kBN / 16; ++kk)
                     if (leader) umma_ts2(d, a + (kk >> 2) * 64 + (kk & 3) * 8, b0 + kk * (2048 >> 4), kHi, idesc_pv, (acc || kk > 0) ? 1u : 0u);
             };
-            // "operand ready": straight from the TMA barrier when nothing has to touch the tile in shared memory (K rotated by
-            // the pre-pass, V used in its own format), else from the rotation groups
+            // "K ready": straight from the TMA barrier when the pre-pass has rotated K, else from the rotation groups
             const int kReadyBar = p.k_rot != nullptr ? K_FULL : K_ROT;
-            constexpr int kVReadyBar = kConvertV ? V_READY : V_FULL;
+            constexpr int kVReadyBar = V_FULL;
             int gk = 0, gv = 0, s0 = 0, s1 = 0;   // K tiles, V tiles, S tiles of group 0 / 1 so far
             bool ok = true;
             for (int n = 0; ok; ++n) {
@@ -324,7 +300,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int vs = gv % kVStages;
                     const int ks1 = gk % kKStages;
                     const bool have_next = j + 1 < nk;
-                    if (!(ok = mbar_wait_warp(&bars[kVReadyBar + vs], (gv / kVStages) & 1, p.status, V_READY, abort_flag))) break;
+                    if (!(ok = mbar_wait_warp(&bars[kVReadyBar + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
                     if (j < nk0) {
                         if (!(ok = mbar_wait_warp(&bars[P_FULL + 0], s0 & 1, p.status, P_FULL, abort_flag))) break;
                         if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 0], (n - 1) & 1, p.status, O_FREE, abort_flag))) break;
@@ -371,7 +347,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         constexpr int kHalfRows = kBM / 2;
         bool ok = true;
         TabRegs<kHalfRows> tr;
-        int gk = 0, gv = 0;
+        int gk = 0;
         for (int n = 0; ok; ++n) {
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
             if (w < 0) break;
@@ -385,30 +361,16 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 mbar_arrive_warp(&bars[Q_ROT + i], lane);
             }
             if (!ok) break;
-            // K and V tiles: only where they have to be touched in shared memory (K when no pre-pass has rotated it, V for
-            // the fp16-P variant); otherwise the MMA warp takes them straight from the TMA barriers
-            const bool k_pre = p.k_rot != nullptr;
-            if (k_pre && !kConvertV) continue;
-            if (!k_pre) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
-            for (int j = 0; j < nk; ++j, ++gk, ++gv) {
-                const int ks = gk % kKStages, vs = gv % kVStages;
-                if (!k_pre) {
-                    if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
-#ifndef COROPE_KO_ROT
-                    rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
-#endif
-                    fence_proxy_async();
-                    mbar_arrive_warp(&bars[K_ROT + ks], lane);
-                    if (j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
-                }
-                if (kConvertV) {
-                    if (!(ok = mbar_wait_warp(&bars[V_FULL + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
-#ifndef COROPE_KO_ROT
-                    convert_tile_bf16_to_f16(sV + vs * kTileBytes + rg * (kTileBytes / 2), tid);
-#endif
-                    fence_proxy_async();
-                    mbar_arrive_warp(&bars[V_READY + vs], lane);
-                }
+            // K tiles: only when no pre-pass has rotated them; otherwise the MMA warp takes them straight from the TMA barriers
+            if (p.k_rot != nullptr) continue;
+            load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(rg * kHalfRows) * (kD / 2), tid);
+            for (int j = 0; j < nk; ++j, ++gk) {
+                const int ks = gk % kKStages;
+                if (!(ok = mbar_wait_warp(&bars[K_FULL + ks], (gk / kKStages) & 1, p.status, K_FULL, abort_flag))) break;
+                rotate_tile_regs<T, kHalfRows, kBoxBytes, 1>(sK + ks * kTileBytes + rg * kHalfRows * 128, tr, tid, 1.0f);
+                fence_proxy_async();
+                mbar_arrive_warp(&bars[K_ROT + ks], lane);
+                if (j + 1 < nk) load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)((j + 1) * kBN + rg * kHalfRows) * (kD / 2), tid);
             }
         }
     } else {
@@ -442,9 +404,6 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!(ok = mbar_wait_warp(&bars[S_FULL + wg], gs & 1, p.status, S_FULL + wg, abort_flag))) break;
                 tc_fence_after();
                 const bool diag = causal && (j == nk_i - 1);
-#ifdef COROPE_KO_SMX
-                if (j > 0) { tc_fence_before(); mbar_arrive_warp(&bars[P_FULL + wg], lane); continue; }
-#endif
                 uint32_t s0[32], s1[32];
                 COROPE_TMEM_LD32(tS, s0);
                 COROPE_TMEM_LD32(tS + 32, s1);

@@ -7,6 +7,10 @@ can import this one unchanged).
 q: [B, Hq, N, D]; k, v: [B, Hkv, N, D]; Hq % Hkv == 0 and group size <= 8; causal must be True.
 The math is that of corope-exp/corope_attn_gqa_pytorch.py; forward and backward are CUDA kernels reached
 through the C ABI in include/corope_b200.h (the reference's backward is dense PyTorch).
+
+Device-side errors (an expired bounded wait; a gradient term beyond the value range of the 16-bit backward) set a
+per-device status word; every call first looks at a pinned host mirror of it and raises RuntimeError if an earlier
+call set it (see fused_rope_attn.py).
 """
 
 import torch
@@ -44,12 +48,14 @@ def _forward(q, k, v, causal, sm_scale, theta):
     lse2 = torch.empty((BATCH, H_Q, N_CTX), device=q.device, dtype=torch.float32)
     a_diag = torch.empty((BATCH, H_KV, N_CTX), device=q.device, dtype=torch.float32)
     ws, ws_bytes = _ext.workspace(_ext.OP_GQA_FWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
         rc = _ext.lib().corope_gqa_fwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lse2.data_ptr(), a_diag.data_ptr(),
             BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
             ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
     _ext.raise_for_status(rc, "corope_gqa_fwd")
+    _ext.post_call(q.device)
     return qc, kc, vc, o, lse2, a_diag
 
 
@@ -62,6 +68,7 @@ def _backward(q, k, v, o, lse2, a_diag, grad_output, sm_scale, theta):
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
     ws, ws_bytes = _ext.workspace(_ext.OP_GQA_BWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
         rc = _ext.lib().corope_gqa_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(), lse2.data_ptr(),
@@ -69,6 +76,7 @@ def _backward(q, k, v, o, lse2, a_diag, grad_output, sm_scale, theta):
             BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
             ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
     _ext.raise_for_status(rc, "corope_gqa_bwd")
+    _ext.post_call(q.device)
     return dq, dk, dv
 
 

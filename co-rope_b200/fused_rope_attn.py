@@ -6,6 +6,11 @@ q, k, v: [B, H, N, D] CUDA tensors of one dtype (bf16, fp16 or fp32).  freqs_cos
 ("cat" layout of precompute_freqs_cis) or [N, D/2]; only columns [0, D/2) are read, as in the
 reference (fused_rope_attn.py:88-93).  Positional-only, like torch.autograd.Function.apply.
 The CUDA kernels are reached through the C ABI in include/corope_b200.h.
+
+Device-side errors: kernels never trap; a bounded wait that runs out sets a per-device status word.  Every call
+first looks at a pinned host mirror of that word (refreshed by a side stream after each call, no synchronisation)
+and raises RuntimeError, clearing the word, if an earlier call set it; `_ext.check_status()` does the same with a
+synchronisation.
 """
 
 import torch
@@ -52,12 +57,14 @@ def _forward(q, k, v, causal, sm_scale, freqs_cos, freqs_sin):
     o = torch.empty_like(qc)
     M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
     ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD, B, H, H, N, D, q.dtype, q.device)
+    _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
         rc = _ext.lib().corope_rope_attn_fwd(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), tstride,
             o.data_ptr(), M.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
             ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
     _ext.raise_for_status(rc, "corope_rope_attn_fwd")
+    _ext.post_call(q.device)
     return qc, kc, vc, o, M, cos, sin, tstride
 
 
@@ -71,6 +78,7 @@ def _backward(q, k, v, o, M, cos, sin, tstride, do, causal, sm_scale):
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
     ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD, B, H, H, N, D, q.dtype, q.device)
+    _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
         rc = _ext.lib().corope_rope_attn_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
@@ -78,6 +86,7 @@ def _backward(q, k, v, o, M, cos, sin, tstride, do, causal, sm_scale):
             B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
             ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
     _ext.raise_for_status(rc, "corope_rope_attn_bwd")
+    _ext.post_call(q.device)
     return dq, dk, dv
 
 

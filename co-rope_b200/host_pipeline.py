@@ -9,6 +9,7 @@ call costs about one direction's copy time instead of both directions plus the k
 
 import torch
 
+from . import _ext
 from . import fused_rope_attn as _rope
 from . import flash_attn_co_rope_gqa_triton as _gqa
 
@@ -60,6 +61,13 @@ def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=
     s_in.wait_stream(cur)
     s_out.wait_stream(cur)
     bounds = [(n_units * c) // chunks for c in range(chunks + 1)]
+    with _ext.batched_status(cur.device):
+        _run_chunks(bounds, chunks, uq, uk, uv, udo, uo, udq, udk, udv, G, N, D, cur, s_in, s_out, sm_scale, freqs_cos, freqs_sin, theta)
+    cur.wait_stream(s_out)
+    return ho, hdq, hdk, hdv
+
+
+def _run_chunks(bounds, chunks, uq, uk, uv, udo, uo, udq, udk, udv, G, N, D, cur, s_in, s_out, sm_scale, freqs_cos, freqs_sin, theta):
     for c in range(chunks):
         lo, hi = bounds[c], bounds[c + 1]
         n = hi - lo
@@ -89,5 +97,3 @@ def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=
             udv[lo:hi].copy_(gv.view(n, 1, N, D), non_blocking=True)
         for t in (o, gq, gk, gv):
             t.record_stream(s_out)
-    cur.wait_stream(s_out)
-    return ho, hdq, hdk, hdv

@@ -11,7 +11,15 @@
  * expires writes a non-zero code into `*status_word` (device memory, may be NULL) and the
  * kernel exits cleanly.  While the word is non-zero, later tensor-core launches that are given the
  * same word return without computing (their outputs are then undefined): read and clear it on the
- * host after synchronising.
+ * host after synchronising.  The Python modules of this package do that for the caller: every call
+ * first looks at a pinned host mirror of the word that the previous call's stream refreshed, and
+ * raises (and clears the word) if it was set.
+ *
+ * Supported value range of 16-bit inputs: the tensor-core kernels feed fp16 operands to the MMAs
+ * (rotated Q / K, dS) with saturating conversions, so results are exact in kind for |q|, |k| up to
+ * a few hundred and for gradient magnitudes |dO| up to about 2^10; beyond that single products may
+ * clamp to +-65504 and results lose accuracy without becoming inf / NaN.  fp32 inputs have no such
+ * limit (fp32 arithmetic throughout).
  *
  * Each entry point names the interface of the reference (Superposition09m/Co-RoPE) it stands in for.
  */
@@ -52,6 +60,7 @@ extern "C" {
 /* device-side status codes written to *status_word */
 #define COROPE_DEV_OK 0
 #define COROPE_DEV_WAIT_EXPIRED 0x1000 /* | barrier id: a bounded mbarrier wait ran out */
+#define COROPE_DEV_RANGE 0x2000        /* a gradient term left the range of the 16-bit Co-RoPE backward and was clamped */
 
 int corope_abi_version(void);
 const char* corope_status_string(int status);
@@ -137,19 +146,6 @@ int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, c
                    int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
                    void* workspace, size_t workspace_bytes,
                    int* status_word, void* stream);
-
-/*
- * Selects the kernel family for 16-bit inputs: 0 = automatic (tensor-core kernels where the shape
- * allows, otherwise the general kernels), 1 = always the general (CUDA-core, fp32-arithmetic)
- * kernels.  Process-wide; meant for tests and A/B timing.  Returns the previous value.
- */
-int corope_set_kernel_policy(int policy);
-
-/* Which kernel family the last call of each op used on this thread's process: 0 general, 1 tensor-core. */
-int corope_last_kernel_family(int op);
-
-/* Diagnostic: number of GPU kernel launches this library has issued in this process so far. */
-uint64_t corope_launch_count(void);
 
 #ifdef __cplusplus
 }

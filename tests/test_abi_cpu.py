@@ -11,9 +11,12 @@ from helpers import ext
 
 
 def _declared_symbols():
-    text = open(ext.HEADER_PATH).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(corope_[a-z0-9_]+)\s*\(", text)))
+    syms = set()
+    for path in (ext.HEADER_PATH, ext.DEBUG_HEADER_PATH):   # the drop-in surface and the diagnostics header
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        syms |= set(re.findall(r"\b(corope_[a-z0-9_]+)\s*\(", text))
+    return sorted(syms)
 
 
 def test_library_is_built_and_exports_every_declared_symbol():
@@ -21,7 +24,7 @@ def test_library_is_built_and_exports_every_declared_symbol():
     assert os.path.exists(ext.LIB_PATH)
     L = ctypes.CDLL(ext.LIB_PATH)
     syms = _declared_symbols()
-    assert "corope_rope_attn_fwd" in syms and "corope_gqa_bwd" in syms and len(syms) >= 9
+    assert "corope_rope_attn_fwd" in syms and "corope_gqa_bwd" in syms and "corope_debug_expire_wait" in syms and len(syms) >= 12
     for s in syms:
         assert hasattr(L, s), s
 

@@ -9,11 +9,18 @@ import pytest
 import torch
 
 import oracle
-from helpers import (corope_attention, draw, excess, ext, fused_attention, load_gold, maxdiff, rope_inputs, run_corope, run_fused)
+import os
+
+from helpers import (check16, corope_attention, draw, excess, ext, fused_attention, load_gold, maxdiff, rope_inputs, run_corope, run_fused)
 
 pytestmark = pytest.mark.gpu
 
 TOL_FWD_16, TOL_BWD_16, TOL_32 = 1e-2, 2e-2, 1e-4
+
+
+def _label():
+    """Name of the running test case, for the parity report."""
+    return os.environ.get("PYTEST_CURRENT_TEST", "?").split("::")[-1].split(" ")[0]
 
 
 @pytest.mark.parametrize("name", ["rope_a", "rope_b", "rope_c"])
@@ -66,9 +73,9 @@ def test_fused_rope_general_kernels_16bit(dtype, shape, causal):
     o, dq, dk, dv = run_fused(q, k, v, do, causal, s, cos[:, : D // 2].contiguous(), sin[:, : D // 2].contiguous())
     ro = oracle.rope_attn_fwd(q, k, v, causal, s, cos, sin)
     rdq, rdk, rdv = oracle.rope_attn_bwd(q, k, v, do, causal, s, cos, sin)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
     for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
-        assert excess(got, ref, TOL_BWD_16, dtype) <= 0
+        check16(_label() + " grad", got, ref, TOL_BWD_16, dtype)
 
 
 @pytest.mark.parametrize("shape", [(2, 4, 512, 64), (1, 8, 1024, 128), (4, 16, 2048, 64)])
@@ -106,7 +113,7 @@ def test_fused_rope_tensor_core_forward(dtype, shape):
     o, _, _, _ = run_fused(q, k, v, None, True, D ** -0.5, cos, sin)
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
     ro, lse2, _ = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin, return_aux=True)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -119,9 +126,9 @@ def test_fused_rope_tensor_core_backward(dtype, shape):
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
     ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
-        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -140,9 +147,9 @@ def test_fused_rope_tensor_core_non_causal(dtype, shape):
     else:
         ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, False, D ** -0.5, cos, sin, rows=512)
         refs = (rdq, rdk, rdv)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), refs):
-        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, dtype)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -156,9 +163,9 @@ def test_fused_rope_head_dim_64_on_tensor_cores(dtype, shape, causal):
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
     assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
     ro = oracle.rope_attn_fwd(q, k, v, causal, D ** -0.5, cos, sin)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, causal, D ** -0.5, cos, sin)):
-        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, dtype)
 
 
 def test_fused_rope_llama7b_4k_heads_bf16():
@@ -168,9 +175,9 @@ def test_fused_rope_llama7b_4k_heads_bf16():
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
     o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
     ro, lse2, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024)
-    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, torch.bfloat16, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
-        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
 
 
 def test_fused_rope_identity_tables_and_first_row():
@@ -210,9 +217,9 @@ def test_fused_rope_llama70b_1k_heads_bf16():
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
     o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
     ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
-    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, torch.bfloat16, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
-        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
 
 
 def test_fused_rope_long_context_16k_full_gradients():
@@ -222,45 +229,62 @@ def test_fused_rope_long_context_16k_full_gradients():
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
     o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
     ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024)
-    assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, torch.bfloat16, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
-        assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
 
 
-def test_fused_rope_long_context_64k_sampled_rows():
-    # one head of the Long-64K configuration (N = 65536): O and dQ on the first, a middle and the last block of 1024 rows
+def test_fused_rope_long_context_64k_full_head():
+    # one head of the Long-64K configuration (N = 65536): every row of O and all three gradients (dK and dV over every key
+    # block) against the row-blocked oracle
     B, H, N, D = 1, 1, 65536, 128
     q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=9)
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
-    o, dq, _, _ = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
-    blocks = [0, 37, 63]
-    ro, _, rdq, _, _ = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024, row_blocks=blocks)
-    for b in blocks:
-        sl = slice(b * 1024, (b + 1) * 1024)
-        assert excess(o[:, :, sl], ro[:, :, sl], TOL_FWD_16, torch.bfloat16) <= 0
-        assert excess(dq[:, :, sl], rdq[:, :, sl], TOL_BWD_16, torch.bfloat16) <= 0
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q, k, v, do, True, D ** -0.5, cos, sin, rows=1024)
+    check16(_label() + " O", o, ro, TOL_FWD_16, torch.bfloat16, strict=True)
+    for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
 
 
-def test_corope_config4_unit_bf16():
-    # one (batch, KV head) unit of the Co-RoPE configuration (group of 4 query heads, D = 128): full check at N = 512,
-    # O / dQ on sampled row blocks at the full N = 2048
+def test_fused_rope_llama7b_4k_full_launch_heads_across_chunks():
+    # the whole Llama-7B-4K launch (B = 2, H = 32: 64 heads, i.e. 8 head chunks of the forward scheduler and 16 of the
+    # backward's) with four heads from different chunks and both batch entries checked against the oracle
+    B, H, N, D = 2, 32, 4096, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=16)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    for t in (o, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    for b, h in ((0, 0), (0, 13), (1, 7), (1, 31)):
+        sl = (slice(b, b + 1), slice(h, h + 1))
+        ro, _, rdq, rdk, rdv = oracle.rope_attn_fwd_bwd_chunked(q[sl], k[sl], v[sl], do[sl], True, D ** -0.5, cos, sin, rows=1024)
+        tag = "%s b%d h%d" % (_label(), b, h)
+        check16(tag + " O", o[sl], ro, TOL_FWD_16, torch.bfloat16, strict=True)
+        for name, got, ref in zip("qkv", (dq[sl], dk[sl], dv[sl]), (rdq, rdk, rdv)):
+            check16(tag + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
+
+
+def test_corope_config4_units_bf16():
+    # (batch, KV head) units of the Co-RoPE configuration (groups of 4 query heads, D = 128): one unit at N = 512, and a
+    # launch of two units at the configured N = 2048 -- O, dQ, dK and dV of both units in full (the oracle runs every
+    # block of 32 query rows, so dK / dV are complete sums)
     D, G = 128, 4
-    for N, blocks in ((512, None), (2048, [0, 31, 63])):
-        q = draw((1, G, N, D), 21, torch.bfloat16)
-        k = draw((1, 1, N, D), 22, torch.bfloat16)
-        v = draw((1, 1, N, D), 23, torch.bfloat16)
-        do = draw((1, G, N, D), 24, torch.bfloat16)
+    for N, units in ((512, 1), (2048, 2)):
+        q = draw((1, G * units, N, D), 21, torch.bfloat16)
+        k = draw((1, units, N, D), 22, torch.bfloat16)
+        v = draw((1, units, N, D), 23, torch.bfloat16)
+        do = draw((1, G * units, N, D), 24, torch.bfloat16)
         o, dq, dk, dv = run_corope(q, k, v, do, D ** -0.5, 10000.0)
-        ro, _, _, rdq, rdk, rdv = oracle.corope_gqa_fwd_bwd_chunked(q, k, v, do, D ** -0.5, 10000.0, rows=32, row_blocks=blocks)
-        if blocks is None:
-            assert excess(o, ro, TOL_FWD_16, torch.bfloat16) <= 0
-            for name, got, ref in zip("qkv", (dq, dk, dv), (rdq, rdk, rdv)):
-                assert excess(got, ref, TOL_BWD_16, torch.bfloat16) <= 0, "d" + name
-        else:
-            for b in blocks:
-                sl = slice(b * 32, (b + 1) * 32)
-                assert excess(o[:, :, sl], ro[:, :, sl], TOL_FWD_16, torch.bfloat16) <= 0
-                assert excess(dq[:, :, sl], rdq[:, :, sl], TOL_BWD_16, torch.bfloat16) <= 0
+        assert ext.lib().corope_last_kernel_family(ext.OP_GQA_FWD) == 1 and ext.lib().corope_last_kernel_family(ext.OP_GQA_BWD) == 1
+        for u in range(units):
+            hq, hk = slice(u * G, (u + 1) * G), slice(u, u + 1)
+            ro, _, _, rdq, rdk, rdv = oracle.corope_gqa_fwd_bwd_chunked(q[:, hq], k[:, hk], v[:, hk], do[:, hq], D ** -0.5, 10000.0, rows=32)
+            tag = "%s N%d unit%d" % (_label(), N, u)
+            check16(tag + " O", o[:, hq], ro, TOL_FWD_16, torch.bfloat16, strict=True)
+            check16(tag + " dQ", dq[:, hq], rdq, TOL_BWD_16, torch.bfloat16)
+            check16(tag + " dK", dk[:, hk], rdk, TOL_BWD_16, torch.bfloat16)
+            check16(tag + " dV", dv[:, hk], rdv, TOL_BWD_16, torch.bfloat16)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -278,9 +302,9 @@ def test_corope_tensor_core_groups(dtype, cfg):
     assert ext.lib().corope_last_kernel_family(ext.OP_GQA_FWD) == 1
     assert ext.lib().corope_last_kernel_family(ext.OP_GQA_BWD) == 1
     ro = oracle.corope_gqa_fwd(q, k, v, True, D ** -0.5, 10000.0)
-    assert excess(o, ro, TOL_FWD_16, dtype) <= 0
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
     for name, got, ref in zip("qkv", (dq, dk, dv), oracle.corope_gqa_bwd(q, k, v, do, True, D ** -0.5, 10000.0)):
-        assert excess(got, ref, TOL_BWD_16, dtype) <= 0, "d" + name
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, dtype)
 
 
 def test_host_pipeline_matches_direct_call():
@@ -324,3 +348,130 @@ def test_fused_rope_tensor_core_results_are_reproducible():
         assert torch.equal(first[2], again[2]), "dK differs between runs"
         assert torch.equal(first[3], again[3]), "dV differs between runs"
         assert maxdiff(first[1], again[1]) < 1e-2
+
+
+def test_fused_rope_head_dim_64_half_tables_with_poisoned_surroundings():
+    # D = 64 on the tensor-core path with [N, D/2] tables that are the tail of a larger NaN-filled buffer: nothing outside
+    # the tables' own [N, 32] columns may be read (a read past the end of a row would pull NaN into the results)
+    B, H, N, D = 1, 2, 512, 64
+    dtype = torch.bfloat16
+    q, k, v, do = rope_inputs(B, H, N, D, dtype, seed=18)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    bufs = []
+    for t in (cos, sin):
+        buf = torch.full((3 * N * 32,), float("nan"), device="cuda")
+        buf[N * 32: 2 * N * 32] = t[:, :32].contiguous().reshape(-1).cuda()
+        bufs.append(buf[N * 32: 2 * N * 32].view(N, 32))
+    o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, bufs[0], bufs[1])
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1 and ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    for t in (o, dq, dk, dv):
+        assert torch.isfinite(t).all()
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    check16(_label() + " O", o, ro, TOL_FWD_16, dtype, strict=True)
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, dtype)
+
+
+@pytest.mark.parametrize("policy", [0, 2])
+def test_fused_rope_in_kernel_rotation_policy(policy):
+    # policy 2: the tensor-core kernels rotate K (forward) and Q (backward) tiles in shared memory themselves -- no rotated
+    # copy is written to the workspace; results must match the oracle like the default variant's
+    B, H, N, D = 2, 3, 1024, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=19)
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    prev = ext.lib().corope_set_kernel_policy(policy)
+    try:
+        n0 = ext.lib().corope_launch_count()
+        o, dq, dk, dv = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+        launches = ext.lib().corope_launch_count() - n0
+    finally:
+        ext.lib().corope_set_kernel_policy(prev)
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1 and ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    if policy == 2:   # forward: table pack + main kernel; backward: delta + table pack + main kernel + dQ finalize -- no pre-rotation kernels
+        assert launches == 6, launches
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    check16(_label() + " O", o, ro, TOL_FWD_16, torch.bfloat16, strict=True)
+    for name, got, ref in zip("qkv", (dq, dk, dv), oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin)):
+        check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
+
+
+@pytest.mark.parametrize("qk_scale,vdo_scale", [(1.0, 16.0), (1.0, 64.0), (1.0, 1024.0), (2.0, 16.0)])
+def test_fused_rope_scaled_inputs_bf16(qk_scale, vdo_scale):
+    # inputs far from N(0,1).  v and dO (the linear paths: P V, dV = P^T dO, dP = dO V^T) multiplied by 16, 64 and 1024 --
+    # the magnitudes a loss-scaled training step produces -- and q, k by 2 (scores x 4).  O scales with v, dV with dO, dQ / dK
+    # with both, so each tolerance is relative to the magnitude of its reference tensor; everything must stay finite.
+    # (Scores far beyond that are outside what 16-bit operands can resolve: the error of a score grows as |score| * 2^-11,
+    # for this kernel as for the reference's fp16 Triton kernels; see the value-range note in the C header.)
+    B, H, N, D = 1, 2, 512, 128
+    q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=20)
+    q, k, v, do = q * qk_scale, k * qk_scale, v * vdo_scale, do * vdo_scale
+    cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    outs = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
+    ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
+    refs = (ro,) + tuple(oracle.rope_attn_bwd(q, k, v, do, True, D ** -0.5, cos, sin))
+    for name, got, ref, tol in zip(("O", "dQ", "dK", "dV"), outs, refs, (TOL_FWD_16, TOL_BWD_16, TOL_BWD_16, TOL_BWD_16)):
+        assert torch.isfinite(got).all(), name
+        mag = max(1.0, ref.abs().max().item())
+        check16("%s qk x%g v,dO x%g %s (tolerance x %.0f)" % (_label(), qk_scale, vdo_scale, name, mag), got, ref, tol * mag, torch.bfloat16)
+
+
+@pytest.mark.parametrize("scale", [16.0, 1024.0])
+def test_corope_scaled_gradients_bf16(scale):
+    # output gradients as a loss-scaled fp16 / bf16 training step produces them (dO x 16, x 1024): dK of the tensor-core
+    # backward is summed in fixed point with a range-safe slow path, so either the gradients are within (magnitude-relative)
+    # tolerance or the status word reports that a term was clamped -- never a silently wrapped sum
+    B, Hq, Hkv, N, D = 1, 4, 1, 256, 128
+    q = draw((B, Hq, N, D), 51, torch.bfloat16)
+    k = draw((B, Hkv, N, D), 52, torch.bfloat16)
+    v = draw((B, Hkv, N, D), 53, torch.bfloat16)
+    do = draw((B, Hq, N, D), 54, torch.bfloat16) * scale
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    o = corope_attention(qd, kd, vd, True, D ** -0.5, 10000.0)
+    o.backward(do.cuda())
+    assert ext.lib().corope_last_kernel_family(ext.OP_GQA_BWD) == 1
+    try:
+        ext.check_status()
+        reported = False
+    except RuntimeError as e:
+        assert "0x2000" in str(e)
+        reported = True
+    refs = oracle.corope_gqa_bwd(q, k, v, do, True, D ** -0.5, 10000.0)
+    for name, got, ref in zip(("dQ", "dK", "dV"), (qd.grad, kd.grad, vd.grad), refs):
+        got = got.float().cpu()
+        assert torch.isfinite(got).all(), name
+        if not reported:
+            mag = max(1.0, ref.abs().max().item())
+            check16("%s x%d %s (tolerance x %.0f)" % (_label(), int(scale), name, mag), got, ref, TOL_BWD_16 * mag, torch.bfloat16)
+
+
+def test_bounded_wait_expiry_is_reported_and_cleared():
+    # the failure-detection path of the kernels: a wait that runs out records COROPE_DEV_WAIT_EXPIRED | id in the status
+    # word and the kernel returns.  A test-only kernel waits (bounded, 2000 polls) on a barrier nobody arrives at.
+    dev = torch.device("cuda", 0)
+    lib = ext.lib()
+    ext.check_status(dev)
+    word = ext.status_word(dev)
+    rc = lib.corope_debug_expire_wait(word.data_ptr(), 2000, torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0x1000 | 0x7e
+    # a launch that is handed a set word returns without computing (outputs keep their previous contents) ...
+    B, H, N, D = 1, 1, 256, 128
+    q, k, v, _ = (t.cuda() for t in rope_inputs(B, H, N, D, torch.bfloat16, seed=21))
+    cos, sin = (t.cuda() for t in oracle.precompute_freqs_cis(D, N, 10000.0))
+    ext.post_call(dev)          # what every entry point does after its launch: refresh the host mirror of the word
+    torch.cuda.synchronize()
+    # ... and the next call through the drop-in entry point raises before launching anything, and clears the word
+    with pytest.raises(RuntimeError, match="0x107e"):
+        fused_attention(q, k, v, True, D ** -0.5, cos, sin)
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0
+    o = fused_attention(q, k, v, True, D ** -0.5, cos, sin)
+    ext.check_status(dev)
+    ro = oracle.rope_attn_fwd(q.cpu(), k.cpu(), v.cpu(), True, D ** -0.5, cos.cpu(), sin.cpu())
+    check16(_label() + " O after clearing", o.float().cpu(), ro, TOL_FWD_16, torch.bfloat16, strict=True)
+    # check_status() itself: synchronising form of the same report
+    lib.corope_debug_expire_wait(word.data_ptr(), 100, torch.cuda.current_stream(dev).cuda_stream)
+    with pytest.raises(RuntimeError, match="bounded"):
+        ext.check_status(dev)
+    ext.check_status(dev)

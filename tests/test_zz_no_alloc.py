@@ -2,9 +2,9 @@
 
 It serves callers that cannot allocate device memory where they call the library (a fixed, fully planned memory
 arena; a hard memory budget; a point where an allocation would stall the device), so its scratch is a fixed array
-inside the library.  The test checks two calls in a row against the regular entry point (which takes a caller
-workspace): the second call uses a different length and different tables, so it would fail if anything left in the
-shared array by the first call were read.  This file sorts last so that a run stopping at the first failure has
+inside the library.  The test checks calls in a row against the regular entry point (which takes a caller
+workspace) and against the CPU oracle: each call uses a different length, different tables, dtype or mask, so it would
+fail if anything left in the shared array by an earlier call were read.  This file sorts last so that a run stopping at the first failure has
 already run every other test.
 """
 
@@ -42,18 +42,50 @@ def _call(fn_noalloc, q, k, v, cos, sin, causal, sm_scale):
 
 def test_noalloc_forward_matches_regular_entry_point_twice():
     dev = torch.device("cuda", 0)
-    cases = [((1, 2, 512, 128), 10000.0, 3), ((2, 1, 256, 128), 500.0, 4)]   # both take the tensor-core kernel (which needs the table)
-    for shape, theta, seed in cases:
+    lib = ext.lib()
+    # all take the tensor-core kernel (which needs the table); successive calls differ in length, tables, dtype and mask, so
+    # anything read from what an earlier call left in the shared array would show
+    cases = [((1, 2, 512, 128), 10000.0, 3, torch.bfloat16, True), ((2, 1, 256, 128), 500.0, 4, torch.bfloat16, True),
+             ((1, 2, 384, 128), 10000.0, 5, torch.float16, True), ((1, 1, 256, 128), 2000.0, 6, torch.bfloat16, False)]
+    for shape, theta, seed, dtype, causal in cases:
         B, H, N, D = shape
-        q, k, v, _ = (t.to(dev) for t in rope_inputs(B, H, N, D, torch.bfloat16, seed=seed))
-        cos, sin = oracle.precompute_freqs_cis(D, N, theta)
-        cos, sin = cos.to(dev), sin.to(dev)
-        o_ref, lse_ref = _call(False, q, k, v, cos, sin, True, D ** -0.5)
-        o_new, lse_new = _call(True, q, k, v, cos, sin, True, D ** -0.5)
-        assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
+        hq, hk, hv, _ = rope_inputs(B, H, N, D, dtype, seed=seed)
+        q, k, v = (t.to(dev) for t in (hq, hk, hv))
+        hcos, hsin = oracle.precompute_freqs_cis(D, N, theta)
+        cos, sin = hcos.to(dev), hsin.to(dev)
+        o_ref, lse_ref = _call(False, q, k, v, cos, sin, causal, D ** -0.5)
+        assert lib.corope_last_kernel_family(ext.OP_ROPE_FWD) == 1
+        # make the general kernels the last family on record, so that the assertion below is about the call that follows
+        prev = lib.corope_set_kernel_policy(1)
+        _call(False, q, k, v, cos, sin, causal, D ** -0.5)
+        lib.corope_set_kernel_policy(prev)
+        assert lib.corope_last_kernel_family(ext.OP_ROPE_FWD) == 0
+        o_new, lse_new = _call(True, q, k, v, cos, sin, causal, D ** -0.5)
+        assert lib.corope_last_kernel_family(ext.OP_ROPE_FWD) == 1   # recorded by the allocation-free entry point itself
         assert not torch.isnan(o_new).any() and not torch.isnan(lse_new).any()
         assert (o_new.float() - o_ref.float()).abs().max().item() <= 1e-2
         assert (lse_new - lse_ref).abs().max().item() <= 1e-3
+        # and against the CPU oracle, so that a fault shared by both entry points cannot hide
+        ro, rlse2, _ = oracle.rope_attn_fwd(hq, hk, hv, causal, D ** -0.5, hcos, hsin, return_aux=True)
+        assert (o_new.float().cpu() - ro).abs().max().item() <= 1e-2
+        assert (lse_new.cpu() - rlse2).abs().max().item() <= 2e-2
+
+
+def test_noalloc_follows_the_kernel_policy():
+    dev = torch.device("cuda", 0)
+    lib = ext.lib()
+    B, H, N, D = 1, 1, 256, 128
+    hq, hk, hv, _ = rope_inputs(B, H, N, D, torch.bfloat16, seed=7)
+    q, k, v = (t.to(dev) for t in (hq, hk, hv))
+    hcos, hsin = oracle.precompute_freqs_cis(D, N, 10000.0)
+    prev = lib.corope_set_kernel_policy(1)
+    try:
+        o, _ = _call(True, q, k, v, hcos.to(dev), hsin.to(dev), True, D ** -0.5)
+    finally:
+        lib.corope_set_kernel_policy(prev)
+    assert lib.corope_last_kernel_family(ext.OP_ROPE_FWD) == 0
+    ro = oracle.rope_attn_fwd(hq, hk, hv, True, D ** -0.5, hcos, hsin)
+    assert (o.float().cpu() - ro).abs().max().item() <= 1e-2
 
 
 def test_noalloc_rejects_sizes_beyond_the_fixed_array():
