@@ -511,8 +511,9 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.tolist()
 
+    last = None
     for _ in range(args.warmup):
-        step(dq_, dk_, dv_, ddo)
+        last = step(dq_, dk_, dv_, ddo)   # held like in the timed loop, so that the allocator's pool has its final size before timing starts
     sync_all()
     pkg.check_status()
 
@@ -702,7 +703,8 @@ def main():
 
     peaks = load_peaks()
     if sustained is not None:
-        sustained["frac_of_sustained_peak"] = sustained["value"] / peaks["tflops_sustained"] if kind == "rope" else None
+        sustained["value_per_gpu"] = sustained["value"] / world
+        sustained["frac_of_sustained_peak"] = sustained["value"] / world / peaks["tflops_sustained"] if kind == "rope" else None
         sustained["peak_sustained"] = peaks["tflops_sustained"]
     dom_is_bwd = bwd_ms >= fwd_ms
     fam = lib.corope_last_kernel_family((1 if dom_is_bwd else 0) + (0 if kind == "rope" else 2))
@@ -746,6 +748,7 @@ def main():
 
     cpu_baseline = None
     if not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)   # torchrun pins OMP_NUM_THREADS to 1; the other ranks are done by now
         t1, f1, how = cpu_reference_sample(kind, Hq, Hkv, N, D, 1)
         n_cpu = int(max(1, min(B * Hkv, 12.0 / max(t1, 1e-3))))
         t, f, how = cpu_reference_sample(kind, Hq, Hkv, N, D, n_cpu)

@@ -395,16 +395,18 @@ def test_fused_rope_in_kernel_rotation_policy(policy):
         check16(_label() + " d" + name, got, ref, TOL_BWD_16, torch.bfloat16)
 
 
-@pytest.mark.parametrize("qk_scale,vdo_scale", [(1.0, 16.0), (1.0, 64.0), (1.0, 1024.0), (2.0, 16.0)])
-def test_fused_rope_scaled_inputs_bf16(qk_scale, vdo_scale):
-    # inputs far from N(0,1).  v and dO (the linear paths: P V, dV = P^T dO, dP = dO V^T) multiplied by 16, 64 and 1024 --
-    # the magnitudes a loss-scaled training step produces -- and q, k by 2 (scores x 4).  O scales with v, dV with dO, dQ / dK
-    # with both, so each tolerance is relative to the magnitude of its reference tensor; everything must stay finite.
+@pytest.mark.parametrize("qk_scale,v_scale,do_scale", [(1.0, 16.0, 16.0), (1.0, 64.0, 64.0), (1.0, 1.0, 256.0), (1.0, 1.0, 1024.0), (2.0, 16.0, 16.0)])
+def test_fused_rope_scaled_inputs_bf16(qk_scale, v_scale, do_scale):
+    # inputs far from N(0,1).  v and dO (the linear paths: P V, dV = P^T dO, dP = dO V^T) multiplied by 16 and 64, dO alone by
+    # 256 and 1024 -- the magnitudes a loss-scaled training step produces -- and q, k by 2 (scores x 4).  O scales with v, dV
+    # with dO, dQ / dK with both, so each tolerance is relative to the magnitude of its reference tensor; everything must stay
+    # finite.  The limit is the fp16 operand dS = P (dP - delta) of the dK / dQ products: |dO| |v| sqrt(D) has to stay below
+    # 65504, which v, dO x 1024 together would not.
     # (Scores far beyond that are outside what 16-bit operands can resolve: the error of a score grows as |score| * 2^-11,
     # for this kernel as for the reference's fp16 Triton kernels; see the value-range note in the C header.)
     B, H, N, D = 1, 2, 512, 128
     q, k, v, do = rope_inputs(B, H, N, D, torch.bfloat16, seed=20)
-    q, k, v, do = q * qk_scale, k * qk_scale, v * vdo_scale, do * vdo_scale
+    q, k, v, do = q * qk_scale, k * qk_scale, v * v_scale, do * do_scale
     cos, sin = oracle.precompute_freqs_cis(D, N, 10000.0)
     outs = run_fused(q, k, v, do, True, D ** -0.5, cos, sin)
     ro = oracle.rope_attn_fwd(q, k, v, True, D ** -0.5, cos, sin)
@@ -412,7 +414,7 @@ def test_fused_rope_scaled_inputs_bf16(qk_scale, vdo_scale):
     for name, got, ref, tol in zip(("O", "dQ", "dK", "dV"), outs, refs, (TOL_FWD_16, TOL_BWD_16, TOL_BWD_16, TOL_BWD_16)):
         assert torch.isfinite(got).all(), name
         mag = max(1.0, ref.abs().max().item())
-        check16("%s qk x%g v,dO x%g %s (tolerance x %.0f)" % (_label(), qk_scale, vdo_scale, name, mag), got, ref, tol * mag, torch.bfloat16)
+        check16("%s qk x%g v x%g dO x%g %s (tolerance x %.0f)" % (_label(), qk_scale, v_scale, do_scale, name, mag), got, ref, tol * mag, torch.bfloat16)
 
 
 @pytest.mark.parametrize("scale", [16.0, 1024.0])
