@@ -22,6 +22,7 @@ SOURCES = ["abi.cu", "rope_general.cu", "rope_fwd_sm100.cu", "rope_bwd_sm100.cu"
 
 DTYPE_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 OP_ROPE_FWD, OP_ROPE_BWD, OP_GQA_FWD, OP_GQA_BWD = 0, 1, 2, 3
+OP_ROPE_FWD_FREQS, OP_ROPE_BWD_FREQS, OP_FLASH_FWD, OP_FLASH_BWD = 4, 5, 6, 7
 
 _lock = threading.Lock()
 _lib = None
@@ -86,6 +87,9 @@ def lib():
             L.corope_set_kernel_policy.argtypes = [i32]
             L.corope_last_kernel_family.restype = i32
             L.corope_last_kernel_family.argtypes = [i32]
+            if hasattr(L, "corope_debug_synth_tables"):
+                L.corope_debug_synth_tables.restype = i32
+                L.corope_debug_synth_tables.argtypes = [vp, vp, vp, i32, i32, vp]
             if hasattr(L, "corope_debug_expire_wait"):
                 L.corope_debug_expire_wait.restype = i32
                 L.corope_debug_expire_wait.argtypes = [vp, ctypes.c_uint, vp]
@@ -96,6 +100,14 @@ def lib():
             L.corope_rope_attn_bwd.restype = i32
             L.corope_rope_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32,
                                                vp, sz, vp, vp]
+            L.corope_rope_attn_fwd_freqs.restype = i32
+            L.corope_rope_attn_fwd_freqs.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
+            L.corope_rope_attn_bwd_freqs.restype = i32
+            L.corope_rope_attn_bwd_freqs.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
+            L.corope_flash_attn_fwd.restype = i32
+            L.corope_flash_attn_fwd.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
+            L.corope_flash_attn_bwd.restype = i32
+            L.corope_flash_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
             L.corope_gqa_fwd.restype = i32
             L.corope_gqa_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp, sz, vp, vp]
             L.corope_gqa_bwd.restype = i32

@@ -15,7 +15,7 @@ constexpr size_t kAlign = 256;
 bool head_dim_ok(int D) { return D == 32 || D == 64 || D == 128; }
 
 struct RopeWorkspace {
-    size_t packed_tab, rot, delta, dq_acc, pad[5], total;
+    size_t packed_tab, synth_cos, synth_sin, rot, delta, dq_acc, pad[5], total;
 };
 
 // 16-bit problems with D = 64 and N % 128 == 0 run zero-padded to D = 128 on the tensor-core kernels (half of the MMA work
@@ -23,28 +23,41 @@ struct RopeWorkspace {
 // padded copies.
 bool rope_d64_padded(int N, int D, int dtype) { return D == 64 && dtype != COROPE_DTYPE_F32 && N % 128 == 0; }
 
-RopeWorkspace rope_workspace_layout(bool bwd, int B, int H, int N, int D, int dtype) {
+// Hq query heads, Hkv K / V heads (equal for the fused-RoPE ops).  `synth`: room for fp32 cos / sin tables [N, D/2] that the
+// entry points taking frequencies instead of tables fill in.
+RopeWorkspace rope_workspace_layout(bool bwd, int B, int Hq, int Hkv, int N, int D, int dtype, bool synth) {
     RopeWorkspace w{};
     const bool padded = rope_d64_padded(N, D, dtype);
     const int Dk = padded ? 128 : D;                 // head dimension the kernels see
     const bool tc = dtype != COROPE_DTYPE_F32 && Dk == 128;
-    const size_t elems = (size_t)B * H * N * Dk;
+    const size_t q_elems = (size_t)B * Hq * N * Dk, kv_elems = (size_t)B * Hkv * N * Dk;
     size_t off = 0;
     w.packed_tab = off;
     off += align_up((size_t)N * (Dk / 2) * sizeof(uint32_t) + 64, kAlign);   // + the work counter behind the table
+    if (synth) {
+        w.synth_cos = off;
+        off += align_up((size_t)N * (D / 2) * sizeof(float), kAlign);
+        w.synth_sin = off;
+        off += align_up((size_t)N * (D / 2) * sizeof(float), kAlign);
+    }
     w.rot = off;   // tensor-core kernels: fp16 copy of the rotated K (forward) / rotated and scaled Q (backward)
-    if (tc) off += align_up(elems * 2, kAlign);
+    if (tc) off += align_up((bwd ? q_elems : kv_elems) * 2, kAlign);
     if (bwd) {
         w.delta = off;
-        off += align_up((size_t)B * H * N * sizeof(float), kAlign);
+        off += align_up((size_t)B * Hq * N * sizeof(float), kAlign);
         w.dq_acc = off;
-        if (tc) off += align_up(elems * sizeof(float), kAlign);
+        if (tc) off += align_up(q_elems * sizeof(float), kAlign);
     }
-    if (padded)   // forward: q, v, o (+ k before its rotation shares o's buffer); backward: k, v, dO / dq, dk (+ q before its rotation), dv
+    if (padded) {
+        // forward: q, v, o (k before its rotation shares o's buffer: needs the larger of the two); backward: k, v, dO / dq,
+        // dk (q before its rotation shares dk's buffer), dv
+        const size_t fwd_sizes[3] = {q_elems, kv_elems, q_elems};
+        const size_t bwd_sizes[5] = {kv_elems, kv_elems, q_elems, q_elems, kv_elems};
         for (int i = 0; i < (bwd ? 5 : 3); ++i) {
             w.pad[i] = off;
-            off += align_up(elems * 2, kAlign);
+            off += align_up((bwd ? bwd_sizes[i] : fwd_sizes[i]) * 2, kAlign);
         }
+    }
     w.total = off < kAlign ? kAlign : off;
     return w;
 }
@@ -125,8 +138,12 @@ const char* corope_status_string(int status) {
 size_t corope_workspace_bytes(int op, int B, int Hq, int Hkv, int N, int D, int dtype) {
     if (B <= 0 || Hq <= 0 || Hkv <= 0 || N <= 0 || D <= 0) return 0;
     switch (op) {
-        case COROPE_OP_ROPE_FWD: return rope_workspace_layout(false, B, Hq, N, D, dtype).total;
-        case COROPE_OP_ROPE_BWD: return rope_workspace_layout(true, B, Hq, N, D, dtype).total;
+        case COROPE_OP_ROPE_FWD: return rope_workspace_layout(false, B, Hq, Hq, N, D, dtype, false).total;
+        case COROPE_OP_ROPE_BWD: return rope_workspace_layout(true, B, Hq, Hq, N, D, dtype, false).total;
+        case COROPE_OP_ROPE_FWD_FREQS: return rope_workspace_layout(false, B, Hq, Hq, N, D, dtype, true).total;
+        case COROPE_OP_ROPE_BWD_FREQS: return rope_workspace_layout(true, B, Hq, Hq, N, D, dtype, true).total;
+        case COROPE_OP_FLASH_FWD: return Hq % Hkv ? 0 : rope_workspace_layout(false, B, Hq, Hkv, N, D, dtype, false).total;
+        case COROPE_OP_FLASH_BWD: return Hq % Hkv ? 0 : rope_workspace_layout(true, B, Hq, Hkv, N, D, dtype, false).total;
         case COROPE_OP_GQA_FWD: return gqa_workspace_layout(false, B, Hq, Hkv, N, D, dtype).total;
         case COROPE_OP_GQA_BWD: return gqa_workspace_layout(true, B, Hq, Hkv, N, D, dtype).total;
         default: return 0;
@@ -139,76 +156,113 @@ int corope_set_kernel_policy(int policy) { return g_policy.exchange(policy); }
 
 int corope_last_kernel_family(int op) { return (op >= 0 && op < 4) ? g_last_family[op].load() : -1; }
 
-int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const float* cos, const float* sin, int64_t table_row_stride, void* o,
-                         float* lse2, int B, int H, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
-                         size_t workspace_bytes, int* status_word, void* stream) {
-    if (!q || !k || !v || !cos || !sin || !o || !lse2) return COROPE_ERR_NULL_POINTER;
-    if (int e = check_common(B, H, N, D, dtype)) return e;
-    RopeWorkspace w = rope_workspace_layout(false, B, H, N, D, dtype);
+}  // extern "C"
+
+namespace {
+
+// Where the rotation comes from: caller tables (cos / sin + row stride), per-pair frequencies (tables are synthesized into
+// the workspace first), or nothing at all (plain attention).
+struct Rotation {
+    const float* cos = nullptr;
+    const float* sin = nullptr;
+    int64_t stride = 0;
+    const float* inv_freq = nullptr;
+    bool none = false;
+};
+
+// ops whose kernel family is recorded: the fused-RoPE pair also stands for its variants
+constexpr int kFamFwd = COROPE_OP_ROPE_FWD, kFamBwd = COROPE_OP_ROPE_BWD;
+
+int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, void* o, float* lse2, int B, int Hq, int Hkv, int N, int D,
+                  int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !o || !lse2) return COROPE_ERR_NULL_POINTER;
+    if (!rot.none && !rot.inv_freq && (!rot.cos || !rot.sin)) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_common(B, Hq, N, D, dtype)) return e;
+    if (Hkv <= 0 || Hq % Hkv != 0) return COROPE_ERR_BAD_GROUP;
+    RopeWorkspace w = rope_workspace_layout(false, B, Hq, Hkv, N, D, dtype, rot.inv_freq != nullptr);
     if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
     cudaStream_t s = (cudaStream_t)stream;
+    if (rot.inv_freq) {
+        float* c = reinterpret_cast<float*>((char*)workspace + w.synth_cos);
+        float* sn = reinterpret_cast<float*>((char*)workspace + w.synth_sin);
+        if (int e = launch_synth_tables(rot.inv_freq, c, sn, N, D / 2, s)) return e;
+        rot.cos = c; rot.sin = sn; rot.stride = D / 2;
+    }
     RopeParams p{};
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
-    p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
-    p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
+    p.cos = rot.none ? nullptr : rot.cos; p.sin = rot.none ? nullptr : rot.sin; p.table_stride = rot.stride;
+    p.B = B; p.H = Hq; p.Hkv = Hkv; p.no_rope = rot.none ? 1 : 0;
+    p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    const int policy = g_policy.load();
+    if (policy == 0 && rope_d64_padded(N, D, dtype)) {
         // D = 64: zero-padded copies of q, k, v in the layout that keeps the rotation pairs together, the D = 128 kernels, o back
-        const size_t rows = (size_t)B * H * N;
+        const size_t rows = (size_t)B * Hq * N, kv_rows = (size_t)B * Hkv * N;
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         void* k_rot = (char*)workspace + w.rot;
         void* qp = (char*)workspace + w.pad[0];
         void* vp = (char*)workspace + w.pad[1];
         void* op = (char*)workspace + w.pad[2];   // first the padded k (until it is rotated), then the padded output
-        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, 64, s, 32)) return e;
+        if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
         if (int e = launch_pad_d64(q, qp, rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, op, rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, vp, rows, 0, dtype, s)) return e;
-        if (int e = launch_rope_prerotate(op, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, op, kv_rows, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, vp, kv_rows, 0, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(op, k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
         p.q = qp; p.k = op; p.v = vp; p.out_o = op; p.D = 128;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);
         p.k_rot = k_rot;
-        g_last_family[COROPE_OP_ROPE_FWD] = 1;
+        g_last_family[kFamFwd] = 1;
         if (int e = launch_rope_fwd_tc(p, dtype, s)) return e;
         return launch_unpad_d64(op, o, rows, 0, dtype, s);
     }
-    if (g_policy.load() != 1 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {
+    if (policy != 1 && rope_fwd_tc_supported(B, Hq, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
-        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
+        if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));
-        if (g_policy.load() == 0) {   // policy 2: every K tile is rotated in shared memory by the main kernel, nothing rotated is written to HBM
+        // policy 2: every K tile is rotated in shared memory by the main kernel, nothing rotated is written to HBM (for plain
+        // attention the "rotation" by the identity table is what brings K to fp16, the format Q is written in)
+        if (policy == 0) {
             void* k_rot = (char*)workspace + w.rot;
-            if (int e = launch_rope_prerotate(k, k_rot, tab, B, H, N, 1.0f, dtype, s)) return e;
+            if (int e = launch_rope_prerotate(k, k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
             p.k_rot = k_rot;
         }
-        g_last_family[COROPE_OP_ROPE_FWD] = 1;
+        g_last_family[kFamFwd] = 1;
         return launch_rope_fwd_tc(p, dtype, s);
     }
-    g_last_family[COROPE_OP_ROPE_FWD] = 0;
+    g_last_family[kFamFwd] = 0;
     return launch_rope_fwd_general(p, dtype, s);
 }
 
-int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, const float* cos,
-                         const float* sin, int64_t table_row_stride, void* dq, void* dk, void* dv, int B, int H, int N, int D, int dtype,
-                         int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
-    if (!q || !k || !v || !o || !d_o || !lse2 || !cos || !sin || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
-    if (int e = check_common(B, H, N, D, dtype)) return e;
-    RopeWorkspace w = rope_workspace_layout(true, B, H, N, D, dtype);
+int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, Rotation rot, void* dq,
+                  void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
+                  size_t workspace_bytes, int* status_word, void* stream) {
+    if (!q || !k || !v || !o || !d_o || !lse2 || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
+    if (!rot.none && !rot.inv_freq && (!rot.cos || !rot.sin)) return COROPE_ERR_NULL_POINTER;
+    if (int e = check_common(B, Hq, N, D, dtype)) return e;
+    if (Hkv <= 0 || Hq % Hkv != 0) return COROPE_ERR_BAD_GROUP;
+    RopeWorkspace w = rope_workspace_layout(true, B, Hq, Hkv, N, D, dtype, rot.inv_freq != nullptr);
     if (int e = check_workspace(workspace, workspace_bytes, w.total)) return e;
     cudaStream_t s = (cudaStream_t)stream;
+    if (rot.inv_freq) {
+        float* c = reinterpret_cast<float*>((char*)workspace + w.synth_cos);
+        float* sn = reinterpret_cast<float*>((char*)workspace + w.synth_sin);
+        if (int e = launch_synth_tables(rot.inv_freq, c, sn, N, D / 2, s)) return e;
+        rot.cos = c; rot.sin = sn; rot.stride = D / 2;
+    }
     RopeParams p{};
     p.q = q; p.k = k; p.v = v; p.o = o; p.d_o = d_o; p.dq = dq; p.dk = dk; p.dv = dv;
     p.lse2 = const_cast<float*>(lse2);
     p.delta = reinterpret_cast<float*>((char*)workspace + w.delta);
-    p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
-    p.B = B; p.H = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    p.cos = rot.none ? nullptr : rot.cos; p.sin = rot.none ? nullptr : rot.sin; p.table_stride = rot.stride;
+    p.B = B; p.H = Hq; p.Hkv = Hkv; p.no_rope = rot.none ? 1 : 0;
+    p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
     const int policy = g_policy.load();
-    const bool tc_direct = policy != 1 && !(policy == 0 && rope_d64_padded(N, D, dtype)) && rope_bwd_tc_supported(B, H, N, D, dtype, causal);
+    const bool tc_direct = policy != 1 && !(policy == 0 && rope_d64_padded(N, D, dtype)) && rope_bwd_tc_supported(B, Hq, N, D, dtype, causal);
     if (!(tc_direct && policy == 0))   // the tensor-core path at D = 128 computes delta in its fused pre-pass
         if (int e = launch_rope_delta(p, dtype, s)) return e;
-    if (g_policy.load() == 0 && rope_d64_padded(N, D, dtype)) {
-        const size_t rows = (size_t)B * H * N;
+    if (policy == 0 && rope_d64_padded(N, D, dtype)) {
+        const size_t rows = (size_t)B * Hq * N, kv_rows = (size_t)B * Hkv * N;
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         void* q_rot = (char*)workspace + w.rot;
         void* kp = (char*)workspace + w.pad[0];
@@ -216,26 +270,26 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
         void* dop = (char*)workspace + w.pad[2];   // padded dO; after the main kernel the padded dq (the finalize kernel writes it)
         void* dkp = (char*)workspace + w.pad[3];   // first the padded q (until it is rotated), then the padded dk
         void* dvp = (char*)workspace + w.pad[4];
-        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, 64, s, 32)) return e;
+        if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
         if (int e = launch_pad_d64(q, dkp, rows, 1, dtype, s)) return e;
-        if (int e = launch_rope_prerotate(dkp, q_rot, tab, B, H, N, sm_scale * kLog2e, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, kp, rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, vp, rows, 0, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(dkp, q_rot, tab, B, Hq, N, sm_scale * kLog2e, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, kp, kv_rows, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, vp, kv_rows, 0, dtype, s)) return e;
         if (int e = launch_pad_d64(d_o, dop, rows, 0, dtype, s)) return e;
         p.q = dkp; p.k = kp; p.v = vp; p.d_o = dop; p.dq = dop; p.dk = dkp; p.dv = dvp; p.D = 128;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
         p.q_rot = q_rot;
-        g_last_family[COROPE_OP_ROPE_BWD] = 1;
+        g_last_family[kFamBwd] = 1;
         if (int e = launch_rope_bwd_tc(p, dtype, s)) return e;
         if (int e = launch_unpad_d64(dop, dq, rows, 1, dtype, s)) return e;
-        if (int e = launch_unpad_d64(dkp, dk, rows, 1, dtype, s)) return e;
-        return launch_unpad_d64(dvp, dv, rows, 0, dtype, s);
+        if (int e = launch_unpad_d64(dkp, dk, kv_rows, 1, dtype, s)) return e;
+        return launch_unpad_d64(dvp, dv, kv_rows, 0, dtype, s);
     }
     if (tc_direct) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
-        if (int e = launch_pack_tables(cos, sin, table_row_stride, tab, N, D / 2, s)) return e;
+        if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, D / 2, s)) return e;
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * (D / 2));   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
@@ -244,11 +298,74 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
             if (int e = launch_rope_bwd_prepass(p, dtype, s)) return e;   // delta, rotated Q, cleared dQ accumulator
             p.dq_acc_zeroed = 1;
         }
-        g_last_family[COROPE_OP_ROPE_BWD] = 1;
+        g_last_family[kFamBwd] = 1;
         return launch_rope_bwd_tc(p, dtype, s);
     }
-    g_last_family[COROPE_OP_ROPE_BWD] = 0;
+    g_last_family[kFamBwd] = 0;
     return launch_rope_bwd_general(p, dtype, s);
+}
+
+Rotation from_tables(const float* cos, const float* sin, int64_t stride) {
+    Rotation r;
+    r.cos = cos; r.sin = sin; r.stride = stride;
+    return r;
+}
+Rotation from_freqs(const float* inv_freq) {
+    Rotation r;
+    r.inv_freq = inv_freq;
+    return r;
+}
+Rotation no_rotation() {
+    Rotation r;
+    r.none = true;
+    return r;
+}
+
+}  // namespace
+
+extern "C" {
+
+int corope_rope_attn_fwd(const void* q, const void* k, const void* v, const float* cos, const float* sin, int64_t table_row_stride, void* o,
+                         float* lse2, int B, int H, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
+                         size_t workspace_bytes, int* status_word, void* stream) {
+    return rope_fwd_impl(q, k, v, from_tables(cos, sin, table_row_stride), o, lse2, B, H, H, N, D, dtype, causal, sm_scale, workspace,
+                         workspace_bytes, status_word, stream);
+}
+
+int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, const float* cos,
+                         const float* sin, int64_t table_row_stride, void* dq, void* dk, void* dv, int B, int H, int N, int D, int dtype,
+                         int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    return rope_bwd_impl(q, k, v, o, d_o, lse2, from_tables(cos, sin, table_row_stride), dq, dk, dv, B, H, H, N, D, dtype, causal, sm_scale,
+                         workspace, workspace_bytes, status_word, stream);
+}
+
+int corope_rope_attn_fwd_freqs(const void* q, const void* k, const void* v, const float* inv_freq, void* o, float* lse2, int B, int H, int N,
+                               int D, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word,
+                               void* stream) {
+    if (!inv_freq) return COROPE_ERR_NULL_POINTER;
+    return rope_fwd_impl(q, k, v, from_freqs(inv_freq), o, lse2, B, H, H, N, D, dtype, causal, sm_scale, workspace, workspace_bytes,
+                         status_word, stream);
+}
+
+int corope_rope_attn_bwd_freqs(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                               const float* inv_freq, void* dq, void* dk, void* dv, int B, int H, int N, int D, int dtype, int causal,
+                               float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    if (!inv_freq) return COROPE_ERR_NULL_POINTER;
+    return rope_bwd_impl(q, k, v, o, d_o, lse2, from_freqs(inv_freq), dq, dk, dv, B, H, H, N, D, dtype, causal, sm_scale, workspace,
+                         workspace_bytes, status_word, stream);
+}
+
+int corope_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, int B, int Hq, int Hkv, int N, int D, int dtype,
+                          int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    return rope_fwd_impl(q, k, v, no_rotation(), o, lse2, B, Hq, Hkv, N, D, dtype, causal, sm_scale, workspace, workspace_bytes, status_word,
+                         stream);
+}
+
+int corope_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, void* dq, void* dk,
+                          void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
+                          size_t workspace_bytes, int* status_word, void* stream) {
+    return rope_bwd_impl(q, k, v, o, d_o, lse2, no_rotation(), dq, dk, dv, B, Hq, Hkv, N, D, dtype, causal, sm_scale, workspace,
+                         workspace_bytes, status_word, stream);
 }
 
 static int check_gqa(int B, int Hq, int Hkv, int N, int D, int dtype) {

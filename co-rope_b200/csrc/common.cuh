@@ -56,7 +56,9 @@ struct RopeParams {
     const float* sin;
     int64_t table_stride;
     const uint32_t* packed_tab;  // [N, D/2] (cos, sin) pairs in 16-bit fixed point, built per call in the workspace
-    int B, H, N, D;
+    int B, H, N, D;     // H = number of query heads
+    int Hkv;            // number of K / V heads (H % Hkv == 0; query head h reads KV head h / (H / Hkv)); equals H for the fused-RoPE ops
+    int no_rope;        // 1 = plain attention: no rotation anywhere (cos / sin are null, the packed table holds the identity)
     int causal;
     float sm_scale;
     int* status;
@@ -533,11 +535,14 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s);
 // tensor-core backward, D = 128, 16-bit: delta, the rotated fp16 copy of Q (scaled by sm_scale * log2e) into p.q_rot and a
 // zeroed p.dq_acc in one launch; sets nothing in p
 int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s);
+// cos == nullptr packs the identity rotation (plain attention)
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src = -1);
+// cos / sin tables [N, half_d] fp32 for positions 0 .. N-1 from per-pair frequencies: angle = float(n) * inv_freq[d]
+int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, cudaStream_t s);
 int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
 int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
 int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
-                          cudaStream_t s);
+                          cudaStream_t s);   // H = heads of x
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);

@@ -29,3 +29,8 @@ extern "C" int corope_debug_expire_wait(int* status_word, unsigned max_polls, vo
     corope::count_launch();
     return (int)cudaGetLastError();
 }
+
+extern "C" int corope_debug_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, void* stream) {
+    if (!inv_freq || !cos_out || !sin_out || N <= 0 || half_d <= 0) return COROPE_ERR_NULL_POINTER;
+    return corope::launch_synth_tables(inv_freq, cos_out, sin_out, N, half_d, (cudaStream_t)stream);
+}

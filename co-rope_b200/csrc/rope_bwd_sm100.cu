@@ -126,12 +126,16 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
-    const int BH = p.B * p.H;
+    const int G = p.H / p.Hkv;            // query heads per K / V head (1 for the fused-RoPE ops)
+    const int BH = p.B * p.Hkv;           // units are taken per K / V head; a unit sweeps the query tiles of all G heads of its group
     const int n_kb = N / kBK;
     const int n_units = BH * n_kb;
     const bool causal = p.causal != 0;
-    // per unit (jb, bh): first query row visited q_first = causal ? jb * kBK : 0 (causal: the block's own diagonal) and
-    // n_steps = (N - q_first) / kBQ, which is even, so the two-buffer indices of a unit's first step are always 0
+    // per unit (jb, bh): first query row visited q_first = causal ? jb * kBK : 0 (causal: the block's own diagonal),
+    // spg = (N - q_first) / kBQ steps per query head (even) and n_steps = G * spg, so the two-buffer indices of a unit's
+    // first step are always 0.  Step s works on query head bh * G + s / spg, rows q_first + (s % spg) * kBQ .. + kBQ - 1.
+    auto step_q0 = [&](int q_first, int spg, int s) { return q_first + (s % spg) * kBQ; };
+    auto step_row = [&](int bh, int q_first, int spg, int s) { return (bh * G + s / spg) * N + q_first + (s % spg) * kBQ; };
 
     if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
         if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
@@ -198,11 +202,11 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const Unit un = unit_of(w, n_kb, BH);
                 const int row_base = un.bh * N;
                 const int q_first = causal ? un.jb * kBK : 0;
-                const int n_steps = (N - q_first) / kBQ;
+                const int spg = (N - q_first) / kBQ, n_steps = G * spg;
                 auto load_step = [&](int s) -> bool {
                     const int gs = g + s, st = gs % kStages;
                     if (gs >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((gs / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) return false;
-                    const int qr = row_base + q_first + s * kBQ;
+                    const int qr = step_row(un.bh, q_first, spg, s);
                     mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
                     tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
                     tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
@@ -288,7 +292,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
                 if (w < 0) break;
                 const Unit un = unit_of(w, n_kb, BH);
-                const int n_steps = (N - (causal ? un.jb * kBK : 0)) / kBQ;
+                const int n_steps = G * ((N - (causal ? un.jb * kBK : 0)) / kBQ);
                 {
                     const int st0 = g % kStages, b0 = g & 1;
                     ok = mbar_wait_warp(&bars[K_ROT], n & 1, p.status, K_ROT, abort_flag) && mbar_wait_warp(&bars[V_FULL], n & 1, p.status, V_FULL, abort_flag) &&
@@ -348,7 +352,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             if (w < 0) break;
             const Unit un = unit_of(w, n_kb, BH);
             const int q_first = causal ? un.jb * kBK : 0;
-            const int n_steps = (N - q_first) / kBQ;
+            const int spg = (N - q_first) / kBQ, n_steps = G * spg;
             {
                 TabRegs<kBQ> trk;
                 load_table_regs<kBQ>(trk, p.packed_tab + (size_t)(un.jb * kBK + rg * kBQ) * (kD / 2), tid);
@@ -366,7 +370,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 rotate_tile_regs<T, kQHalf, kQBox, 2>(sQ + st * kQBytes + rg * kQHalf * 128, tr, tid, p.sm_scale * kLog2e);
                 fence_proxy_async();
                 mbar_arrive_warp(&bars[Q_ROT + st], lane);
-                if (s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(q_first + (s + 1) * kBQ + rg * kQHalf) * (kD / 2), tid);
+                if (s + 1 < n_steps) load_table_regs<kQHalf>(tr, p.packed_tab + (size_t)(step_q0(q_first, spg, s + 1) + rg * kQHalf) * (kD / 2), tid);
             }
             g += n_steps;
         }
@@ -385,7 +389,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const Unit un = unit_of(w, n_kb, BH);
         const int jb = un.jb, row_base = un.bh * N;
         const int q_first = causal ? jb * kBK : 0;
-        const int n_steps = (N - q_first) / kBQ;
+        const int spg = (N - q_first) / kBQ, n_steps = G * spg;
         const int key = jb * kBK + row;
         for (int s = 0; s < n_steps; ++s) {
             const int gs = g + s, u = gs >> 1, st = gs % kStages, b = gs & 1;
@@ -398,7 +402,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tc_fence_after();
             const float* lse = sLD + st * 2 * kBQ;
             const float* dlt = lse + kBQ;
-            const int q0 = q_first + s * kBQ;
+            const int q0 = step_q0(q_first, spg, s);
             const bool diag = causal && q0 < jb * kBK + kBK;   // some keys of this block lie above the diagonal for these queries
             {
                 const int c = wg;   // this group's 32 query columns
@@ -501,7 +505,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const Unit un = unit_of(w, n_kb, BH);
         const int row_base = un.bh * N;
         const int q_first = causal ? un.jb * kBK : 0;
-        const int n_steps = (N - q_first) / kBQ;
+        const int spg = (N - q_first) / kBQ, n_steps = G * spg;
         for (int s = 0; s < n_steps; ++s) {
             const int gs = g + s, b = gs & 1;
             if (!(ok = mbar_wait_warp(&bars[DQ_DONE + b], (gs >> 1) & 1, p.status, DQ_DONE + b, abort_flag))) break;
@@ -524,7 +528,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             fence_proxy_async();
             named_bar_sync(1, 128);
             if (threadIdx.x == kDrainWarp0 * 32) {
-                tma_reduce_add_2d(&mapDQ, 0, row_base + q_first + s * kBQ, sDQ);
+                tma_reduce_add_2d(&mapDQ, 0, step_row(un.bh, q_first, spg, s), sDQ);
                 bulk_commit_group();
             }
         }
@@ -567,13 +571,13 @@ __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __
 template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv, mdo, mdq;
-    const uint64_t rows = (uint64_t)p.B * p.H * p.N;
+    const uint64_t rows = (uint64_t)p.B * p.H * p.N, kv_rows = (uint64_t)p.B * p.Hkv * p.N;
     if (int e = p.q_rot ? encode_tensor_map_2d_sw128(&mq, p.q_rot, rows, kD, kBQ, 64, COROPE_DTYPE_F16)
                         : encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype))
         return e;
     if (int e = encode_tensor_map_2d_sw128(&mdo, p.d_o, rows, kD, kBQ, 64, dtype)) return e;
-    if (int e = encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBK, 64, dtype)) return e;
-    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mk, p.k, kv_rows, kD, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, kv_rows, kD, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_f32(&mdq, p.dq_acc, rows, kD, kBQ, kD)) return e;
     cudaError_t e = p.dq_acc_zeroed ? cudaSuccess : cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
@@ -583,7 +587,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     int dev = 0, sms = 0;
     if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
-    const unsigned units = (unsigned)((p.N / kBK) * p.B * p.H);
+    const unsigned units = (unsigned)((p.N / kBK) * p.B * p.Hkv);
     const unsigned grid = units < (unsigned)sms ? units : (unsigned)sms;   // persistent: one CTA per SM
     kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, mdq, p); count_launch();
     e = cudaGetLastError();

@@ -133,6 +133,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
     const int BH = p.B * p.H;
+    const int G = p.H / p.Hkv;   // query heads per K / V head (1 for the fused-RoPE ops); query head bh reads KV head bh / G
     // N is a multiple of 128: when it is not a multiple of 256 the last item of a head has only Q0; its Q1 tile (and, causal,
     // the K tile behind the diagonal) lies beyond the head -- TMA fetches whatever is there (the next head's rows, zeros
     // behind the tensor), the results are finite and are not stored
@@ -219,8 +220,9 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                         tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
                         tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
                     }
+                    const int kv_base = (wi.bh / G) * N;
                     for (int j = 0; ok && j < nk; ++j, ++gk) {
-                        const int r = row_base + j * kBN;
+                        const int r = kv_base + j * kBN;
                         const int ks = gk % kKStages;
                         if (gk >= kKStages && !(ok = mbar_wait(&bars[K_EMPTY + ks], ((gk / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag))) break;
                         mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
@@ -239,7 +241,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int w = fetch_item(bars, item_ring, n, lane, false, p.status, abort_flag);
                     if (w < 0) break;
                     const WorkItem wi = work_item(w, n_qt, BH);
-                    const int row_base = wi.bh * N, nk = causal ? 2 * wi.t + 2 : nk_all;
+                    const int row_base = (wi.bh / G) * N, nk = causal ? 2 * wi.t + 2 : nk_all;
                     for (int j = 0; j < nk; ++j, ++gv) {
                         const int r = row_base + j * kBN;
                         const int vs = gv % kVStages;
@@ -521,12 +523,12 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv;
-    const uint64_t rows = (uint64_t)p.B * p.H * p.N;
+    const uint64_t rows = (uint64_t)p.B * p.H * p.N, kv_rows = (uint64_t)p.B * p.Hkv * p.N;
     if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBM, 64, dtype)) return e;
-    if (int e = p.k_rot ? encode_tensor_map_2d_sw128(&mk, p.k_rot, rows, kD, kBN, 64, COROPE_DTYPE_F16)
-                        : encode_tensor_map_2d_sw128(&mk, p.k, rows, kD, kBN, 64, dtype))
+    if (int e = p.k_rot ? encode_tensor_map_2d_sw128(&mk, p.k_rot, kv_rows, kD, kBN, 64, COROPE_DTYPE_F16)
+                        : encode_tensor_map_2d_sw128(&mk, p.k, kv_rows, kD, kBN, 64, dtype))
         return e;
-    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, rows, kD, kBN, 64, dtype)) return e;
+    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, kv_rows, kD, kBN, 64, dtype)) return e;
     auto kern = rope_fwd_sm100_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;

@@ -45,7 +45,7 @@ __device__ __forceinline__ void stage_rows(float* dst, const T* X, int r0, int N
         if (pos < N) {
             float x1 = Elem<T>::to_f32(X[(size_t)pos * D + d]);
             float x2 = Elem<T>::to_f32(X[(size_t)pos * D + d + H2]);
-            if (ROTATE) {
+            if (ROTATE && cosT != nullptr) {   // null tables: plain attention, no rotation
                 float c = cosT[pos * ts + d], s = sinT[pos * ts + d];
                 y1 = (x1 * c - x2 * s) * scale;
                 y2 = (x2 * c + x1 * s) * scale;
@@ -138,9 +138,10 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
     const int bh = blockIdx.y;
     const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;  // longest causal rows first
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kvh = bh / (p.H / p.Hkv);   // [B, H] flattened -> [B, Hkv] flattened: the heads of a group are adjacent
     const T* Q = reinterpret_cast<const T*>(p.q) + (size_t)bh * N * D;
-    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bh * N * D;
-    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bh * N * D;
+    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)kvh * N * D;
+    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)kvh * N * D;
     T* O = reinterpret_cast<T*>(p.out_o) + (size_t)bh * N * D;
 
     stage_rows<T, D, D, true>(q_s, Q, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
@@ -244,9 +245,10 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParam
     const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t base = (size_t)bh * N * D;
+    const size_t kv_base = (size_t)(bh / (p.H / p.Hkv)) * N * D;
     const T* Q = reinterpret_cast<const T*>(p.q) + base;
-    const T* K = reinterpret_cast<const T*>(p.k) + base;
-    const T* V = reinterpret_cast<const T*>(p.v) + base;
+    const T* K = reinterpret_cast<const T*>(p.k) + kv_base;
+    const T* V = reinterpret_cast<const T*>(p.v) + kv_base;
     const T* DO = reinterpret_cast<const T*>(p.d_o) + base;
     T* DQ = reinterpret_cast<T*>(p.dq) + base;
 
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParam
     for (int r = 0; r < kRowsPerWarp; ++r) {
         const int i = m0 + row0 + r;
         if (i >= N) continue;  // warp-uniform: i does not depend on the lane
-        store_inverse_rotated<T, D>(DQ + (size_t)i * D, acc[r], i, p.cos, p.sin, p.table_stride, p.sm_scale, lane, true);
+        store_inverse_rotated<T, D>(DQ + (size_t)i * D, acc[r], i, p.cos, p.sin, p.table_stride, p.sm_scale, lane, p.cos != nullptr);
     }
 }
 
@@ -305,14 +307,13 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
     float* dl_s = lse_s + kTile;              // [32]
 
     const int N = p.N;
-    const int bh = blockIdx.y;
+    const int kvh = blockIdx.y;         // KV head (over batch x Hkv); its G query heads are kvh * G .. kvh * G + G - 1
+    const int G = p.H / p.Hkv;
     const int n0 = blockIdx.x * kRows;  // causal: low key blocks are the long ones and come first
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t base = (size_t)bh * N * D;
-    const T* Q = reinterpret_cast<const T*>(p.q) + base;
+    const size_t base = (size_t)kvh * N * D;
     const T* K = reinterpret_cast<const T*>(p.k) + base;
     const T* V = reinterpret_cast<const T*>(p.v) + base;
-    const T* DO = reinterpret_cast<const T*>(p.d_o) + base;
     T* DK = reinterpret_cast<T*>(p.dk) + base;
     T* DV = reinterpret_cast<T*>(p.dv) + base;
 
@@ -327,6 +328,10 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
         for (int c = 0; c < NC; ++c) dk[r][c] = dv[r][c] = 0.f;
 
     const int i_begin = p.causal ? n0 : 0;
+    for (int g = 0; g < G; ++g) {   // dK / dV are summed over the group's query heads
+    const int bh = kvh * G + g;
+    const T* Q = reinterpret_cast<const T*>(p.q) + (size_t)bh * N * D;
+    const T* DO = reinterpret_cast<const T*>(p.d_o) + (size_t)bh * N * D;
     for (int i0 = i_begin; i0 < N; i0 += kTile) {
         __syncthreads();
         stage_rows<T, D, D + 1, true>(q_s, Q, i0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
@@ -353,6 +358,7 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
         accumulate_cols<D, D + 1>(dv, s, do_s, lane);
         accumulate_cols<D, D + 1>(dk, dp, q_s, lane);
     }
+    }
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r) {
         const int j = n0 + row0 + r;
@@ -360,7 +366,7 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
 #pragma unroll
         for (int c = 0; c < NC; ++c) DV[(size_t)j * D + lane + 32 * c] = Elem<T>::from_f32(dv[r][c]);
         // q_s carried sm_scale * log2e, so dk holds dK~ * log2e: undo with ln2
-        store_inverse_rotated<T, D>(DK + (size_t)j * D, dk[r], j, p.cos, p.sin, p.table_stride, kLn2, lane, true);
+        store_inverse_rotated<T, D>(DK + (size_t)j * D, dk[r], j, p.cos, p.sin, p.table_stride, kLn2, lane, p.cos != nullptr);
     }
 }
 
@@ -374,7 +380,20 @@ __global__ void pack_tables_kernel(const float* __restrict__ cosT, const float* 
     if (idx == 0) out[(size_t)N * half_d] = 0u;   // the word after the table: work counter of the persistent forward kernel
     if (idx >= (size_t)N * half_d) return;
     int n = (int)(idx / half_d), d = (int)(idx % half_d);
-    out[idx] = d < half_src ? pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]) : pack_unorm_pair(1.f, 0.f);
+    out[idx] = (cosT != nullptr && d < half_src) ? pack_unorm_pair(cosT[n * ts + d], sinT[n * ts + d]) : pack_unorm_pair(1.f, 0.f);
+}
+
+// cos / sin tables for positions 0 .. N-1 from the per-pair frequencies, as precompute_freqs_cis forms them
+// (fused-rope/rope_attn_pytorch.py:33-47): angle = float(position) * inv_freq[d] in fp32, then cos / sin of it.
+__global__ void synth_tables_kernel(const float* __restrict__ inv_freq, float* __restrict__ cosT, float* __restrict__ sinT, int N, int half_d) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)N * half_d) return;
+    const int n = (int)(idx / half_d), d = (int)(idx % half_d);
+    const float ang = __fmul_rn((float)n, inv_freq[d]);
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    cosT[idx] = cs;
+    sinT[idx] = sn;
 }
 
 // D = 64 <-> D = 128 with zero padding, 16-byte chunks.  "rope" layout keeps the half-layout pairs together for the
@@ -503,7 +522,8 @@ int launch_bwd_t(const RopeParams& p, cudaStream_t s) {
         auto kern = rope_bwd_dkdv_general_kernel<T, D>;
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, kThreads, smem, s>>>(p); count_launch();
+        dim3 grid_kv((p.N + kRows - 1) / kRows, p.B * p.Hkv);   // one CTA per 32 keys of a KV head; it sums over the group's query heads
+        kern<<<grid_kv, kThreads, smem, s>>>(p); count_launch();
         return (int)cudaGetLastError();
     }
 }
@@ -596,6 +616,13 @@ int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s) {
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src) {
     size_t n = (size_t)N * half_d;
     pack_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(cos, sin, stride, packed, N, half_d, half_src < 0 ? half_d : half_src);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, cudaStream_t s) {
+    size_t n = (size_t)N * half_d;
+    synth_tables_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(inv_freq, cos_out, sin_out, N, half_d);
     count_launch();
     return (int)cudaGetLastError();
 }

@@ -110,3 +110,75 @@ class _attention(torch.autograd.Function):
 
 
 attention = _attention.apply
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# The same attention with the tables left out of the interface: for callers whose cos / sin tables are the output of the
+# reference's precompute_freqs_cis(D, N, theta) (fused-rope/rope_attn_pytorch.py:10-49) the angles can be formed on the
+# device from D/2 frequencies, so no [N, D] tables have to exist at all.  The explicit-table entry point above stays the
+# general case (other positions, scaled frequencies).
+# ---------------------------------------------------------------------------------------------------------------------
+def inv_freq_of(theta, D, device):
+    """The D/2 frequencies exactly as precompute_freqs_cis computes them (rope_attn_pytorch.py:29), on `device`."""
+    return 1.0 / (theta ** (torch.arange(0, D, 2, device=device).float() / D))
+
+
+def _forward_freqs(q, k, v, causal, sm_scale, inv_freq):
+    HEAD_DIM_K = q.shape[-1]
+    assert HEAD_DIM_K in SUPPORTED_HEAD_DIMS, "corope_b200 supports head dims %s" % (SUPPORTED_HEAD_DIMS,)
+    assert q.shape == k.shape == v.shape and q.dim() == 4
+    assert q.dtype == k.dtype == v.dtype and q.dtype in _ext.DTYPE_CODES
+    for t in (q, k, v, inv_freq):
+        _ext.require_cuda(t)
+    B, H, N, D = q.shape
+    assert inv_freq.dtype == torch.float32 and inv_freq.numel() == D // 2 and inv_freq.is_contiguous()
+    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    o = torch.empty_like(qc)
+    M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
+    ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD_FREQS, B, H, H, N, D, q.dtype, q.device)
+    _ext.pre_call(q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_rope_attn_fwd_freqs(
+            qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), inv_freq.data_ptr(), o.data_ptr(), M.data_ptr(), B, H, N, D,
+            _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_rope_attn_fwd_freqs")
+    _ext.post_call(q.device)
+    return qc, kc, vc, o, M
+
+
+def _backward_freqs(q, k, v, o, M, inv_freq, do, causal, sm_scale):
+    do = do.contiguous()
+    B, H, N, D = q.shape
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD_FREQS, B, H, H, N, D, q.dtype, q.device)
+    _ext.pre_call(q.device)
+    with torch.cuda.device(q.device):
+        rc = _ext.lib().corope_rope_attn_bwd_freqs(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(), inv_freq.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+    _ext.raise_for_status(rc, "corope_rope_attn_bwd_freqs")
+    _ext.post_call(q.device)
+    return dq, dk, dv
+
+
+class _attention_theta(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale, theta):
+        inv_freq = inv_freq_of(theta, q.shape[-1], q.device)
+        qc, kc, vc, o, M = _forward_freqs(q, k, v, causal, sm_scale, inv_freq)
+        ctx.save_for_backward(qc, kc, vc, o, M, inv_freq)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, M, inv_freq = ctx.saved_tensors
+        dq, dk, dv = _backward_freqs(q, k, v, o, M, inv_freq, do, ctx.causal, ctx.sm_scale)
+        return dq, dk, dv, None, None, None
+
+
+attention_theta = _attention_theta.apply   # attention_theta(q, k, v, causal, sm_scale, theta): positions 0 .. N-1, base theta

@@ -43,6 +43,10 @@ extern "C" {
 #define COROPE_OP_ROPE_BWD 1
 #define COROPE_OP_GQA_FWD 2
 #define COROPE_OP_GQA_BWD 3
+#define COROPE_OP_ROPE_FWD_FREQS 4   /* corope_rope_attn_fwd_freqs: as ROPE_FWD plus room for the synthesized tables */
+#define COROPE_OP_ROPE_BWD_FREQS 5
+#define COROPE_OP_FLASH_FWD 6        /* corope_flash_attn_fwd (Hq query heads, Hkv K / V heads) */
+#define COROPE_OP_FLASH_BWD 7
 
 /* host-side argument errors */
 #define COROPE_OK 0
@@ -119,6 +123,47 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
                          int B, int H, int N, int D, int dtype, int causal, float sm_scale,
                          void* workspace, size_t workspace_bytes,
                          int* status_word, void* stream);
+
+/*
+ * Fused RoPE attention with the cos / sin tables synthesized on the device instead of read from the caller: the angle
+ * of position n and pair d is float(n) * inv_freq[d] in fp32, exactly how precompute_freqs_cis forms it
+ * (fused-rope/rope_attn_pytorch.py:29-47: inv_freq[d] = 1 / theta^(2d/D), positions 0 .. N-1), followed by cosf / sinf.
+ * For callers whose tables are that function's output, this removes the tables from the interface and from HBM
+ * traffic; corope_rope_attn_fwd / _bwd with explicit tables remain the general case (arbitrary positions, scaled
+ * or interpolated frequencies).   inv_freq : D/2 floats in device memory.  Workspace: COROPE_OP_ROPE_FWD_FREQS /
+ * COROPE_OP_ROPE_BWD_FREQS.  Everything else as corope_rope_attn_fwd / corope_rope_attn_bwd.
+ */
+int corope_rope_attn_fwd_freqs(const void* q, const void* k, const void* v, const float* inv_freq,
+                               void* o, float* lse2,
+                               int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                               void* workspace, size_t workspace_bytes,
+                               int* status_word, void* stream);
+int corope_rope_attn_bwd_freqs(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                               const float* lse2, const float* inv_freq,
+                               void* dq, void* dk, void* dv,
+                               int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                               void* workspace, size_t workspace_bytes,
+                               int* status_word, void* stream);
+
+/*
+ * Plain flash attention (no RoPE) with grouped K / V heads.  Replaces _attention.forward / .backward of the reference's
+ * un-fused kernel (fused-rope/flash_attn_v2_triton.py:513-631; head mapping off_h_kv = off_h_q // GROUP_SIZE :194-196);
+ * the math is that of assets/flashattn-gqa/attn_gqa_pytorch.py:17-190.
+ *   q, o, d_o, dq : [B,Hq,N,D];  k, v, dk, dv : [B,Hkv,N,D];  Hq % Hkv == 0 (any group size);  lse2 : [B,Hq,N].
+ * dk / dv are summed over each group (the reference's backward takes Hq == Hkv only, :560; this one takes both).
+ * Same kernels as the fused-RoPE ops with the rotation switched off.  Workspace: COROPE_OP_FLASH_FWD / COROPE_OP_FLASH_BWD.
+ */
+int corope_flash_attn_fwd(const void* q, const void* k, const void* v,
+                          void* o, float* lse2,
+                          int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
+                          void* workspace, size_t workspace_bytes,
+                          int* status_word, void* stream);
+int corope_flash_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                          const float* lse2,
+                          void* dq, void* dk, void* dv,
+                          int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
+                          void* workspace, size_t workspace_bytes,
+                          int* status_word, void* stream);
 
 /*
  * Co-RoPE GQA attention forward (causal only).  Replaces the launch in _attention.forward

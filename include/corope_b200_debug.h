@@ -37,6 +37,13 @@ uint64_t corope_launch_count(void);
  */
 int corope_debug_expire_wait(int* status_word, unsigned max_polls, void* stream);
 
+/*
+ * The table synthesis of corope_rope_attn_fwd_freqs / _bwd_freqs on its own: cos_out / sin_out [N, half_d] fp32 (device)
+ * from inv_freq [half_d] (device), angle = float(n) * inv_freq[d].  Lets a test compare the synthesized tables with
+ * precompute_freqs_cis element by element.
+ */
+int corope_debug_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,14 +1,15 @@
 """Generate the golden vectors under tests/golden/ from the reference's own PyTorch code.
 
-Run in a container that has the reference checkout (it is not available on the
-GPU box, which is why the vectors are committed):
+Run where a checkout of the reference is available (the tests themselves must not
+depend on one, which is why the vectors are committed):
 
     TORCH_COMPILE_DISABLE=1 python tests/golden/make_golden.py /path/to/reference
 
 For every case it draws seeded N(0,1) inputs, rounds them to fp16 (so they
 are stored exactly in 2 bytes and are exact in fp32), upcasts to fp32, and
 runs the reference's `attention_pytorch` forward and its hand-written backward
-(fused-rope/rope_attn_pytorch.py:87-227, corope-exp/corope_attn_gqa_pytorch.py:9-303).
+(fused-rope/rope_attn_pytorch.py:87-227, corope-exp/corope_attn_gqa_pytorch.py:9-303,
+assets/flashattn-gqa/attn_gqa_pytorch.py:10-193).
 Outputs are stored in fp32.
 """
 
@@ -32,6 +33,14 @@ COROPE_CASES = {
     "corope_a": (2, 4, 2, 64, 32, 32 ** -0.5, 10000.0, 42),
     "corope_b": (1, 4, 1, 48, 64, 64 ** -0.5, 10000.0, 5),
     "corope_c": (1, 2, 2, 32, 128, 128 ** -0.5, 500.0, 6),
+}
+
+
+GQA_CASES = {
+    # name: (B, Hq, Hkv, N, D, causal, sm_scale, seed)   -- plain attention with grouped K / V heads
+    "attn_gqa_a": (2, 4, 2, 64, 32, True, 32 ** -0.5, 11),
+    "attn_gqa_b": (1, 6, 2, 80, 64, False, 0.5, 12),
+    "attn_gqa_c": (1, 2, 2, 128, 128, True, 128 ** -0.5, 13),
 }
 
 
@@ -78,6 +87,24 @@ def main(ref_root):
         np.savez(os.path.join(HERE, name + ".npz"),
                  meta=np.array([B, Hq, Hkv, N, D, seed], dtype=np.int64),
                  scal=np.array([sm_scale, theta], dtype=np.float64),
+                 q=q16.numpy(), k=k16.numpy(), v=v16.numpy(), do=do16.numpy(),
+                 o=o.detach().numpy(), dq=q.grad.numpy(), dk=k.grad.numpy(), dv=v.grad.numpy())
+        print(name, "ok", tuple(o.shape))
+
+
+    gqa = _load(os.path.join(ref_root, "assets", "flashattn-gqa", "attn_gqa_pytorch.py"), "ref_attn_gqa_pytorch")
+    for name, (B, Hq, Hkv, N, D, causal, sm_scale, seed) in GQA_CASES.items():
+        gen = torch.Generator().manual_seed(seed)
+        q16 = _draw((B, Hq, N, D), gen)
+        k16 = _draw((B, Hkv, N, D), gen)
+        v16 = _draw((B, Hkv, N, D), gen)
+        do16 = _draw((B, Hq, N, D), gen)
+        q, k, v = (t.float().requires_grad_(True) for t in (q16, k16, v16))
+        o = gqa.attention_pytorch(q, k, v, causal, sm_scale)
+        o.backward(do16.float())
+        np.savez(os.path.join(HERE, name + ".npz"),
+                 meta=np.array([B, Hq, Hkv, N, D, int(causal), seed], dtype=np.int64),
+                 scal=np.array([sm_scale], dtype=np.float64),
                  q=q16.numpy(), k=k16.numpy(), v=v16.numpy(), do=do16.numpy(),
                  o=o.detach().numpy(), dq=q.grad.numpy(), dk=k.grad.numpy(), dv=v.grad.numpy())
         print(name, "ok", tuple(o.shape))

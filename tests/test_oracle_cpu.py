@@ -68,7 +68,7 @@ def test_corope_oracle_matches_golden(name):
 
 def test_every_golden_file_is_covered():
     names = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLD, "*.npz")))
-    assert names == ["corope_a", "corope_b", "corope_c", "rope_a", "rope_b", "rope_c"]
+    assert names == ["attn_gqa_a", "attn_gqa_b", "attn_gqa_c", "corope_a", "corope_b", "corope_c", "rope_a", "rope_b", "rope_c"]
 
 
 def test_corope_manual_backward_equals_autograd():
@@ -161,3 +161,46 @@ def test_corope_oracle_matches_live_reference():
     assert (dq - qq.grad).abs().max() < 1e-5
     assert (dk - kk.grad).abs().max() < 1e-5
     assert (dv - vv.grad).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("name", ["attn_gqa_a", "attn_gqa_b", "attn_gqa_c"])
+def test_plain_gqa_oracle_matches_golden(name):
+    # plain attention with grouped K / V heads: outputs of the reference's assets/flashattn-gqa/attn_gqa_pytorch.py
+    g = np.load(os.path.join(GOLD, name + ".npz"))
+    B, Hq, Hkv, N, D, causal, _ = g["meta"].tolist()
+    (sm_scale,) = g["scal"].tolist()
+    q, k, v, do = (_t(g[x]) for x in ("q", "k", "v", "do"))
+    o = oracle.attn_gqa_fwd(q, k, v, bool(causal), sm_scale)
+    dq, dk, dv = oracle.attn_gqa_bwd(q, k, v, do, bool(causal), sm_scale)
+    assert (o - _t(g["o"])).abs().max() < 1e-6
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        assert got.shape == _t(g[key]).shape
+        assert (got - _t(g[key])).abs().max() < 5e-6, key
+    oc, lse2, dqc, dkc, dvc = oracle.attn_gqa_fwd_bwd_chunked(q, k, v, do, bool(causal), sm_scale, rows=16)
+    assert (oc - _t(g["o"])).abs().max() < 2e-6
+    for got, key in ((dqc, "dq"), (dkc, "dk"), (dvc, "dv")):
+        assert (got - _t(g[key])).abs().max() < 1e-5, key
+    # with the rotation by identity tables the fused-RoPE oracle must give the same (group size 1 only)
+    if Hq == Hkv:
+        o2 = oracle.rope_attn_fwd(q, k, v, bool(causal), sm_scale, torch.ones(N, D), torch.zeros(N, D))
+        assert (o2 - o).abs().max() < 1e-6
+
+
+def test_plain_gqa_oracle_matches_live_reference():
+    path = os.path.join(REF, "assets", "flashattn-gqa", "attn_gqa_pytorch.py")
+    if not os.path.exists(path):
+        pytest.skip("no reference checkout")
+    spec = importlib.util.spec_from_file_location("ref_attn_gqa_pytorch_live", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    gen = torch.Generator().manual_seed(77)
+    q = torch.randn((2, 8, 48, 64), generator=gen)
+    k, v = (torch.randn((2, 2, 48, 64), generator=gen) for _ in range(2))
+    do = torch.randn((2, 8, 48, 64), generator=gen)
+    for causal in (True, False):
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+        o = ref.attention_pytorch(qq, kk, vv, causal, 0.3)
+        o.backward(do)
+        assert (oracle.attn_gqa_fwd(q, k, v, causal, 0.3) - o.detach()).abs().max() < 1e-6
+        for got, want in zip(oracle.attn_gqa_bwd(q, k, v, do, causal, 0.3), (qq.grad, kk.grad, vv.grad)):
+            assert (got - want).abs().max() < 5e-6
