@@ -100,6 +100,17 @@ def lib():
             L.corope_rope_attn_bwd.restype = i32
             L.corope_rope_attn_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32,
                                                vp, sz, vp, vp]
+            sp = ctypes.POINTER(Strides)
+            L.corope_rope_attn_fwd_strided.restype = i32
+            L.corope_rope_attn_fwd_strided.argtypes = [vp, vp, vp, vp, vp, i64, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp, sp]
+            L.corope_rope_attn_bwd_strided.restype = i32
+            L.corope_rope_attn_bwd_strided.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i64, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32,
+                                                       vp, sz, vp, vp, sp]
+            L.corope_flash_attn_fwd_strided.restype = i32
+            L.corope_flash_attn_fwd_strided.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp, sp]
+            L.corope_flash_attn_bwd_strided.restype = i32
+            L.corope_flash_attn_bwd_strided.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp, sz,
+                                                        vp, vp, sp]
             L.corope_rope_attn_fwd_freqs.restype = i32
             L.corope_rope_attn_fwd_freqs.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp, sz, vp, vp]
             L.corope_rope_attn_bwd_freqs.restype = i32
@@ -114,6 +125,27 @@ def lib():
             L.corope_gqa_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp, sz, vp, vp]
             _lib = L
         return _lib
+
+
+class Strides(ctypes.Structure):
+    """corope_strides_t of the C header: {batch, head, row} strides in elements of q, k, v, o, d_o, dq, dk, dv."""
+    _fields_ = [(name, ctypes.c_int64 * 3) for name in ("q", "k", "v", "o", "d_o", "dq", "dk", "dv")]
+
+
+def strides_of(**tensors):
+    """A Strides struct filled from the given [B, H, N, D] tensors (keyword = field name); other fields stay zero."""
+    st = Strides()
+    for name, t in tensors.items():
+        getattr(st, name)[:] = list(t.stride()[:3])
+    return st
+
+
+def kernel_layout(t):
+    """`t` itself when the kernels can take its layout directly (unit stride along the head dimension, no overlapping
+    or broadcast strides), else a contiguous copy."""
+    if t.stride(-1) == 1 and all(s > 0 for s in t.stride()) and t.stride(2) >= t.shape[3]:
+        return t
+    return t.contiguous()
 
 
 def require_cuda(t):

@@ -129,6 +129,7 @@ const char* corope_status_string(int status) {
         case COROPE_ERR_TENSOR_MAP: return "TMA tensor map could not be encoded";
         case COROPE_ERR_NO_DEVICE: return "no usable CUDA device or driver entry point";
         case COROPE_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        case COROPE_ERR_BAD_STRIDE: return "row stride smaller than the head dimension, or a negative stride";
         default: break;
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);
@@ -170,11 +171,35 @@ struct Rotation {
     bool none = false;
 };
 
+// Fills the kernels' stride fields from the ABI struct (null = contiguous [B, H, N, D]).
+void set_strides(RopeParams& p, const corope_strides_t* st, int Hq, int Hkv, int N, int D) {
+    auto conv = [](const int64_t (&a)[3]) {
+        Strides r;
+        r.b = a[0]; r.h = a[1]; r.n = a[2];
+        return r;
+    };
+    const Strides cq = contiguous_strides(Hq, N, D), ckv = contiguous_strides(Hkv, N, D);
+    p.sq = st ? conv(st->q) : cq;
+    p.sk = st ? conv(st->k) : ckv;
+    p.sv = st ? conv(st->v) : ckv;
+    p.so = st ? conv(st->o) : cq;
+    p.sdo = st ? conv(st->d_o) : cq;
+    p.sdq = st ? conv(st->dq) : cq;
+    p.sdk = st ? conv(st->dk) : ckv;
+    p.sdv = st ? conv(st->dv) : ckv;
+}
+// The tensor-core paths move rows with TMA and 16-byte vector accesses: base pointers and all strides must be multiples of 16 bytes.
+bool vec_ok(const void* ptr, const Strides& st) {
+    return ((uintptr_t)ptr % 16) == 0 && st.b % 8 == 0 && st.h % 8 == 0 && st.n % 8 == 0 && st.n > 0;
+}
+bool strides_positive(const Strides& st, int D) { return st.n >= D && st.b >= 0 && st.h >= 0; }
+
 // ops whose kernel family is recorded: the fused-RoPE pair also stands for its variants
 constexpr int kFamFwd = COROPE_OP_ROPE_FWD, kFamBwd = COROPE_OP_ROPE_BWD;
 
 int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, void* o, float* lse2, int B, int Hq, int Hkv, int N, int D,
-                  int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+                  int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream,
+                  const corope_strides_t* strides = nullptr) {
     if (!q || !k || !v || !o || !lse2) return COROPE_ERR_NULL_POINTER;
     if (!rot.none && !rot.inv_freq && (!rot.cos || !rot.sin)) return COROPE_ERR_NULL_POINTER;
     if (int e = check_common(B, Hq, N, D, dtype)) return e;
@@ -193,27 +218,32 @@ int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, voi
     p.cos = rot.none ? nullptr : rot.cos; p.sin = rot.none ? nullptr : rot.sin; p.table_stride = rot.stride;
     p.B = B; p.H = Hq; p.Hkv = Hkv; p.no_rope = rot.none ? 1 : 0;
     p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    const int policy = g_policy.load();
+    set_strides(p, strides, Hq, Hkv, N, D);
+    if (!strides_positive(p.sq, D) || !strides_positive(p.sk, D) || !strides_positive(p.sv, D) || !strides_positive(p.so, D)) return COROPE_ERR_BAD_STRIDE;
+    // rows are moved with TMA / 16-byte vectors on the tensor-core paths; otherwise the CUDA-core kernels take over
+    const bool vec = vec_ok(q, p.sq) && vec_ok(k, p.sk) && vec_ok(v, p.sv) && vec_ok(o, p.so);
+    const int policy = vec ? g_policy.load() : 1;
     if (policy == 0 && rope_d64_padded(N, D, dtype)) {
         // D = 64: zero-padded copies of q, k, v in the layout that keeps the rotation pairs together, the D = 128 kernels, o back
-        const size_t rows = (size_t)B * Hq * N, kv_rows = (size_t)B * Hkv * N;
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         void* k_rot = (char*)workspace + w.rot;
         void* qp = (char*)workspace + w.pad[0];
         void* vp = (char*)workspace + w.pad[1];
         void* op = (char*)workspace + w.pad[2];   // first the padded k (until it is rotated), then the padded output
         if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
-        if (int e = launch_pad_d64(q, qp, rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, op, kv_rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, vp, kv_rows, 0, dtype, s)) return e;
-        if (int e = launch_rope_prerotate(op, k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
+        if (int e = launch_pad_d64(q, p.sq, qp, B, Hq, N, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, p.sk, op, B, Hkv, N, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, p.sv, vp, B, Hkv, N, 0, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(op, contiguous_strides(Hkv, N, 128), k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
+        const Strides so_caller = p.so;
         p.q = qp; p.k = op; p.v = vp; p.out_o = op; p.D = 128;
+        set_strides(p, nullptr, Hq, Hkv, N, 128);   // the padded copies are contiguous
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);
         p.k_rot = k_rot;
         g_last_family[kFamFwd] = 1;
         if (int e = launch_rope_fwd_tc(p, dtype, s)) return e;
-        return launch_unpad_d64(op, o, rows, 0, dtype, s);
+        return launch_unpad_d64(op, o, so_caller, B, Hq, N, 0, dtype, s);
     }
     if (policy != 1 && rope_fwd_tc_supported(B, Hq, N, D, dtype, causal)) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
@@ -224,7 +254,7 @@ int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, voi
         // attention the "rotation" by the identity table is what brings K to fp16, the format Q is written in)
         if (policy == 0) {
             void* k_rot = (char*)workspace + w.rot;
-            if (int e = launch_rope_prerotate(k, k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
+            if (int e = launch_rope_prerotate(k, p.sk, k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
             p.k_rot = k_rot;
         }
         g_last_family[kFamFwd] = 1;
@@ -236,7 +266,7 @@ int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, voi
 
 int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, Rotation rot, void* dq,
                   void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
-                  size_t workspace_bytes, int* status_word, void* stream) {
+                  size_t workspace_bytes, int* status_word, void* stream, const corope_strides_t* strides = nullptr) {
     if (!q || !k || !v || !o || !d_o || !lse2 || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
     if (!rot.none && !rot.inv_freq && (!rot.cos || !rot.sin)) return COROPE_ERR_NULL_POINTER;
     if (int e = check_common(B, Hq, N, D, dtype)) return e;
@@ -257,12 +287,16 @@ int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, co
     p.cos = rot.none ? nullptr : rot.cos; p.sin = rot.none ? nullptr : rot.sin; p.table_stride = rot.stride;
     p.B = B; p.H = Hq; p.Hkv = Hkv; p.no_rope = rot.none ? 1 : 0;
     p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
-    const int policy = g_policy.load();
+    set_strides(p, strides, Hq, Hkv, N, D);
+    for (const Strides* st : {&p.sq, &p.sk, &p.sv, &p.so, &p.sdo, &p.sdq, &p.sdk, &p.sdv})
+        if (!strides_positive(*st, D)) return COROPE_ERR_BAD_STRIDE;
+    const bool vec = vec_ok(q, p.sq) && vec_ok(k, p.sk) && vec_ok(v, p.sv) && vec_ok(o, p.so) && vec_ok(d_o, p.sdo) && vec_ok(dq, p.sdq) &&
+                     vec_ok(dk, p.sdk) && vec_ok(dv, p.sdv);
+    const int policy = vec ? g_policy.load() : 1;
     const bool tc_direct = policy != 1 && !(policy == 0 && rope_d64_padded(N, D, dtype)) && rope_bwd_tc_supported(B, Hq, N, D, dtype, causal);
     if (!(tc_direct && policy == 0))   // the tensor-core path at D = 128 computes delta in its fused pre-pass
         if (int e = launch_rope_delta(p, dtype, s)) return e;
     if (policy == 0 && rope_d64_padded(N, D, dtype)) {
-        const size_t rows = (size_t)B * Hq * N, kv_rows = (size_t)B * Hkv * N;
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
         void* q_rot = (char*)workspace + w.rot;
         void* kp = (char*)workspace + w.pad[0];
@@ -271,21 +305,23 @@ int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, co
         void* dkp = (char*)workspace + w.pad[3];   // first the padded q (until it is rotated), then the padded dk
         void* dvp = (char*)workspace + w.pad[4];
         if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
-        if (int e = launch_pad_d64(q, dkp, rows, 1, dtype, s)) return e;
-        if (int e = launch_rope_prerotate(dkp, q_rot, tab, B, Hq, N, sm_scale * kLog2e, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, kp, kv_rows, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, vp, kv_rows, 0, dtype, s)) return e;
-        if (int e = launch_pad_d64(d_o, dop, rows, 0, dtype, s)) return e;
+        if (int e = launch_pad_d64(q, p.sq, dkp, B, Hq, N, 1, dtype, s)) return e;
+        if (int e = launch_rope_prerotate(dkp, contiguous_strides(Hq, N, 128), q_rot, tab, B, Hq, N, sm_scale * kLog2e, dtype, s)) return e;
+        if (int e = launch_pad_d64(k, p.sk, kp, B, Hkv, N, 1, dtype, s)) return e;
+        if (int e = launch_pad_d64(v, p.sv, vp, B, Hkv, N, 0, dtype, s)) return e;
+        if (int e = launch_pad_d64(d_o, p.sdo, dop, B, Hq, N, 0, dtype, s)) return e;
+        const Strides sdq_caller = p.sdq, sdk_caller = p.sdk, sdv_caller = p.sdv;
         p.q = dkp; p.k = kp; p.v = vp; p.d_o = dop; p.dq = dop; p.dk = dkp; p.dv = dvp; p.D = 128;
+        set_strides(p, nullptr, Hq, Hkv, N, 128);   // the padded copies are contiguous
         p.packed_tab = tab;
         p.sched_counter = reinterpret_cast<int*>(tab + (size_t)N * 64);   // zeroed by the table pack
         p.dq_acc = reinterpret_cast<float*>((char*)workspace + w.dq_acc);
         p.q_rot = q_rot;
         g_last_family[kFamBwd] = 1;
         if (int e = launch_rope_bwd_tc(p, dtype, s)) return e;
-        if (int e = launch_unpad_d64(dop, dq, rows, 1, dtype, s)) return e;
-        if (int e = launch_unpad_d64(dkp, dk, kv_rows, 1, dtype, s)) return e;
-        return launch_unpad_d64(dvp, dv, kv_rows, 0, dtype, s);
+        if (int e = launch_unpad_d64(dop, dq, sdq_caller, B, Hq, N, 1, dtype, s)) return e;
+        if (int e = launch_unpad_d64(dkp, dk, sdk_caller, B, Hkv, N, 1, dtype, s)) return e;
+        return launch_unpad_d64(dvp, dv, sdv_caller, B, Hkv, N, 0, dtype, s);
     }
     if (tc_direct) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);
@@ -337,6 +373,36 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
                          int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
     return rope_bwd_impl(q, k, v, o, d_o, lse2, from_tables(cos, sin, table_row_stride), dq, dk, dv, B, H, H, N, D, dtype, causal, sm_scale,
                          workspace, workspace_bytes, status_word, stream);
+}
+
+int corope_rope_attn_fwd_strided(const void* q, const void* k, const void* v, const float* cos, const float* sin, int64_t table_row_stride,
+                                 void* o, float* lse2, int B, int H, int N, int D, int dtype, int causal, float sm_scale, void* workspace,
+                                 size_t workspace_bytes, int* status_word, void* stream, const corope_strides_t* strides) {
+    return rope_fwd_impl(q, k, v, from_tables(cos, sin, table_row_stride), o, lse2, B, H, H, N, D, dtype, causal, sm_scale, workspace,
+                         workspace_bytes, status_word, stream, strides);
+}
+
+int corope_rope_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                                 const float* cos, const float* sin, int64_t table_row_stride, void* dq, void* dk, void* dv, int B, int H,
+                                 int N, int D, int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes,
+                                 int* status_word, void* stream, const corope_strides_t* strides) {
+    return rope_bwd_impl(q, k, v, o, d_o, lse2, from_tables(cos, sin, table_row_stride), dq, dk, dv, B, H, H, N, D, dtype, causal, sm_scale,
+                         workspace, workspace_bytes, status_word, stream, strides);
+}
+
+int corope_flash_attn_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse2, int B, int Hq, int Hkv, int N, int D,
+                                  int dtype, int causal, float sm_scale, void* workspace, size_t workspace_bytes, int* status_word,
+                                  void* stream, const corope_strides_t* strides) {
+    return rope_fwd_impl(q, k, v, no_rotation(), o, lse2, B, Hq, Hkv, N, D, dtype, causal, sm_scale, workspace, workspace_bytes, status_word,
+                         stream, strides);
+}
+
+int corope_flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, void* dq,
+                                  void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
+                                  void* workspace, size_t workspace_bytes, int* status_word, void* stream,
+                                  const corope_strides_t* strides) {
+    return rope_bwd_impl(q, k, v, o, d_o, lse2, no_rotation(), dq, dk, dv, B, Hq, Hkv, N, D, dtype, causal, sm_scale, workspace,
+                         workspace_bytes, status_word, stream, strides);
 }
 
 int corope_rope_attn_fwd_freqs(const void* q, const void* k, const void* v, const float* inv_freq, void* o, float* lse2, int B, int H, int N,

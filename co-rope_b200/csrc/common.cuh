@@ -38,6 +38,23 @@ __host__ __device__ inline size_t dtype_bytes(int dtype) { return dtype == COROP
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Strides of a [B, H, N, D] tensor in elements; the head-dim stride is always 1.  Tensor-core paths also need every
+// stride to be a multiple of 8 elements (16 bytes, the TMA granularity) -- the entry points check that.
+struct Strides {
+    int64_t b, h, n;
+};
+__host__ __device__ inline Strides contiguous_strides(int H, int N, int D) {
+    Strides st;
+    st.n = D;
+    st.h = (int64_t)N * D;
+    st.b = (int64_t)H * N * D;
+    return st;
+}
+// element offset of row n of head-slice bh (= b * H + h) of a tensor with H heads
+__host__ __device__ inline int64_t row_offset(const Strides& st, int H, int bh, int n) {
+    return (int64_t)(bh / H) * st.b + (int64_t)(bh % H) * st.h + (int64_t)n * st.n;
+}
+
 // Launch parameters common to the fused-RoPE kernels.
 struct RopeParams {
     const void* q;
@@ -65,6 +82,7 @@ struct RopeParams {
     int* sched_counter; // zeroed word in the workspace: next work item / unit of the persistent tensor-core kernels
     const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
     const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
+    Strides sq, sk, sv, so, sdo, sdq, sdk, sdv;   // strides of q, k, v, o (forward output or backward input), dO, dq, dk, dv
     int dq_acc_zeroed;  // backward: the pre-pass has already cleared dq_acc (otherwise the launcher of the main kernel does)
 };
 
@@ -178,6 +196,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
         "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+// 4-D tiled TMA load (coordinates: head-dim column, row, head, batch) into shared memory, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int x, int n, int h, int b, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(n), "r"(h), "r"(b)
         : "memory");
 }
 // 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on an mbarrier.
@@ -539,10 +564,11 @@ int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s);
 int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint32_t* packed, int N, int half_d, cudaStream_t s, int half_src = -1);
 // cos / sin tables [N, half_d] fp32 for positions 0 .. N-1 from per-pair frequencies: angle = float(n) * inv_freq[d]
 int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, cudaStream_t s);
-int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
-int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s);
-int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
-                          cudaStream_t s);   // H = heads of x
+// x / out: [B, H, N, 64] with strides st (the padded side is contiguous [B*H*N, 128])
+int launch_pad_d64(const void* x, const Strides& st, void* out, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s);
+int launch_unpad_d64(const void* xp, void* out, const Strides& st, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s);
+int launch_rope_prerotate(const void* x, const Strides& st, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale,
+                          int dtype, cudaStream_t s);   // H = heads of x; out is contiguous [B*H*N, 128]
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
 int launch_rope_fwd_tc(const RopeParams& p, int dtype, cudaStream_t s);
 bool rope_bwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);
@@ -575,6 +601,32 @@ inline int encode_tensor_map_2d_sw128(CUtensorMap* out, const void* base, uint64
     cuuint32_t estr[2] = {1, 1};
     CUtensorMapDataType dt = dtype == COROPE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = fn(out, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : COROPE_ERR_TENSOR_MAP;
+}
+
+// The same for a [B, H, N, D] tensor of 16-bit elements with arbitrary batch / head / row strides (multiples of 8 elements):
+// a 4-D map with dimensions (D, N, H, B) and a [box_rows, box_cols] box inside one head.  Rows beyond N read as zeros.
+inline int encode_tensor_map_4d_sw128(CUtensorMap* out, const void* base, uint64_t B, uint64_t H, uint64_t N, uint64_t D, const Strides& st,
+                                      uint32_t box_rows, uint32_t box_cols, int dtype) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                 CUtensorMapFloatOOBfill);
+    static EncodeFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !sym) return COROPE_ERR_NO_DEVICE;
+        fn = (EncodeFn)sym;
+    }
+    cuuint64_t gdim[4] = {D, N, H, B};
+    // a dimension of extent 1 is never stepped over, but its stride still has to be a valid one
+    cuuint64_t gstride[3] = {(cuuint64_t)st.n * 2, (cuuint64_t)(H > 1 ? st.h : st.n * (int64_t)N) * 2, (cuuint64_t)(B > 1 ? st.b : st.n * (int64_t)N) * 2};
+    cuuint32_t box[4] = {box_cols, box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMapDataType dt = dtype == COROPE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUresult r = fn(out, dt, 4, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : COROPE_ERR_TENSOR_MAP;
 }

@@ -56,6 +56,7 @@ extern "C" int corope_rope_attn_fwd_noalloc(const void* q, const void* k, const 
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2;
     p.cos = cos; p.sin = sin; p.table_stride = table_row_stride;
     p.B = B; p.H = H; p.Hkv = H; p.N = N; p.D = D; p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.status = status_word;
+    p.sq = p.sk = p.sv = p.so = contiguous_strides(H, N, D);
     // the kernel-selection policy of the diagnostics header applies here too: 1 = general kernels; 0 and 2 both mean the
     // tensor-core kernel with its in-kernel K rotation (this entry point has no room for a rotated copy)
     if (kernel_policy() != 1 && rope_fwd_tc_supported(B, H, N, D, dtype, causal)) {

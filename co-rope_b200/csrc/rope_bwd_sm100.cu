@@ -200,18 +200,19 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 mbar_arrive(&bars[UNIT_FULL + slot]);
                 if (w < 0) break;
                 const Unit un = unit_of(w, n_kb, BH);
-                const int row_base = un.bh * N;
                 const int q_first = causal ? un.jb * kBK : 0;
                 const int spg = (N - q_first) / kBQ, n_steps = G * spg;
                 auto load_step = [&](int s) -> bool {
                     const int gs = g + s, st = gs % kStages;
                     if (gs >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((gs / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) return false;
-                    const int qr = step_row(un.bh, q_first, spg, s);
+                    const int qr = step_row(un.bh, q_first, spg, s);   // flat row of the contiguous side inputs (LSE, delta)
+                    const int qhead = un.bh * G + s / spg, q0 = step_q0(q_first, spg, s);
+                    const int qb = qhead / p.H, qh = qhead % p.H;      // coordinates of the 4-D maps
                     mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
-                    tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
-                    tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
-                    tma_load_2d(sDO + st * kQBytes, &mapDO, 0, qr, &bars[QDO_FULL + st]);
-                    tma_load_2d(sDO + st * kQBytes + kQBox, &mapDO, 64, qr, &bars[QDO_FULL + st]);
+                    tma_load_4d(sQ + st * kQBytes, &mapQ, 0, q0, qh, qb, &bars[QDO_FULL + st]);
+                    tma_load_4d(sQ + st * kQBytes + kQBox, &mapQ, 64, q0, qh, qb, &bars[QDO_FULL + st]);
+                    tma_load_4d(sDO + st * kQBytes, &mapDO, 0, q0, qh, qb, &bars[QDO_FULL + st]);
+                    tma_load_4d(sDO + st * kQBytes + kQBox, &mapDO, 64, q0, qh, qb, &bars[QDO_FULL + st]);
                     bulk_load_1d(sLD + st * 2 * kBQ, p.lse2 + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
                     bulk_load_1d(sLD + st * 2 * kBQ + kBQ, p.delta + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
                     return true;
@@ -221,13 +222,13 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (!(ok = load_step(0) && load_step(1))) break;
                 // K and V are read by MMAs up to the previous unit's last step
                 if (n > 0 && !(ok = mbar_wait(&bars[ACC_FULL], (n - 1) & 1, p.status, ACC_FULL, abort_flag))) break;
-                const int kr = row_base + un.jb * kBK;
+                const int kr = un.jb * kBK, kb = un.bh / p.Hkv, kh = un.bh % p.Hkv;
                 mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
-                tma_load_2d(sK, &mapK, 0, kr, &bars[K_FULL]);
-                tma_load_2d(sK + kKVBox, &mapK, 64, kr, &bars[K_FULL]);
+                tma_load_4d(sK, &mapK, 0, kr, kh, kb, &bars[K_FULL]);
+                tma_load_4d(sK + kKVBox, &mapK, 64, kr, kh, kb, &bars[K_FULL]);
                 mbar_arrive_expect_tx(&bars[V_FULL], kKVBytes);
-                tma_load_2d(sV, &mapV, 0, kr, &bars[V_FULL]);
-                tma_load_2d(sV + kKVBox, &mapV, 64, kr, &bars[V_FULL]);
+                tma_load_4d(sV, &mapV, 0, kr, kh, kb, &bars[V_FULL]);
+                tma_load_4d(sV + kKVBox, &mapV, 64, kr, kh, kb, &bars[V_FULL]);
                 for (int s = 2; ok && s < n_steps; ++s) ok = load_step(s);
                 g += n_steps;
             }
@@ -387,7 +388,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
         if (w < 0) break;
         const Unit un = unit_of(w, n_kb, BH);
-        const int jb = un.jb, row_base = un.bh * N;
+        const int jb = un.jb;
         const int q_first = causal ? jb * kBK : 0;
         const int spg = (N - q_first) / kBQ, n_steps = G * spg;
         const int key = jb * kBK + row;
@@ -441,9 +442,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (ok) ok = mbar_wait_warp(&bars[ACC_FULL], n & 1, p.status, ACC_FULL, abort_flag);
         if (ok) {
             tc_fence_after();
-            const size_t grow = (size_t)row_base + key;
             if (wg == 0) {
-                T* dst = reinterpret_cast<T*>(p.dv) + grow * kD;
+                T* dst = reinterpret_cast<T*>(p.dv) + row_offset(p.sdv, p.Hkv, un.bh, key);
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -457,7 +457,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     for (int i = 0; i < 4; ++i) d4[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
                 }
             } else {
-                T* dst = reinterpret_cast<T*>(p.dk) + grow * kD;
+                T* dst = reinterpret_cast<T*>(p.dk) + row_offset(p.sdk, p.Hkv, un.bh, key);
                 const uint32_t* tab = p.packed_tab + (size_t)key * (kD / 2);
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -503,7 +503,6 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         const int w = fetch_unit(bars, unit_ring, n, lane, p.status, abort_flag);
         if (w < 0) break;
         const Unit un = unit_of(w, n_kb, BH);
-        const int row_base = un.bh * N;
         const int q_first = causal ? un.jb * kBK : 0;
         const int spg = (N - q_first) / kBQ, n_steps = G * spg;
         for (int s = 0; s < n_steps; ++s) {
@@ -548,7 +547,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 // 64 columns when a D = 64 problem runs zero-padded; the packed table then holds the identity in columns 32..63), 8-byte stores
 template <typename T>
 __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const uint32_t* __restrict__ packed,
-                                            size_t rows, int N, float scale) {
+                                            size_t rows, int N, float scale, Strides sdq, int H) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 16) return;
     const size_t row = idx >> 4;
@@ -564,20 +563,22 @@ __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __
     o1.y = pack2<T>((x1[2] * cs[2].x + x2[2] * cs[2].y) * scale, (x1[3] * cs[3].x + x2[3] * cs[3].y) * scale);
     o2.x = pack2<T>((x2[0] * cs[0].x - x1[0] * cs[0].y) * scale, (x2[1] * cs[1].x - x1[1] * cs[1].y) * scale);
     o2.y = pack2<T>((x2[2] * cs[2].x - x1[2] * cs[2].y) * scale, (x2[3] * cs[3].x - x1[3] * cs[3].y) * scale);
-    *reinterpret_cast<uint2*>(dq + row * kD + d) = o1;
-    *reinterpret_cast<uint2*>(dq + row * kD + d + 64) = o2;
+    T* out = dq + row_offset(sdq, H, (int)(row / (size_t)N), pos);
+    *reinterpret_cast<uint2*>(out + d) = o1;
+    *reinterpret_cast<uint2*>(out + d + 64) = o2;
 }
 
 template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv, mdo, mdq;
-    const uint64_t rows = (uint64_t)p.B * p.H * p.N, kv_rows = (uint64_t)p.B * p.Hkv * p.N;
-    if (int e = p.q_rot ? encode_tensor_map_2d_sw128(&mq, p.q_rot, rows, kD, kBQ, 64, COROPE_DTYPE_F16)
-                        : encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBQ, 64, dtype))
+    const uint64_t rows = (uint64_t)p.B * p.H * p.N;
+    // 4-D maps (head dim, row, head, batch) over the caller's tensors with their own strides; the pre-rotated Q copy is contiguous
+    if (int e = p.q_rot ? encode_tensor_map_4d_sw128(&mq, p.q_rot, p.B, p.H, p.N, kD, contiguous_strides(p.H, p.N, kD), kBQ, 64, COROPE_DTYPE_F16)
+                        : encode_tensor_map_4d_sw128(&mq, p.q, p.B, p.H, p.N, kD, p.sq, kBQ, 64, dtype))
         return e;
-    if (int e = encode_tensor_map_2d_sw128(&mdo, p.d_o, rows, kD, kBQ, 64, dtype)) return e;
-    if (int e = encode_tensor_map_2d_sw128(&mk, p.k, kv_rows, kD, kBK, 64, dtype)) return e;
-    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, kv_rows, kD, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_4d_sw128(&mdo, p.d_o, p.B, p.H, p.N, kD, p.sdo, kBQ, 64, dtype)) return e;
+    if (int e = encode_tensor_map_4d_sw128(&mk, p.k, p.B, p.Hkv, p.N, kD, p.sk, kBK, 64, dtype)) return e;
+    if (int e = encode_tensor_map_4d_sw128(&mv, p.v, p.B, p.Hkv, p.N, kD, p.sv, kBK, 64, dtype)) return e;
     if (int e = encode_tensor_map_2d_f32(&mdq, p.dq_acc, rows, kD, kBQ, kD)) return e;
     cudaError_t e = p.dq_acc_zeroed ? cudaSuccess : cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
@@ -594,7 +595,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     if (e != cudaSuccess) return (int)e;
     const size_t n = rows * 16;
     rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.packed_tab, rows, p.N,
-                                                                              p.sm_scale); count_launch();
+                                                                              p.sm_scale, p.sdq, p.H); count_launch();
     return (int)cudaGetLastError();
 }
 

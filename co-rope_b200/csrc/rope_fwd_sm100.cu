@@ -135,8 +135,8 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     const int BH = p.B * p.H;
     const int G = p.H / p.Hkv;   // query heads per K / V head (1 for the fused-RoPE ops); query head bh reads KV head bh / G
     // N is a multiple of 128: when it is not a multiple of 256 the last item of a head has only Q0; its Q1 tile (and, causal,
-    // the K tile behind the diagonal) lies beyond the head -- TMA fetches whatever is there (the next head's rows, zeros
-    // behind the tensor), the results are finite and are not stored
+    // the K tile behind the diagonal) lies beyond the head -- TMA fills those rows with zeros, the results are finite and are
+    // not stored
     const int n_qt = (N + 2 * kBM - 1) / (2 * kBM);
     const int n_items = n_qt * BH;
     // K tiles an item sees: up to its diagonal (causal: Q0 one tile less than Q1), or all of them
@@ -212,22 +212,23 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     mbar_arrive(&bars[ITEM_FULL + slot]);
                     if (w < 0) break;
                     const WorkItem wi = work_item(w, n_qt, BH);
-                    const int row_base = wi.bh * N, nk = causal ? 2 * wi.t + 2 : nk_all;
+                    const int nk = causal ? 2 * wi.t + 2 : nk_all;
+                    const int qb = wi.bh / p.H, qh = wi.bh % p.H;                       // batch and head coordinates of the 4-D maps
+                    const int kb = (wi.bh / G) / p.Hkv, kh = (wi.bh / G) % p.Hkv;
                     for (int i = 0; i < 2; ++i) {
                         if (n > 0 && !(ok = mbar_wait(&bars[Q_EMPTY + i], (n - 1) & 1, p.status, Q_EMPTY, abort_flag))) break;
-                        const int r = row_base + wi.t * 2 * kBM + i * kBM;
+                        const int r = wi.t * 2 * kBM + i * kBM;   // rows at or beyond N (a head's last, half-empty item) read as zeros
                         mbar_arrive_expect_tx(&bars[Q_FULL + i], kTileBytes);
-                        tma_load_2d(sQ + i * kTileBytes, &mapQ, 0, r, &bars[Q_FULL + i]);
-                        tma_load_2d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, &bars[Q_FULL + i]);
+                        tma_load_4d(sQ + i * kTileBytes, &mapQ, 0, r, qh, qb, &bars[Q_FULL + i]);
+                        tma_load_4d(sQ + i * kTileBytes + kBoxBytes, &mapQ, 64, r, qh, qb, &bars[Q_FULL + i]);
                     }
-                    const int kv_base = (wi.bh / G) * N;
                     for (int j = 0; ok && j < nk; ++j, ++gk) {
-                        const int r = kv_base + j * kBN;
+                        const int r = j * kBN;
                         const int ks = gk % kKStages;
                         if (gk >= kKStages && !(ok = mbar_wait(&bars[K_EMPTY + ks], ((gk / kKStages) - 1) & 1, p.status, K_EMPTY, abort_flag))) break;
                         mbar_arrive_expect_tx(&bars[K_FULL + ks], kTileBytes);
-                        tma_load_2d(sK + ks * kTileBytes, &mapK, 0, r, &bars[K_FULL + ks]);
-                        tma_load_2d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, &bars[K_FULL + ks]);
+                        tma_load_4d(sK + ks * kTileBytes, &mapK, 0, r, kh, kb, &bars[K_FULL + ks]);
+                        tma_load_4d(sK + ks * kTileBytes + kBoxBytes, &mapK, 64, r, kh, kb, &bars[K_FULL + ks]);
                     }
                 }
             }
@@ -241,14 +242,15 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int w = fetch_item(bars, item_ring, n, lane, false, p.status, abort_flag);
                     if (w < 0) break;
                     const WorkItem wi = work_item(w, n_qt, BH);
-                    const int row_base = (wi.bh / G) * N, nk = causal ? 2 * wi.t + 2 : nk_all;
+                    const int nk = causal ? 2 * wi.t + 2 : nk_all;
+                    const int kb = (wi.bh / G) / p.Hkv, kh = (wi.bh / G) % p.Hkv;
                     for (int j = 0; j < nk; ++j, ++gv) {
-                        const int r = row_base + j * kBN;
+                        const int r = j * kBN;
                         const int vs = gv % kVStages;
                         if (gv >= kVStages && !(ok = mbar_wait(&bars[V_EMPTY + vs], ((gv / kVStages) - 1) & 1, p.status, V_EMPTY, abort_flag))) break;
                         mbar_arrive_expect_tx(&bars[V_FULL + vs], kTileBytes);
-                        tma_load_2d(sV + vs * kTileBytes, &mapV, 0, r, &bars[V_FULL + vs]);
-                        tma_load_2d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, &bars[V_FULL + vs]);
+                        tma_load_4d(sV + vs * kTileBytes, &mapV, 0, r, kh, kb, &bars[V_FULL + vs]);
+                        tma_load_4d(sV + vs * kTileBytes + kBoxBytes, &mapV, 64, r, kh, kb, &bars[V_FULL + vs]);
                     }
                 }
             }
@@ -491,8 +493,8 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tc_fence_after();
             const float inv = 1.f / l_tot;
             const bool in_head = (2 * wi.t + wg) * kBM < N;   // false for the Q1 tile of a head's last, half-empty item
-            const size_t grow = (size_t)wi.bh * N + (size_t)(2 * wi.t + wg) * kBM + row;
-            T* orow = reinterpret_cast<T*>(p.out_o) + grow * kD + half * 64;
+            const size_t grow = (size_t)wi.bh * N + (size_t)(2 * wi.t + wg) * kBM + row;   // row of the (contiguous) LSE
+            T* orow = reinterpret_cast<T*>(p.out_o) + row_offset(p.so, p.H, wi.bh, (2 * wi.t + wg) * kBM + row) + half * 64;
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t r[32];
@@ -523,12 +525,12 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv;
-    const uint64_t rows = (uint64_t)p.B * p.H * p.N, kv_rows = (uint64_t)p.B * p.Hkv * p.N;
-    if (int e = encode_tensor_map_2d_sw128(&mq, p.q, rows, kD, kBM, 64, dtype)) return e;
-    if (int e = p.k_rot ? encode_tensor_map_2d_sw128(&mk, p.k_rot, kv_rows, kD, kBN, 64, COROPE_DTYPE_F16)
-                        : encode_tensor_map_2d_sw128(&mk, p.k, kv_rows, kD, kBN, 64, dtype))
+    // 4-D maps (head dim, row, head, batch): the caller's q / k / v with their own strides; the pre-rotated K copy is contiguous
+    if (int e = encode_tensor_map_4d_sw128(&mq, p.q, p.B, p.H, p.N, kD, p.sq, kBM, 64, dtype)) return e;
+    if (int e = p.k_rot ? encode_tensor_map_4d_sw128(&mk, p.k_rot, p.B, p.Hkv, p.N, kD, contiguous_strides(p.Hkv, p.N, kD), kBN, 64, COROPE_DTYPE_F16)
+                        : encode_tensor_map_4d_sw128(&mk, p.k, p.B, p.Hkv, p.N, kD, p.sk, kBN, 64, dtype))
         return e;
-    if (int e = encode_tensor_map_2d_sw128(&mv, p.v, kv_rows, kD, kBN, 64, dtype)) return e;
+    if (int e = encode_tensor_map_4d_sw128(&mv, p.v, p.B, p.Hkv, p.N, kD, p.sv, kBN, 64, dtype)) return e;
     auto kern = rope_fwd_sm100_kernel<T>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;

@@ -16,6 +16,11 @@
 namespace corope {
 namespace {
 
+// element offset of flat row index `row` (= (b * H + h) * N + n) in a strided [B, H, N, D] tensor
+__device__ __forceinline__ int64_t flat_row_offset(const Strides& st, int H, int N, size_t row) {
+    return row_offset(st, H, (int)(row / (size_t)N), (int)(row % (size_t)N));
+}
+
 constexpr int kRows = 32;     // rows per CTA
 constexpr int kTile = 32;     // streamed rows per step
 constexpr int kThreads = 128;
@@ -35,16 +40,16 @@ __device__ __forceinline__ float warp_sum(float v) {
 // Stage `kTile` rows [r0, r0+32) of X[N][D] into dst[32][LD] as fp32, rotated by the half-layout RoPE
 // and multiplied by `scale`.  Rows >= N become zeros.
 template <typename T, int D, int LD, bool ROTATE>
-__device__ __forceinline__ void stage_rows(float* dst, const T* X, int r0, int N, const float* cosT, const float* sinT, int64_t ts,
-                                           float scale) {
+__device__ __forceinline__ void stage_rows(float* dst, const T* X, int64_t xs, int r0, int N, const float* cosT, const float* sinT, int64_t ts,
+                                           float scale) {   // xs: row stride of X in elements
     constexpr int H2 = D / 2;
     for (int idx = threadIdx.x; idx < kTile * H2; idx += kThreads) {
         int r = idx / H2, d = idx % H2;
         int pos = r0 + r;
         float y1 = 0.f, y2 = 0.f;
         if (pos < N) {
-            float x1 = Elem<T>::to_f32(X[(size_t)pos * D + d]);
-            float x2 = Elem<T>::to_f32(X[(size_t)pos * D + d + H2]);
+            float x1 = Elem<T>::to_f32(X[(int64_t)pos * xs + d]);
+            float x2 = Elem<T>::to_f32(X[(int64_t)pos * xs + d + H2]);
             if (ROTATE && cosT != nullptr) {   // null tables: plain attention, no rotation
                 float c = cosT[pos * ts + d], s = sinT[pos * ts + d];
                 y1 = (x1 * c - x2 * s) * scale;
@@ -139,12 +144,12 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
     const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;  // longest causal rows first
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kvh = bh / (p.H / p.Hkv);   // [B, H] flattened -> [B, Hkv] flattened: the heads of a group are adjacent
-    const T* Q = reinterpret_cast<const T*>(p.q) + (size_t)bh * N * D;
-    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)kvh * N * D;
-    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)kvh * N * D;
-    T* O = reinterpret_cast<T*>(p.out_o) + (size_t)bh * N * D;
+    const T* Q = reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.H, bh, 0);
+    const T* K = reinterpret_cast<const T*>(p.k) + row_offset(p.sk, p.Hkv, kvh, 0);
+    const T* V = reinterpret_cast<const T*>(p.v) + row_offset(p.sv, p.Hkv, kvh, 0);
+    T* O = reinterpret_cast<T*>(p.out_o) + row_offset(p.so, p.H, bh, 0);
 
-    stage_rows<T, D, D, true>(q_s, Q, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+    stage_rows<T, D, D, true>(q_s, Q, p.sq.n, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
 
     float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][NC];
 #pragma unroll
@@ -158,8 +163,8 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
     const int n_end = p.causal ? min(N, m0 + kRows) : N;
     for (int j0 = 0; j0 < n_end; j0 += kTile) {
         __syncthreads();
-        stage_rows<T, D, D + 1, true>(k_s, K, j0, N, p.cos, p.sin, p.table_stride, 1.f);
-        stage_rows<T, D, D, false>(v_s, V, j0, N, nullptr, nullptr, 0, 1.f);
+        stage_rows<T, D, D + 1, true>(k_s, K, p.sk.n, j0, N, p.cos, p.sin, p.table_stride, 1.f);
+        stage_rows<T, D, D, false>(v_s, V, p.sv.n, j0, N, nullptr, nullptr, 0, 1.f);
         __syncthreads();
         float s[kRowsPerWarp];
         dot_rows<D>(s, q_s, row0, k_s, lane);
@@ -186,7 +191,7 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
         if (i >= N) continue;
         float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) O[(size_t)i * D + lane + 32 * c] = Elem<T>::from_f32(acc[r][c] * inv);
+        for (int c = 0; c < NC; ++c) O[(int64_t)i * p.so.n + lane + 32 * c] = Elem<T>::from_f32(acc[r][c] * inv);
         if (lane == 0) p.lse2[(size_t)bh * N + i] = m[r] + log2f(l[r]);
     }
 }
@@ -195,26 +200,30 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
 // delta = rowsum(O * dO)   (fused_rope_attn.py:324-337)
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D) {
+__global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D, Strides so,
+                                  Strides sdo, int H, int N) {
     size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
     float s = 0.f;
-    for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(o[row * D + d]) * Elem<T>::to_f32(d_o[row * D + d]);
+    const T* orow = o + flat_row_offset(so, H, N, row);
+    const T* drow = d_o + flat_row_offset(sdo, H, N, row);
+    for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(orow[d]) * Elem<T>::to_f32(drow[d]);
     s = warp_sum(s);
     if (lane == 0) delta[row] = s;
 }
 
 // Same for 16-bit elements and D = 128: 16 threads per row, 16 bytes of O and of dO per thread.
 template <typename T>
-__global__ void rope_delta_d128_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows) {
+__global__ void rope_delta_d128_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, Strides so,
+                                       Strides sdo, int H, int N) {
     const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t row = t >> 4;
     const int part = (int)(t & 15);
     float s = 0.f;
     if (row < rows) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + row * 128) + part);
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + row * 128) + part);
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(so, H, N, row)) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(sdo, H, N, row)) + part);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -244,16 +253,15 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParam
     const int bh = blockIdx.y;
     const int m0 = (gridDim.x - 1 - blockIdx.x) * kRows;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t base = (size_t)bh * N * D;
-    const size_t kv_base = (size_t)(bh / (p.H / p.Hkv)) * N * D;
-    const T* Q = reinterpret_cast<const T*>(p.q) + base;
-    const T* K = reinterpret_cast<const T*>(p.k) + kv_base;
-    const T* V = reinterpret_cast<const T*>(p.v) + kv_base;
-    const T* DO = reinterpret_cast<const T*>(p.d_o) + base;
-    T* DQ = reinterpret_cast<T*>(p.dq) + base;
+    const int kvh = bh / (p.H / p.Hkv);
+    const T* Q = reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.H, bh, 0);
+    const T* K = reinterpret_cast<const T*>(p.k) + row_offset(p.sk, p.Hkv, kvh, 0);
+    const T* V = reinterpret_cast<const T*>(p.v) + row_offset(p.sv, p.Hkv, kvh, 0);
+    const T* DO = reinterpret_cast<const T*>(p.d_o) + row_offset(p.sdo, p.H, bh, 0);
+    T* DQ = reinterpret_cast<T*>(p.dq) + row_offset(p.sdq, p.H, bh, 0);
 
-    stage_rows<T, D, D, true>(q_s, Q, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
-    stage_rows<T, D, D, false>(do_s, DO, m0, N, nullptr, nullptr, 0, 1.f);
+    stage_rows<T, D, D, true>(q_s, Q, p.sq.n, m0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+    stage_rows<T, D, D, false>(do_s, DO, p.sdo.n, m0, N, nullptr, nullptr, 0, 1.f);
 
     const int row0 = warp * kRowsPerWarp;
     float lse[kRowsPerWarp], dl[kRowsPerWarp], acc[kRowsPerWarp][NC];
@@ -268,8 +276,8 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParam
     const int n_end = p.causal ? min(N, m0 + kRows) : N;
     for (int j0 = 0; j0 < n_end; j0 += kTile) {
         __syncthreads();
-        stage_rows<T, D, D + 1, true>(k_s, K, j0, N, p.cos, p.sin, p.table_stride, 1.f);
-        stage_rows<T, D, D + 1, false>(v_s, V, j0, N, nullptr, nullptr, 0, 1.f);
+        stage_rows<T, D, D + 1, true>(k_s, K, p.sk.n, j0, N, p.cos, p.sin, p.table_stride, 1.f);
+        stage_rows<T, D, D + 1, false>(v_s, V, p.sv.n, j0, N, nullptr, nullptr, 0, 1.f);
         __syncthreads();
         float s[kRowsPerWarp], dp[kRowsPerWarp];
         dot_rows<D>(s, q_s, row0, k_s, lane);
@@ -288,7 +296,7 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dq_general_kernel(RopeParam
     for (int r = 0; r < kRowsPerWarp; ++r) {
         const int i = m0 + row0 + r;
         if (i >= N) continue;  // warp-uniform: i does not depend on the lane
-        store_inverse_rotated<T, D>(DQ + (size_t)i * D, acc[r], i, p.cos, p.sin, p.table_stride, p.sm_scale, lane, p.cos != nullptr);
+        store_inverse_rotated<T, D>(DQ + (int64_t)i * p.sdq.n, acc[r], i, p.cos, p.sin, p.table_stride, p.sm_scale, lane, p.cos != nullptr);
     }
 }
 
@@ -311,14 +319,13 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
     const int G = p.H / p.Hkv;
     const int n0 = blockIdx.x * kRows;  // causal: low key blocks are the long ones and come first
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const size_t base = (size_t)kvh * N * D;
-    const T* K = reinterpret_cast<const T*>(p.k) + base;
-    const T* V = reinterpret_cast<const T*>(p.v) + base;
-    T* DK = reinterpret_cast<T*>(p.dk) + base;
-    T* DV = reinterpret_cast<T*>(p.dv) + base;
+    const T* K = reinterpret_cast<const T*>(p.k) + row_offset(p.sk, p.Hkv, kvh, 0);
+    const T* V = reinterpret_cast<const T*>(p.v) + row_offset(p.sv, p.Hkv, kvh, 0);
+    T* DK = reinterpret_cast<T*>(p.dk) + row_offset(p.sdk, p.Hkv, kvh, 0);
+    T* DV = reinterpret_cast<T*>(p.dv) + row_offset(p.sdv, p.Hkv, kvh, 0);
 
-    stage_rows<T, D, D, true>(k_s, K, n0, N, p.cos, p.sin, p.table_stride, 1.f);
-    stage_rows<T, D, D, false>(v_s, V, n0, N, nullptr, nullptr, 0, 1.f);
+    stage_rows<T, D, D, true>(k_s, K, p.sk.n, n0, N, p.cos, p.sin, p.table_stride, 1.f);
+    stage_rows<T, D, D, false>(v_s, V, p.sv.n, n0, N, nullptr, nullptr, 0, 1.f);
 
     const int row0 = warp * kRowsPerWarp;
     float dk[kRowsPerWarp][NC], dv[kRowsPerWarp][NC];
@@ -330,12 +337,12 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
     const int i_begin = p.causal ? n0 : 0;
     for (int g = 0; g < G; ++g) {   // dK / dV are summed over the group's query heads
     const int bh = kvh * G + g;
-    const T* Q = reinterpret_cast<const T*>(p.q) + (size_t)bh * N * D;
-    const T* DO = reinterpret_cast<const T*>(p.d_o) + (size_t)bh * N * D;
+    const T* Q = reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.H, bh, 0);
+    const T* DO = reinterpret_cast<const T*>(p.d_o) + row_offset(p.sdo, p.H, bh, 0);
     for (int i0 = i_begin; i0 < N; i0 += kTile) {
         __syncthreads();
-        stage_rows<T, D, D + 1, true>(q_s, Q, i0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
-        stage_rows<T, D, D + 1, false>(do_s, DO, i0, N, nullptr, nullptr, 0, 1.f);
+        stage_rows<T, D, D + 1, true>(q_s, Q, p.sq.n, i0, N, p.cos, p.sin, p.table_stride, p.sm_scale * kLog2e);
+        stage_rows<T, D, D + 1, false>(do_s, DO, p.sdo.n, i0, N, nullptr, nullptr, 0, 1.f);
         if (threadIdx.x < kTile) {
             int i = i0 + threadIdx.x;
             lse_s[threadIdx.x] = i < N ? p.lse2[(size_t)bh * N + i] : 0.f;
@@ -364,9 +371,9 @@ __global__ void __launch_bounds__(kThreads) rope_bwd_dkdv_general_kernel(RopePar
         const int j = n0 + row0 + r;
         if (j >= N) continue;
 #pragma unroll
-        for (int c = 0; c < NC; ++c) DV[(size_t)j * D + lane + 32 * c] = Elem<T>::from_f32(dv[r][c]);
+        for (int c = 0; c < NC; ++c) DV[(int64_t)j * p.sdv.n + lane + 32 * c] = Elem<T>::from_f32(dv[r][c]);
         // q_s carried sm_scale * log2e, so dk holds dK~ * log2e: undo with ln2
-        store_inverse_rotated<T, D>(DK + (size_t)j * D, dk[r], j, p.cos, p.sin, p.table_stride, kLn2, lane, p.cos != nullptr);
+        store_inverse_rotated<T, D>(DK + (int64_t)j * p.sdk.n, dk[r], j, p.cos, p.sin, p.table_stride, kLn2, lane, p.cos != nullptr);
     }
 }
 
@@ -400,7 +407,8 @@ __global__ void synth_tables_kernel(const float* __restrict__ inv_freq, float* _
 // D = 128 kernels: first half of the row (32 columns) to columns 0..31, second half to columns 64..95; "plain" layout
 // puts the 64 columns first.  Everything else is zero, so dot products and rotations are unchanged.
 template <typename T>
-__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout) {
+__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout, Strides st, int H,
+                                                      int N) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16 output chunks
     if (idx >= rows * 16) return;
     const size_t r = idx >> 4;
@@ -413,17 +421,18 @@ __global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T
         src = c;
     }
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + r * 64 + src * 8);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + flat_row_offset(st, H, N, r) + src * 8);
     *reinterpret_cast<uint4*>(out + r * 128 + c * 8) = v;
 }
 template <typename T>
-__global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout) {
+__global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout, Strides st,
+                                                        int H, int N) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 8 output chunks
     if (idx >= rows * 8) return;
     const size_t r = idx >> 3;
     const int c = (int)(idx & 7);
     const int src = rope_layout ? (c < 4 ? c : c + 4) : c;
-    *reinterpret_cast<uint4*>(out + r * 64 + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
+    *reinterpret_cast<uint4*>(out + flat_row_offset(st, H, N, r) + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
 }
 
 // Rotation as a pass of its own, for the tensor-core kernels at D = 128: out[r, :] = rot(x[r, :]) * scale as fp16, with the
@@ -433,13 +442,14 @@ __global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp
 // its diagonal).  One thread = 8 pairs of one row: two 16-byte loads, 32 bytes of table, two 16-byte stores.
 template <typename T>
 __global__ void __launch_bounds__(256) rope_prerotate_d128_kernel(const T* __restrict__ x, __half* __restrict__ out,
-                                                                   const uint32_t* __restrict__ tab, size_t rows, int N, float scale) {
+                                                                   const uint32_t* __restrict__ tab, size_t rows, int N, float scale, Strides st,
+                                                                   int H) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 8) return;
     const size_t row = idx >> 3;
     const int c = (int)(idx & 7) * 8;
     const int n = (int)(row % (size_t)N);
-    const uint4* src = reinterpret_cast<const uint4*>(x + row * 128 + c);
+    const uint4* src = reinterpret_cast<const uint4*>(x + flat_row_offset(st, H, N, row) + c);
     uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
     const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
     const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
@@ -457,19 +467,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) rope_bwd_prepass_d128_kernel(const T* __restrict__ q, const T* __restrict__ o, const T* __restrict__ d_o,
                                                                      const uint32_t* __restrict__ tab, __half* __restrict__ q_rot,
                                                                      float* __restrict__ delta, float* __restrict__ dq_acc, size_t rows, int N,
-                                                                     float scale) {
+                                                                     float scale, Strides sq, Strides so, Strides sdo, int H) {
     const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t row = t >> 4;
     const int part = (int)(t & 15);
     const bool live = row < rows;
     float s = 0.f;
     if (live) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + row * 128) + part);
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + row * 128) + part);
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(so, H, N, row)) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(sdo, H, N, row)) + part);
         if (part < 8) {
             const int c = part * 8;
             const int n = (int)(row % (size_t)N);
-            const uint4* src = reinterpret_cast<const uint4*>(q + row * 128 + c);
+            const uint4* src = reinterpret_cast<const uint4*>(q + flat_row_offset(sq, H, N, row) + c);
             uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
             const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
             const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
@@ -560,12 +570,16 @@ int launch_rope_bwd_general(const RopeParams& p, int dtype, cudaStream_t s) {
 
 int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     size_t rows = (size_t)p.B * p.H * p.N;
-    if (p.D == 128 && dtype != COROPE_DTYPE_F32) {
+    // the 16-bytes-per-thread form needs 16-byte aligned rows; row strides that are not multiples of 8 elements take the scalar form
+    auto aligned = [](const void* ptr, const Strides& st) {
+        return ((uintptr_t)ptr % 16) == 0 && st.b % 8 == 0 && st.h % 8 == 0 && st.n % 8 == 0;
+    };
+    if (p.D == 128 && dtype != COROPE_DTYPE_F32 && aligned(p.o, p.so) && aligned(p.d_o, p.sdo)) {
         const unsigned blocks = (unsigned)((rows * 16 + 255) / 256);
         if (dtype == COROPE_DTYPE_BF16)
-            rope_delta_d128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows);
+            rope_delta_d128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.so, p.sdo, p.H, p.N);
         else
-            rope_delta_d128_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows);
+            rope_delta_d128_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.so, p.sdo, p.H, p.N);
         count_launch();
         return (int)cudaGetLastError();
     }
@@ -573,28 +587,28 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     unsigned blocks = (unsigned)((rows + warps - 1) / warps);
     switch (dtype) {
         case COROPE_DTYPE_F32:
-            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D); count_launch();
+            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
             break;
         case COROPE_DTYPE_BF16:
             rope_delta_kernel<__nv_bfloat16>
-                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D); count_launch();
+                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
             break;
         case COROPE_DTYPE_F16:
-            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D); count_launch();
+            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
             break;
         default: return COROPE_ERR_BAD_DTYPE;
     }
     return (int)cudaGetLastError();
 }
 
-int launch_rope_prerotate(const void* x, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
+int launch_rope_prerotate(const void* x, const Strides& st, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale, int dtype,
                           cudaStream_t s) {
     const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale);
+        rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale, st, H);
     else
-        rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale);
+        rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale, st, H);
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -605,10 +619,10 @@ int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s) {
     const float scale = p.sm_scale * kLog2e;
     if (dtype == COROPE_DTYPE_BF16)
         rope_bwd_prepass_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)p.q, (const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o,
-                                                                        p.packed_tab, (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale);
+                                                                        p.packed_tab, (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, p.sq, p.so, p.sdo, p.H);
     else
         rope_bwd_prepass_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)p.q, (const __half*)p.o, (const __half*)p.d_o, p.packed_tab,
-                                                                 (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale);
+                                                                 (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, p.sq, p.so, p.sdo, p.H);
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -627,22 +641,24 @@ int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, i
     return (int)cudaGetLastError();
 }
 
-int launch_pad_d64(const void* x, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s) {
+int launch_pad_d64(const void* x, const Strides& st, void* out, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s) {
+    const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 16 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout);
+        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout, st, H, N);
     else
-        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout);
+        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout, st, H, N);
     count_launch();
     return (int)cudaGetLastError();
 }
 
-int launch_unpad_d64(const void* xp, void* out, size_t rows, int rope_layout, int dtype, cudaStream_t s) {
+int launch_unpad_d64(const void* xp, void* out, const Strides& st, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s) {
+    const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        unpad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)xp, (__nv_bfloat16*)out, rows, rope_layout);
+        unpad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)xp, (__nv_bfloat16*)out, rows, rope_layout, st, H, N);
     else
-        unpad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)xp, (__half*)out, rows, rope_layout);
+        unpad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)xp, (__half*)out, rows, rope_layout, st, H, N);
     count_launch();
     return (int)cudaGetLastError();
 }

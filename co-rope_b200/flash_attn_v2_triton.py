@@ -37,16 +37,17 @@ def _forward(q, k, v, causal, sm_scale):
     assert H_Q % H_KV == 0, "number of query heads must be a multiple of the number of K / V heads"
     for t in (q, k, v):
         _ext.require_cuda(t)
-    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    qc, kc, vc = _ext.kernel_layout(q), _ext.kernel_layout(k), _ext.kernel_layout(v)   # own strides, no copies (as :601-603)
     o = torch.empty_like(qc)
     M = torch.empty((B, H_Q, N), device=q.device, dtype=torch.float32)
     ws, ws_bytes = _ext.workspace(_ext.OP_FLASH_FWD, B, H_Q, H_KV, N, D, q.dtype, q.device)
+    st = _ext.strides_of(q=qc, k=kc, v=vc, o=o)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_flash_attn_fwd(
+        rc = _ext.lib().corope_flash_attn_fwd_strided(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), M.data_ptr(), B, H_Q, H_KV, N, D,
             _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
-            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_flash_attn_fwd")
     _ext.post_call(q.device)
     return qc, kc, vc, o, M
@@ -54,19 +55,20 @@ def _forward(q, k, v, causal, sm_scale):
 
 def _backward(q, k, v, o, M, do, causal, sm_scale):
     """One corope_flash_attn_bwd call on what _forward returned.  Returns (dq, dk, dv)."""
-    do = do.contiguous()
+    do = _ext.kernel_layout(do)
     B, H_Q, N, D = q.shape
     H_KV = k.shape[1]
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
     ws, ws_bytes = _ext.workspace(_ext.OP_FLASH_BWD, B, H_Q, H_KV, N, D, q.dtype, q.device)
+    st = _ext.strides_of(q=q, k=k, v=v, o=o, d_o=do, dq=dq, dk=dk, dv=dv)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_flash_attn_bwd(
+        rc = _ext.lib().corope_flash_attn_bwd_strided(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H_Q, H_KV, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)),
-            float(sm_scale), ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            float(sm_scale), ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_flash_attn_bwd")
     _ext.post_call(q.device)
     return dq, dk, dv

@@ -52,17 +52,20 @@ def _forward(q, k, v, causal, sm_scale, freqs_cos, freqs_sin):
     for t in (q, k, v):
         _ext.require_cuda(t)
     B, H, N, D = q.shape
-    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    # the kernels take the tensors' own strides, like the reference's (fused_rope_attn.py:709-710): a [B, N, H, D] buffer viewed
+    # as [B, H, N, D] is not copied, and o = empty_like(q) has q's layout (:662)
+    qc, kc, vc = _ext.kernel_layout(q), _ext.kernel_layout(k), _ext.kernel_layout(v)
     cos, sin, tstride = _tables(freqs_cos, freqs_sin, N, D, q.device)
     o = torch.empty_like(qc)
     M = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
     ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_FWD, B, H, H, N, D, q.dtype, q.device)
+    st = _ext.strides_of(q=qc, k=kc, v=vc, o=o)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_rope_attn_fwd(
+        rc = _ext.lib().corope_rope_attn_fwd_strided(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), cos.data_ptr(), sin.data_ptr(), tstride,
             o.data_ptr(), M.data_ptr(), B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
-            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_rope_attn_fwd")
     _ext.post_call(q.device)
     return qc, kc, vc, o, M, cos, sin, tstride
@@ -70,21 +73,22 @@ def _forward(q, k, v, causal, sm_scale, freqs_cos, freqs_sin):
 
 def _backward(q, k, v, o, M, cos, sin, tstride, do, causal, sm_scale):
     """One corope_rope_attn_bwd call on what _forward returned.  Returns (dq, dk, dv)."""
-    # the reference asserts contiguity and N % 128 == 0 (fused_rope_attn.py:727-728, 750); these kernels take any
-    # N, and a non-contiguous dO is made contiguous instead of rejected
-    do = do.contiguous()
+    # the reference asserts a contiguous dO, equal strides and N % 128 == 0 (fused_rope_attn.py:727-728, 750); these kernels
+    # take any N and every tensor's own strides
+    do = _ext.kernel_layout(do)
     B, H, N, D = q.shape
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
     ws, ws_bytes = _ext.workspace(_ext.OP_ROPE_BWD, B, H, H, N, D, q.dtype, q.device)
+    st = _ext.strides_of(q=q, k=k, v=v, o=o, d_o=do, dq=dq, dk=dk, dv=dv)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_rope_attn_bwd(
+        rc = _ext.lib().corope_rope_attn_bwd_strided(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
             cos.data_ptr(), sin.data_ptr(), tstride, dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             B, H, N, D, _ext.DTYPE_CODES[q.dtype], int(bool(causal)), float(sm_scale),
-            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_rope_attn_bwd")
     _ext.post_call(q.device)
     return dq, dk, dv

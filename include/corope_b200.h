@@ -3,7 +3,7 @@
  *
  * Plain pointers and sizes only; no C++ or torch types cross this boundary.  All tensor
  * pointers are DEVICE pointers.  q/k/v/o/dO/dq/dk/dv are row-major contiguous [B, H, N, D]
- * in the element type named by `dtype`.  Every call enqueues work on `stream` (a
+ * in the element type named by `dtype` (the *_strided entry points take other layouts).  Every call enqueues work on `stream` (a
  * cudaStream_t passed as void*) and returns without synchronising.
  *
  * Return value: 0 = OK, < 0 = argument error found on the host (nothing was launched),
@@ -60,6 +60,7 @@ extern "C" {
 #define COROPE_ERR_TENSOR_MAP (-8)     /* TMA descriptor could not be encoded */
 #define COROPE_ERR_NO_DEVICE (-9)      /* no sm_100 device / driver entry point */
 #define COROPE_ERR_TOO_LARGE (-10)     /* size beyond what the entry point supports */
+#define COROPE_ERR_BAD_STRIDE (-11)    /* row stride below D, or a negative stride */
 
 /* device-side status codes written to *status_word */
 #define COROPE_DEV_OK 0
@@ -125,6 +126,33 @@ int corope_rope_attn_bwd(const void* q, const void* k, const void* v, const void
                          int* status_word, void* stream);
 
 /*
+ * Strides, in elements, of the eight [B, H, N, D] tensors an op can touch: {batch, head, row} each; the head-dim stride is
+ * always 1.  The reference hands all four strides of q / k / v / o to its kernels (fused-rope/fused_rope_attn.py:709-710,
+ * flash_attn_v2_triton.py:601-603), so views such as a [B, N, H, D] buffer transposed to [B, H, N, D] need no copy there;
+ * the *_strided entry points below take them here.  Fields an op does not use (d_o, dq, dk, dv in a forward) are ignored.
+ * The tensor-core kernels need every used stride and base pointer to be a multiple of 16 bytes (8 elements for 16-bit
+ * types); other strides run on the CUDA-core kernels.  lse2 (and the tables) stay contiguous.  A NULL `strides` means
+ * contiguous tensors, i.e. the plain entry point.
+ */
+typedef struct corope_strides_t {
+    int64_t q[3], k[3], v[3], o[3], d_o[3], dq[3], dk[3], dv[3];
+} corope_strides_t;
+
+int corope_rope_attn_fwd_strided(const void* q, const void* k, const void* v,
+                                 const float* cos, const float* sin, int64_t table_row_stride,
+                                 void* o, float* lse2,
+                                 int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                                 void* workspace, size_t workspace_bytes,
+                                 int* status_word, void* stream, const corope_strides_t* strides);
+int corope_rope_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                 const float* lse2,
+                                 const float* cos, const float* sin, int64_t table_row_stride,
+                                 void* dq, void* dk, void* dv,
+                                 int B, int H, int N, int D, int dtype, int causal, float sm_scale,
+                                 void* workspace, size_t workspace_bytes,
+                                 int* status_word, void* stream, const corope_strides_t* strides);
+
+/*
  * Fused RoPE attention with the cos / sin tables synthesized on the device instead of read from the caller: the angle
  * of position n and pair d is float(n) * inv_freq[d] in fp32, exactly how precompute_freqs_cis forms it
  * (fused-rope/rope_attn_pytorch.py:29-47: inv_freq[d] = 1 / theta^(2d/D), positions 0 .. N-1), followed by cosf / sinf.
@@ -164,6 +192,18 @@ int corope_flash_attn_bwd(const void* q, const void* k, const void* v, const voi
                           int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
                           void* workspace, size_t workspace_bytes,
                           int* status_word, void* stream);
+
+int corope_flash_attn_fwd_strided(const void* q, const void* k, const void* v,
+                                  void* o, float* lse2,
+                                  int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
+                                  void* workspace, size_t workspace_bytes,
+                                  int* status_word, void* stream, const corope_strides_t* strides);
+int corope_flash_attn_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                  const float* lse2,
+                                  void* dq, void* dk, void* dv,
+                                  int B, int Hq, int Hkv, int N, int D, int dtype, int causal, float sm_scale,
+                                  void* workspace, size_t workspace_bytes,
+                                  int* status_word, void* stream, const corope_strides_t* strides);
 
 /*
  * Co-RoPE GQA attention forward (causal only).  Replaces the launch in _attention.forward

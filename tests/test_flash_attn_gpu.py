@@ -155,3 +155,91 @@ def test_attention_theta_matches_table_path_and_oracle(dtype, shape):
         check16(_label() + " O", got[0], refs[0], TOL_FWD_16, dtype, strict=True)
         for name, a, b in zip(("dQ", "dK", "dV"), got[1:], refs[1:]):
             check16(_label() + " " + name, a, b, TOL_BWD_16, dtype)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# strided tensors: the kernels take every tensor's own {batch, head, row} strides
+# ---------------------------------------------------------------------------------------------------------------------
+def _as_bnhd_view(t):
+    """The same values held in a [B, N, H, D] buffer and viewed as [B, H, N, D] (what a projection followed by
+    .view(B, N, H, D).transpose(1, 2) gives a model)."""
+    return t.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+
+
+def _padded_rows_view(t, pad):
+    """The same values with `pad` unused elements behind every row (row stride D + pad)."""
+    B, H, N, D = t.shape
+    buf = torch.zeros((B, H, N, D + pad), dtype=t.dtype, device=t.device)
+    buf[..., :D] = t
+    return buf[..., :D]
+
+
+@pytest.mark.parametrize("dtype,shape,causal", [(torch.bfloat16, (2, 4, 512, 128), True), (torch.float16, (1, 3, 256, 64), False),
+                                                (torch.float32, (2, 2, 100, 64), True), (torch.bfloat16, (1, 2, 200, 32), True)])
+@pytest.mark.parametrize("layout", ["bnhd", "padded8", "padded2"])
+def test_fused_rope_strided_views_need_no_copies(dtype, shape, causal, layout):
+    # Transposed and row-padded views through the drop-in entry point: same results as contiguous tensors, the outputs
+    # come back in the inputs' layout (o = empty_like(q), fused_rope_attn.py:662), and the library launches exactly the
+    # kernels it launches for contiguous tensors -- no copy kernels of its own, and torch makes none either.
+    # "padded2" (row stride D + 2) is not a multiple of 16 bytes for 16-bit types: those run on the CUDA-core kernels.
+    B, H, N, D = shape
+    q, k, v, do = (draw(shape, 100 + i, dtype).cuda() for i in range(4))
+    cos, sin = (t.cuda() for t in oracle.precompute_freqs_cis(D, N, 10000.0))
+    view = {"bnhd": _as_bnhd_view, "padded8": lambda t: _padded_rows_view(t, 8), "padded2": lambda t: _padded_rows_view(t, 2)}[layout]
+
+    def run(make):
+        qq, kk, vv = (make(t).detach().requires_grad_(True) for t in (q, k, v))
+        n0 = ext.lib().corope_launch_count()
+        o = pkg.fused_rope_attention(qq, kk, vv, causal, D ** -0.5, cos, sin)
+        o.backward(make(do))
+        ext.check_status()
+        return (o, qq.grad, kk.grad, vv.grad), (qq, kk, vv), ext.lib().corope_launch_count() - n0
+
+    ref, _, launches_contig = run(lambda t: t.clone())
+    fam_contig = (ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD), ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD))
+    got, (qq, kk, vv), launches = run(view)
+    fam = (ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD), ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD))
+    assert not qq.is_contiguous()
+    # outputs and gradients are laid out as torch.empty_like lays them out: the input's own strides for a dense view (the
+    # transposed buffer), contiguous for a view with gaps (the padded rows)
+    want = torch.empty_like(qq).stride()
+    assert got[0].stride() == want and got[1].stride() == want and got[2].stride() == torch.empty_like(kk).stride()
+    if layout == "bnhd":
+        assert want == qq.stride() and not got[0].is_contiguous()
+    aligned = dtype == torch.float32 or layout != "padded2"
+    if aligned:
+        assert fam == fam_contig and launches == launches_contig
+        assert torch.equal(got[0], ref[0]) and torch.equal(got[2], ref[2]) and torch.equal(got[3], ref[3])   # fixed summation order
+        assert maxdiff(got[1], ref[1]) < 1e-2
+    else:
+        assert fam == (0, 0)
+        for a, b, tol in zip(got, ref, (TOL_FWD_16, TOL_BWD_16, TOL_BWD_16, TOL_BWD_16)):
+            assert maxdiff(a, b) <= 2 * tol
+
+
+def test_flash_attention_strided_gqa_views():
+    B, Hq, Hkv, N, D = 2, 8, 2, 384, 128
+    q, k, v, do = (t.cuda() for t in _inputs(B, Hq, Hkv, N, D, torch.bfloat16, 110))
+    qq, kk, vv = (_as_bnhd_view(t).detach().requires_grad_(True) for t in (q, k, v))
+    o = flash_attention(qq, kk, vv, True, D ** -0.5)
+    o.backward(_as_bnhd_view(do))
+    ext.check_status()
+    assert ext.lib().corope_last_kernel_family(ext.OP_ROPE_FWD) == 1 and ext.lib().corope_last_kernel_family(ext.OP_ROPE_BWD) == 1
+    assert o.stride() == qq.stride() and kk.grad.stride() == kk.stride()
+    qc, kc, vc, dc = (t.float().cpu() for t in (q, k, v, do))
+    refs = (oracle.attn_gqa_fwd(qc, kc, vc, True, D ** -0.5),) + tuple(oracle.attn_gqa_bwd(qc, kc, vc, dc, True, D ** -0.5))
+    check16(_label() + " O", o.detach().float().cpu(), refs[0], TOL_FWD_16, torch.bfloat16, strict=True)
+    for name, got, ref in zip(("dQ", "dK", "dV"), (qq.grad, kk.grad, vv.grad), refs[1:]):
+        check16(_label() + " " + name, got.float().cpu(), ref, TOL_BWD_16, torch.bfloat16)
+
+
+def test_strided_entry_point_rejects_bad_strides():
+    lib = ext.lib()
+    t = torch.zeros(1, 1, 128, 128, device="cuda", dtype=torch.bfloat16)
+    st = ext.strides_of(q=t, k=t, v=t, o=t)
+    st.q[2] = 64   # row stride smaller than D
+    f = torch.zeros(128, 64, device="cuda")
+    ws, nbytes = ext.workspace(ext.OP_ROPE_FWD, 1, 1, 1, 128, 128, torch.bfloat16, t.device)
+    rc = lib.corope_rope_attn_fwd_strided(t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), f.data_ptr(), 64, t.data_ptr(), f.data_ptr(),
+                                          1, 1, 128, 128, 1, 1, 0.1, ws.data_ptr(), nbytes, None, None, st)
+    assert rc == -11 and b"stride" in lib.corope_status_string(rc)
