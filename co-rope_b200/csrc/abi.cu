@@ -92,6 +92,7 @@ int check_common(int B, int H, int N, int D, int dtype) {
     if (!head_dim_ok(D)) return COROPE_ERR_BAD_HEAD_DIM;
     if (dtype != COROPE_DTYPE_F32 && dtype != COROPE_DTYPE_BF16 && dtype != COROPE_DTYPE_F16) return COROPE_ERR_BAD_DTYPE;
     if ((size_t)B * H > 65535u * 32u) return COROPE_ERR_TOO_LARGE;
+    if ((size_t)B * H * N >= (1ull << 31)) return COROPE_ERR_TOO_LARGE;   // row indices are 32-bit in the kernels
     return COROPE_OK;
 }
 

@@ -105,7 +105,9 @@ static_assert(kSmemBytes <= 232448, "shared memory budget");
 
 constexpr uint32_t TS0 = 0, TD0 = 128, TDV = 256, TDK = 384;
 
-template <typename T>
+// kPlain: one query head per K / V head and every tensor's rows evenly spaced (all contiguous MHA calls): the group and
+// layout arithmetic folds away at compile time (it measured 1 - 2 % of the kernel when left to run-time flags).
+template <typename T, bool kPlain>
 __global__ void __launch_bounds__(kThreads, 1)
 rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                       const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -126,7 +128,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int N = p.N;
-    const int G = p.H / p.Hkv;            // query heads per K / V head (1 for the fused-RoPE ops)
+    const int G = kPlain ? 1 : p.H / p.Hkv;   // query heads per K / V head (1 for the fused-RoPE ops)
+    const bool flat_q = kPlain || p.flat_q, flat_do = kPlain || p.flat_do, flat_k = kPlain || p.flat_k, flat_v = kPlain || p.flat_v;
     const int BH = p.B * p.Hkv;           // units are taken per K / V head; a unit sweeps the query tiles of all G heads of its group
     const int n_kb = N / kBK;
     const int n_units = BH * n_kb;
@@ -134,8 +137,10 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
     // per unit (jb, bh): first query row visited q_first = causal ? jb * kBK : 0 (causal: the block's own diagonal),
     // spg = (N - q_first) / kBQ steps per query head (even) and n_steps = G * spg, so the two-buffer indices of a unit's
     // first step are always 0.  Step s works on query head bh * G + s / spg, rows q_first + (s % spg) * kBQ .. + kBQ - 1.
-    auto step_q0 = [&](int q_first, int spg, int s) { return q_first + (s % spg) * kBQ; };
-    auto step_row = [&](int bh, int q_first, int spg, int s) { return (bh * G + s / spg) * N + q_first + (s % spg) * kBQ; };
+    // (no division when every K / V head has a single query head: then s < spg)
+    auto step_head = [&](int spg, int s) { return G == 1 ? 0 : s / spg; };
+    auto step_q0 = [&](int q_first, int spg, int s) { return q_first + (G == 1 ? s : s % spg) * kBQ; };
+    auto step_row = [&](int bh, int q_first, int spg, int s) { return (bh * G + step_head(spg, s)) * N + step_q0(q_first, spg, s); };
 
     if (reinterpret_cast<uintptr_t>(sm) - reinterpret_cast<uintptr_t>(smem_raw) > kSmemSlack) {   // base less aligned than assumed
         if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_WAIT_EXPIRED | 0xfff);
@@ -206,13 +211,27 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     const int gs = g + s, st = gs % kStages;
                     if (gs >= kStages && !mbar_wait(&bars[QDO_EMPTY + st], ((gs / kStages) - 1) & 1, p.status, QDO_EMPTY, abort_flag)) return false;
                     const int qr = step_row(un.bh, q_first, spg, s);   // flat row of the contiguous side inputs (LSE, delta)
-                    const int qhead = un.bh * G + s / spg, q0 = step_q0(q_first, spg, s);
-                    const int qb = qhead / p.H, qh = qhead % p.H;      // coordinates of the 4-D maps
                     mbar_arrive_expect_tx(&bars[QDO_FULL + st], 2 * kQBytes + 2 * kBQ * (uint32_t)sizeof(float));
-                    tma_load_4d(sQ + st * kQBytes, &mapQ, 0, q0, qh, qb, &bars[QDO_FULL + st]);
-                    tma_load_4d(sQ + st * kQBytes + kQBox, &mapQ, 64, q0, qh, qb, &bars[QDO_FULL + st]);
-                    tma_load_4d(sDO + st * kQBytes, &mapDO, 0, q0, qh, qb, &bars[QDO_FULL + st]);
-                    tma_load_4d(sDO + st * kQBytes + kQBox, &mapDO, 64, q0, qh, qb, &bars[QDO_FULL + st]);
+                    if (flat_q) {
+                        tma_load_2d(sQ + st * kQBytes, &mapQ, 0, qr, &bars[QDO_FULL + st]);
+                        tma_load_2d(sQ + st * kQBytes + kQBox, &mapQ, 64, qr, &bars[QDO_FULL + st]);
+                    }
+                    if (flat_do) {
+                        tma_load_2d(sDO + st * kQBytes, &mapDO, 0, qr, &bars[QDO_FULL + st]);
+                        tma_load_2d(sDO + st * kQBytes + kQBox, &mapDO, 64, qr, &bars[QDO_FULL + st]);
+                    }
+                    if (!flat_q || !flat_do) {   // 4-D maps: (row, head, batch) coordinates
+                        const int qhead = un.bh * G + step_head(spg, s), q0 = step_q0(q_first, spg, s);
+                        const int qb = qhead / p.H, qh = qhead % p.H;
+                        if (!flat_q) {
+                            tma_load_4d(sQ + st * kQBytes, &mapQ, 0, q0, qh, qb, &bars[QDO_FULL + st]);
+                            tma_load_4d(sQ + st * kQBytes + kQBox, &mapQ, 64, q0, qh, qb, &bars[QDO_FULL + st]);
+                        }
+                        if (!flat_do) {
+                            tma_load_4d(sDO + st * kQBytes, &mapDO, 0, q0, qh, qb, &bars[QDO_FULL + st]);
+                            tma_load_4d(sDO + st * kQBytes + kQBox, &mapDO, 64, q0, qh, qb, &bars[QDO_FULL + st]);
+                        }
+                    }
                     bulk_load_1d(sLD + st * 2 * kBQ, p.lse2 + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
                     bulk_load_1d(sLD + st * 2 * kBQ + kBQ, p.delta + qr, kBQ * sizeof(float), &bars[QDO_FULL + st]);
                     return true;
@@ -224,11 +243,11 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (n > 0 && !(ok = mbar_wait(&bars[ACC_FULL], (n - 1) & 1, p.status, ACC_FULL, abort_flag))) break;
                 const int kr = un.jb * kBK, kb = un.bh / p.Hkv, kh = un.bh % p.Hkv;
                 mbar_arrive_expect_tx(&bars[K_FULL], kKVBytes);
-                tma_load_4d(sK, &mapK, 0, kr, kh, kb, &bars[K_FULL]);
-                tma_load_4d(sK + kKVBox, &mapK, 64, kr, kh, kb, &bars[K_FULL]);
+                tma_load_rows(sK, &mapK, flat_k, 0, kr, kh, kb, p.Hkv, N, &bars[K_FULL]);
+                tma_load_rows(sK + kKVBox, &mapK, flat_k, 64, kr, kh, kb, p.Hkv, N, &bars[K_FULL]);
                 mbar_arrive_expect_tx(&bars[V_FULL], kKVBytes);
-                tma_load_4d(sV, &mapV, 0, kr, kh, kb, &bars[V_FULL]);
-                tma_load_4d(sV + kKVBox, &mapV, 64, kr, kh, kb, &bars[V_FULL]);
+                tma_load_rows(sV, &mapV, flat_v, 0, kr, kh, kb, p.Hkv, N, &bars[V_FULL]);
+                tma_load_rows(sV + kKVBox, &mapV, flat_v, 64, kr, kh, kb, p.Hkv, N, &bars[V_FULL]);
                 for (int s = 2; ok && s < n_steps; ++s) ok = load_step(s);
                 g += n_steps;
             }
@@ -443,7 +462,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         if (ok) {
             tc_fence_after();
             if (wg == 0) {
-                T* dst = reinterpret_cast<T*>(p.dv) + row_offset(p.sdv, p.Hkv, un.bh, key);
+                T* dst = reinterpret_cast<T*>(p.dv) + (kPlain ? ((int64_t)un.bh * N + key) * p.sdv.n : row_offset(p.sdv, p.Hkv, un.bh, key));
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t r[32];
@@ -457,7 +476,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     for (int i = 0; i < 4; ++i) d4[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
                 }
             } else {
-                T* dst = reinterpret_cast<T*>(p.dk) + row_offset(p.sdk, p.Hkv, un.bh, key);
+                T* dst = reinterpret_cast<T*>(p.dk) + (kPlain ? ((int64_t)un.bh * N + key) * p.sdk.n : row_offset(p.sdk, p.Hkv, un.bh, key));
                 const uint32_t* tab = p.packed_tab + (size_t)key * (kD / 2);
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -547,12 +566,12 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
 // 64 columns when a D = 64 problem runs zero-padded; the packed table then holds the identity in columns 32..63), 8-byte stores
 template <typename T>
 __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __restrict__ dq, const uint32_t* __restrict__ packed,
-                                            size_t rows, int N, float scale, Strides sdq, int H) {
+                                            size_t rows, int N, float scale, Strides sdq, int H, int flat) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 16) return;
     const size_t row = idx >> 4;
     const int d = (int)(idx & 15) * 4;
-    const int pos = (int)(row % (size_t)N);
+    const int pos = (int)((unsigned)row % (unsigned)N);
     const float4 a1 = *reinterpret_cast<const float4*>(acc + row * kD + d);
     const float4 a2 = *reinterpret_cast<const float4*>(acc + row * kD + d + 64);
     const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(packed + (size_t)pos * (kD / 2) + d));
@@ -563,7 +582,7 @@ __global__ void rope_bwd_dq_finalize_kernel(const float* __restrict__ acc, T* __
     o1.y = pack2<T>((x1[2] * cs[2].x + x2[2] * cs[2].y) * scale, (x1[3] * cs[3].x + x2[3] * cs[3].y) * scale);
     o2.x = pack2<T>((x2[0] * cs[0].x - x1[0] * cs[0].y) * scale, (x2[1] * cs[1].x - x1[1] * cs[1].y) * scale);
     o2.y = pack2<T>((x2[2] * cs[2].x - x1[2] * cs[2].y) * scale, (x2[3] * cs[3].x - x1[3] * cs[3].y) * scale);
-    T* out = dq + row_offset(sdq, H, (int)(row / (size_t)N), pos);
+    T* out = dq + (flat ? (int64_t)row * sdq.n : row_offset(sdq, H, (int)((unsigned)row / (unsigned)N), pos));
     *reinterpret_cast<uint2*>(out + d) = o1;
     *reinterpret_cast<uint2*>(out + d + 64) = o2;
 }
@@ -572,17 +591,22 @@ template <typename T>
 int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     CUtensorMap mq, mk, mv, mdo, mdq;
     const uint64_t rows = (uint64_t)p.B * p.H * p.N;
-    // 4-D maps (head dim, row, head, batch) over the caller's tensors with their own strides; the pre-rotated Q copy is contiguous
-    if (int e = p.q_rot ? encode_tensor_map_4d_sw128(&mq, p.q_rot, p.B, p.H, p.N, kD, contiguous_strides(p.H, p.N, kD), kBQ, 64, COROPE_DTYPE_F16)
-                        : encode_tensor_map_4d_sw128(&mq, p.q, p.B, p.H, p.N, kD, p.sq, kBQ, 64, dtype))
+    // maps over the caller's tensors with their own strides (2-D when the rows collapse, else 4-D: head dim, row, head, batch);
+    // the pre-rotated Q copy is contiguous
+    RopeParams pp = p;
+    bool fq, fdo, fk, fv;
+    if (int e = p.q_rot ? encode_rows_map(&mq, &fq, p.q_rot, p.B, p.H, p.N, kD, contiguous_strides(p.H, p.N, kD), kBQ, 64, COROPE_DTYPE_F16)
+                        : encode_rows_map(&mq, &fq, p.q, p.B, p.H, p.N, kD, p.sq, kBQ, 64, dtype))
         return e;
-    if (int e = encode_tensor_map_4d_sw128(&mdo, p.d_o, p.B, p.H, p.N, kD, p.sdo, kBQ, 64, dtype)) return e;
-    if (int e = encode_tensor_map_4d_sw128(&mk, p.k, p.B, p.Hkv, p.N, kD, p.sk, kBK, 64, dtype)) return e;
-    if (int e = encode_tensor_map_4d_sw128(&mv, p.v, p.B, p.Hkv, p.N, kD, p.sv, kBK, 64, dtype)) return e;
+    if (int e = encode_rows_map(&mdo, &fdo, p.d_o, p.B, p.H, p.N, kD, p.sdo, kBQ, 64, dtype)) return e;
+    if (int e = encode_rows_map(&mk, &fk, p.k, p.B, p.Hkv, p.N, kD, p.sk, kBK, 64, dtype)) return e;
+    if (int e = encode_rows_map(&mv, &fv, p.v, p.B, p.Hkv, p.N, kD, p.sv, kBK, 64, dtype)) return e;
+    pp.flat_q = fq; pp.flat_do = fdo; pp.flat_k = fk; pp.flat_v = fv;
     if (int e = encode_tensor_map_2d_f32(&mdq, p.dq_acc, rows, kD, kBQ, kD)) return e;
     cudaError_t e = p.dq_acc_zeroed ? cudaSuccess : cudaMemsetAsync(p.dq_acc, 0, rows * kD * sizeof(float), s);
     if (e != cudaSuccess) return (int)e;
-    auto kern = rope_bwd_sm100_kernel<T>;
+    const bool plain = p.H == p.Hkv && fq && fdo && fk && fv && rows_collapse(p.sdk, p.Hkv, p.N) && rows_collapse(p.sdv, p.Hkv, p.N);
+    auto kern = plain ? rope_bwd_sm100_kernel<T, true> : rope_bwd_sm100_kernel<T, false>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return (int)e;
     int dev = 0, sms = 0;
@@ -590,12 +614,12 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
     if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
     const unsigned units = (unsigned)((p.N / kBK) * p.B * p.Hkv);
     const unsigned grid = units < (unsigned)sms ? units : (unsigned)sms;   // persistent: one CTA per SM
-    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, mdq, p); count_launch();
+    kern<<<grid, kThreads, kSmemBytes, s>>>(mq, mk, mv, mdo, mdq, pp); count_launch();
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     const size_t n = rows * 16;
     rope_bwd_dq_finalize_kernel<T><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(p.dq_acc, reinterpret_cast<T*>(p.dq), p.packed_tab, rows, p.N,
-                                                                              p.sm_scale, p.sdq, p.H); count_launch();
+                                                                              p.sm_scale, p.sdq, p.H, rows_collapse(p.sdq, p.H, p.N) ? 1 : 0); count_launch();
     return (int)cudaGetLastError();
 }
 

@@ -16,9 +16,24 @@
 namespace corope {
 namespace {
 
-// element offset of flat row index `row` (= (b * H + h) * N + n) in a strided [B, H, N, D] tensor
-__device__ __forceinline__ int64_t flat_row_offset(const Strides& st, int H, int N, size_t row) {
-    return row_offset(st, H, (int)(row / (size_t)N), (int)(row % (size_t)N));
+// Addressing of flat row index `row` (= (b * H + h) * N + n) of a strided [B, H, N, D] tensor in the elementwise kernels.  The
+// host decides once whether the rows are evenly spaced (every contiguous tensor): then the offset is one multiply; the general
+// form costs two integer divisions per thread, which these memory-bound kernels (a few 16-byte accesses per thread) would feel.
+struct RowAddr {
+    Strides st;
+    int H, N;
+    int flat;
+};
+inline RowAddr row_addr(const Strides& st, int H, int N) {
+    RowAddr a;
+    a.st = st; a.H = H; a.N = N;
+    a.flat = rows_collapse(st, H, N) ? 1 : 0;
+    return a;
+}
+__device__ __forceinline__ int64_t flat_row_offset(const RowAddr& a, size_t row) {
+    if (a.flat) return (int64_t)row * a.st.n;
+    const unsigned r = (unsigned)row, bh = r / (unsigned)a.N;   // row counts stay below 2^31 (checked at the entry points)
+    return row_offset(a.st, a.H, (int)bh, (int)(r - bh * (unsigned)a.N));
 }
 
 constexpr int kRows = 32;     // rows per CTA
@@ -200,14 +215,14 @@ __global__ void __launch_bounds__(kThreads) rope_fwd_general_kernel(RopeParams p
 // delta = rowsum(O * dO)   (fused_rope_attn.py:324-337)
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D, Strides so,
-                                  Strides sdo, int H, int N) {
+__global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D, RowAddr ao,
+                                  RowAddr ado) {
     size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
     float s = 0.f;
-    const T* orow = o + flat_row_offset(so, H, N, row);
-    const T* drow = d_o + flat_row_offset(sdo, H, N, row);
+    const T* orow = o + flat_row_offset(ao, row);
+    const T* drow = d_o + flat_row_offset(ado, row);
     for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(orow[d]) * Elem<T>::to_f32(drow[d]);
     s = warp_sum(s);
     if (lane == 0) delta[row] = s;
@@ -215,15 +230,15 @@ __global__ void rope_delta_kernel(const T* __restrict__ o, const T* __restrict__
 
 // Same for 16-bit elements and D = 128: 16 threads per row, 16 bytes of O and of dO per thread.
 template <typename T>
-__global__ void rope_delta_d128_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, Strides so,
-                                       Strides sdo, int H, int N) {
+__global__ void rope_delta_d128_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, RowAddr ao,
+                                       RowAddr ado) {
     const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t row = t >> 4;
     const int part = (int)(t & 15);
     float s = 0.f;
     if (row < rows) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(so, H, N, row)) + part);
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(sdo, H, N, row)) + part);
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(ao, row)) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(ado, row)) + part);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -407,8 +422,7 @@ __global__ void synth_tables_kernel(const float* __restrict__ inv_freq, float* _
 // D = 128 kernels: first half of the row (32 columns) to columns 0..31, second half to columns 64..95; "plain" layout
 // puts the 64 columns first.  Everything else is zero, so dot products and rotations are unchanged.
 template <typename T>
-__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout, Strides st, int H,
-                                                      int N) {
+__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout, RowAddr ax) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16 output chunks
     if (idx >= rows * 16) return;
     const size_t r = idx >> 4;
@@ -421,18 +435,17 @@ __global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T
         src = c;
     }
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + flat_row_offset(st, H, N, r) + src * 8);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + flat_row_offset(ax, r) + src * 8);
     *reinterpret_cast<uint4*>(out + r * 128 + c * 8) = v;
 }
 template <typename T>
-__global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout, Strides st,
-                                                        int H, int N) {
+__global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout, RowAddr ax) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 8 output chunks
     if (idx >= rows * 8) return;
     const size_t r = idx >> 3;
     const int c = (int)(idx & 7);
     const int src = rope_layout ? (c < 4 ? c : c + 4) : c;
-    *reinterpret_cast<uint4*>(out + flat_row_offset(st, H, N, r) + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
+    *reinterpret_cast<uint4*>(out + flat_row_offset(ax, r) + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
 }
 
 // Rotation as a pass of its own, for the tensor-core kernels at D = 128: out[r, :] = rot(x[r, :]) * scale as fp16, with the
@@ -442,14 +455,13 @@ __global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp
 // its diagonal).  One thread = 8 pairs of one row: two 16-byte loads, 32 bytes of table, two 16-byte stores.
 template <typename T>
 __global__ void __launch_bounds__(256) rope_prerotate_d128_kernel(const T* __restrict__ x, __half* __restrict__ out,
-                                                                   const uint32_t* __restrict__ tab, size_t rows, int N, float scale, Strides st,
-                                                                   int H) {
+                                                                   const uint32_t* __restrict__ tab, size_t rows, int N, float scale, RowAddr ax) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * 8) return;
     const size_t row = idx >> 3;
     const int c = (int)(idx & 7) * 8;
     const int n = (int)(row % (size_t)N);
-    const uint4* src = reinterpret_cast<const uint4*>(x + flat_row_offset(st, H, N, row) + c);
+    const uint4* src = reinterpret_cast<const uint4*>(x + flat_row_offset(ax, row) + c);
     uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
     const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
     const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
@@ -467,19 +479,19 @@ template <typename T>
 __global__ void __launch_bounds__(256) rope_bwd_prepass_d128_kernel(const T* __restrict__ q, const T* __restrict__ o, const T* __restrict__ d_o,
                                                                      const uint32_t* __restrict__ tab, __half* __restrict__ q_rot,
                                                                      float* __restrict__ delta, float* __restrict__ dq_acc, size_t rows, int N,
-                                                                     float scale, Strides sq, Strides so, Strides sdo, int H) {
+                                                                     float scale, RowAddr aq, RowAddr ao, RowAddr ado) {
     const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t row = t >> 4;
     const int part = (int)(t & 15);
     const bool live = row < rows;
     float s = 0.f;
     if (live) {
-        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(so, H, N, row)) + part);
-        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(sdo, H, N, row)) + part);
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(o + flat_row_offset(ao, row)) + part);
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(d_o + flat_row_offset(ado, row)) + part);
         if (part < 8) {
             const int c = part * 8;
             const int n = (int)(row % (size_t)N);
-            const uint4* src = reinterpret_cast<const uint4*>(q + flat_row_offset(sq, H, N, row) + c);
+            const uint4* src = reinterpret_cast<const uint4*>(q + flat_row_offset(aq, row) + c);
             uint4 x1 = __ldg(src), x2 = __ldg(src + 8);
             const uint4* tp = reinterpret_cast<const uint4*>(tab + (size_t)n * 64 + c);
             const uint4 t0 = __ldg(tp), t1 = __ldg(tp + 1);
@@ -577,9 +589,9 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     if (p.D == 128 && dtype != COROPE_DTYPE_F32 && aligned(p.o, p.so) && aligned(p.d_o, p.sdo)) {
         const unsigned blocks = (unsigned)((rows * 16 + 255) / 256);
         if (dtype == COROPE_DTYPE_BF16)
-            rope_delta_d128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.so, p.sdo, p.H, p.N);
+            rope_delta_d128_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N));
         else
-            rope_delta_d128_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.so, p.sdo, p.H, p.N);
+            rope_delta_d128_kernel<__half><<<blocks, 256, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N));
         count_launch();
         return (int)cudaGetLastError();
     }
@@ -587,14 +599,14 @@ int launch_rope_delta(const RopeParams& p, int dtype, cudaStream_t s) {
     unsigned blocks = (unsigned)((rows + warps - 1) / warps);
     switch (dtype) {
         case COROPE_DTYPE_F32:
-            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
+            rope_delta_kernel<float><<<blocks, warps * 32, 0, s>>>((const float*)p.o, (const float*)p.d_o, p.delta, rows, p.D, row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N)); count_launch();
             break;
         case COROPE_DTYPE_BF16:
             rope_delta_kernel<__nv_bfloat16>
-                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
+                <<<blocks, warps * 32, 0, s>>>((const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o, p.delta, rows, p.D, row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N)); count_launch();
             break;
         case COROPE_DTYPE_F16:
-            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D, p.so, p.sdo, p.H, p.N); count_launch();
+            rope_delta_kernel<__half><<<blocks, warps * 32, 0, s>>>((const __half*)p.o, (const __half*)p.d_o, p.delta, rows, p.D, row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N)); count_launch();
             break;
         default: return COROPE_ERR_BAD_DTYPE;
     }
@@ -606,9 +618,9 @@ int launch_rope_prerotate(const void* x, const Strides& st, void* out_f16, const
     const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale, st, H);
+        rope_prerotate_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__half*)out_f16, packed, rows, N, scale, row_addr(st, H, N));
     else
-        rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale, st, H);
+        rope_prerotate_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out_f16, packed, rows, N, scale, row_addr(st, H, N));
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -619,10 +631,10 @@ int launch_rope_bwd_prepass(const RopeParams& p, int dtype, cudaStream_t s) {
     const float scale = p.sm_scale * kLog2e;
     if (dtype == COROPE_DTYPE_BF16)
         rope_bwd_prepass_d128_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)p.q, (const __nv_bfloat16*)p.o, (const __nv_bfloat16*)p.d_o,
-                                                                        p.packed_tab, (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, p.sq, p.so, p.sdo, p.H);
+                                                                        p.packed_tab, (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, row_addr(p.sq, p.H, p.N), row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N));
     else
         rope_bwd_prepass_d128_kernel<__half><<<grid, 256, 0, s>>>((const __half*)p.q, (const __half*)p.o, (const __half*)p.d_o, p.packed_tab,
-                                                                 (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, p.sq, p.so, p.sdo, p.H);
+                                                                 (__half*)const_cast<void*>(p.q_rot), p.delta, p.dq_acc, rows, p.N, scale, row_addr(p.sq, p.H, p.N), row_addr(p.so, p.H, p.N), row_addr(p.sdo, p.H, p.N));
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -645,9 +657,9 @@ int launch_pad_d64(const void* x, const Strides& st, void* out, int B, int H, in
     const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 16 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout, st, H, N);
+        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout, row_addr(st, H, N));
     else
-        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout, st, H, N);
+        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout, row_addr(st, H, N));
     count_launch();
     return (int)cudaGetLastError();
 }
@@ -656,9 +668,9 @@ int launch_unpad_d64(const void* xp, void* out, const Strides& st, int B, int H,
     const size_t rows = (size_t)B * H * N;
     const unsigned grid = (unsigned)((rows * 8 + 255) / 256);
     if (dtype == COROPE_DTYPE_BF16)
-        unpad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)xp, (__nv_bfloat16*)out, rows, rope_layout, st, H, N);
+        unpad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)xp, (__nv_bfloat16*)out, rows, rope_layout, row_addr(st, H, N));
     else
-        unpad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)xp, (__half*)out, rows, rope_layout, st, H, N);
+        unpad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)xp, (__half*)out, rows, rope_layout, row_addr(st, H, N));
     count_launch();
     return (int)cudaGetLastError();
 }
