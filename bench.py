@@ -46,11 +46,12 @@ DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 THETA = 10000.0
 REF_COPY = os.path.join(ROOT, "baseline", "_ref")
 
-# DRAM bytes per launch of the two tensor-core kernels, from one ncu capture each (dram__bytes_read.sum +
-# dram__bytes_write.sum) at B=2 H=64 N=1024 D=128 bf16 -- 112.2 MB forward, 288.4 MB backward -- expressed per byte of
-# one [B,H,N,D] bf16 tensor (33.55 MB there).  Traffic of these kernels is proportional to the tensor bytes as long as a
-# head's K/V (and, backward, its fp32 dQ rows) fit in L2, which holds for every workload here.
-NCU_DRAM_PER_TENSOR_BYTE = {"fused_rope_fwd": 112.2 / 33.55, "fused_rope_bwd": 288.4 / 33.55}
+# DRAM bytes per launch of the two tensor-core kernels, from one ncu capture of both (dram__bytes_read.sum +
+# dram__bytes_write.sum) at the Llama-7B-4K shape itself, B=2 H=32 N=4096 D=128 bf16 -- 251.8 MB forward, 628.6 MB backward
+# (profiles/rope_fwd_bwd_sm100_llama7b_4k.md) -- expressed per byte of one [B,H,N,D] bf16 tensor (67.11 MB there).  Traffic of
+# these kernels is proportional to the tensor bytes as long as a head's K/V (and, backward, its fp32 dQ rows) fit in L2, which
+# holds for every workload here; for the default workload on one GPU the factor is exact.
+NCU_DRAM_PER_TENSOR_BYTE = {"fused_rope_fwd": 251.8 / 67.11, "fused_rope_bwd": 628.6 / 67.11}
 
 
 def flops_fwd(B, H, N, D):
@@ -417,13 +418,14 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="N > 1: strong = the workload's units are divided among the ranks; weak = every rank runs the whole workload")
     ap.add_argument("--ref-units", type=int, default=4, help="(batch, head) units per step of the CPU reference arm")
+    ap.add_argument("--autograd", action="store_true", help="time the autograd entry points instead of the direct forward / backward helpers")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-triton", action="store_true", help="skip the child process that times the reference's Triton kernels")
     ap.add_argument("--no-sustained", action="store_true")
     ap.add_argument("--no-variants", action="store_true", help="skip timing the variant that rotates in the kernels (no rotated copies in HBM)")
     ap.add_argument("--sustained-seconds", type=float, default=2.5)
-    ap.add_argument("--e2e-chunks", type=int, default=16, help="chunks of (batch, KV head) units in the host-to-host pipeline of the e2e figure")
+    ap.add_argument("--e2e-chunks", type=int, default=0, help="chunks of (batch, KV head) units in the host-to-host pipeline of the e2e figure (0: the pipeline's own choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -481,22 +483,41 @@ def main():
         cos, sin = oracle.precompute_freqs_cis(D, N, THETA)
         cos, sin = cos[:, : D // 2].contiguous().to(dev), sin[:, : D // 2].contiguous().to(dev)
 
-    def fwd(qq, kk, vv):
-        if kind == "rope":
-            return pkg.fused_rope_attention(qq, kk, vv, True, sm_scale, cos, sin)
-        return pkg.corope_gqa_attention(qq, kk, vv, True, sm_scale, THETA)
+    rope_mod = importlib.import_module("co-rope_b200.fused_rope_attn")
+    gqa_mod = importlib.import_module("co-rope_b200.flash_attn_co_rope_gqa_triton")
 
     def step(qq, kk, vv, dd, evs=None):
-        qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
+        """One forward + backward.  Default: the package's forward / backward helpers (the entry points' checks and the C-ABI
+        calls, without torch.autograd -- what the host pipeline and callers with their own backward pass use); their host cost
+        is 0.1 ms per step, against 0.3 ms through autograd, which matters once a rank's share of the problem takes less than
+        that on the GPU.  --autograd times the autograd entry points instead."""
+        if args.autograd:
+            qq.requires_grad_(True), kk.requires_grad_(True), vv.requires_grad_(True)
+            if evs:
+                evs[0].record()
+            o = (pkg.fused_rope_attention(qq, kk, vv, True, sm_scale, cos, sin) if kind == "rope"
+                 else pkg.corope_gqa_attention(qq, kk, vv, True, sm_scale, THETA))
+            if evs:
+                evs[1].record()
+            g = torch.autograd.grad(o, (qq, kk, vv), dd)
+            if evs:
+                evs[2].record()
+            return o, g
         if evs:
             evs[0].record()
-        o = fwd(qq, kk, vv)
+        if kind == "rope":
+            saved = rope_mod._forward(qq, kk, vv, True, sm_scale, cos, sin)
+        else:
+            saved = gqa_mod._forward(qq, kk, vv, True, sm_scale, THETA)
         if evs:
             evs[1].record()
-        g = torch.autograd.grad(o, (qq, kk, vv), dd)
+        if kind == "rope":
+            g = rope_mod._backward(*saved, dd, True, sm_scale)
+        else:
+            g = gqa_mod._backward(*saved, dd, sm_scale, THETA)
         if evs:
             evs[2].record()
-        return o, g
+        return saved[3], g
 
     def sync_all():
         torch.cuda.synchronize()
@@ -661,8 +682,9 @@ def main():
     e2e = None
     if not args.no_e2e:
         ho, hdq, hdk, hdv = (torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv))   # empty_like alone is pageable
+        nb_in = int(sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo)))
         v4 = lambda t, g: t.view(1, n_loc * g, N, D)
-        chunks = max(1, min(args.e2e_chunks, n_loc))
+        chunks = max(1, min(args.e2e_chunks, n_loc)) if args.e2e_chunks > 0 else pkg.host_pipeline.auto_chunks(2 * nb_in, n_loc)
 
         def e2e_step():   # the package's call for host tensors: chunks of (batch, KV head) units through copy-in / kernel / copy-out streams
             kw = dict(freqs_cos=cos, freqs_sin=sin) if kind == "rope" else dict(theta=THETA)
@@ -721,7 +743,7 @@ def main():
             "frac_of_nominal_2250": ach / 2250.0,
             "traffic": (NCU_DRAM_PER_TENSOR_BYTE["fused_rope_bwd" if dom_is_bwd else "fused_rope_fwd"] * dq_.numel() * dq_.element_size()
                         if fam == 1 else None),
-            "traffic_unit": "bytes per launch (ncu capture at N=1024, scaled by tensor bytes)",
+            "traffic_unit": "bytes per launch (ncu capture of one launch at the Llama-7B-4K shape, scaled by tensor bytes for other sizes)",
             "algorithmic_flops": F_launch,
             "fwd": {"ms": fwd_ms, "tflops": F_rank / (fwd_ms * 1e-3) / 1e12, "frac": F_rank / (fwd_ms * 1e-3) / 1e12 / peaks["tflops"]},
             "bwd": {"ms": bwd_ms, "tflops": 2.5 * F_rank / (bwd_ms * 1e-3) / 1e12, "frac": 2.5 * F_rank / (bwd_ms * 1e-3) / 1e12 / peaks["tflops"]},
@@ -768,6 +790,7 @@ def main():
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
         "config": {"workload": args.workload, "B": B, "Hq": Hq, "Hkv": Hkv, "N": N, "D": D, "causal": True, "sm_scale": sm_scale,
                    "theta": THETA, "units_total": units_total, "units_per_gpu": n_loc,
+                   "api": "autograd entry points" if args.autograd else "forward / backward helpers of the drop-in modules (C-ABI calls without torch.autograd)",
                    "partition": ("(batch, KV head) units %d..%d of %d on rank 0; no data-path collective" % (lo, hi - 1, n_units)) if strong else "every rank runs all units",
                    "l2": "inputs+outputs per step (%.0f MB per GPU) %s the 126 MB L2" %
                    (8 * dq_.numel() * dq_.element_size() / 1e6, "exceed" if 8 * dq_.numel() * dq_.element_size() > 126e6 else "do NOT exceed")},

@@ -77,6 +77,10 @@ def lib():
             L = ctypes.CDLL(LIB_PATH)
             vp, i32, i64, f32, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float, ctypes.c_size_t
             L.corope_abi_version.restype = i32
+            L.corope_status_mirror_refresh.restype = i32
+            L.corope_status_mirror_refresh.argtypes = [vp, vp, vp]
+            L.corope_status_mirror_clear.restype = i32
+            L.corope_status_mirror_clear.argtypes = [vp, vp, vp]
             L.corope_status_string.restype = ctypes.c_char_p
             L.corope_status_string.argtypes = [i32]
             L.corope_workspace_bytes.restype = sz
@@ -154,24 +158,30 @@ def require_cuda(t):
 
 
 class _DeviceStatus:
-    """The device status word of one GPU with a pinned host mirror that a side stream refreshes after every call."""
+    """The device status word of one GPU with a pinned host mirror that the library's side stream refreshes after every call."""
 
     def __init__(self, index):
         dev = torch.device("cuda", index)
+        self.index = index
         self.word = torch.zeros(1, dtype=torch.int32, device=dev)
         self.mirror = torch.zeros(1, dtype=torch.int32).pin_memory()
-        self.stream = torch.cuda.Stream(dev)
-        self.event = None
+        self.word_ptr = self.word.data_ptr()
+        self.mirror_ptr = self.mirror.data_ptr()
+        self.mirror_view = (ctypes.c_int * 1).from_address(self.mirror_ptr)   # a plain int read, no tensor indexing per call
 
 
 def _status(device):
-    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
-    with _lock:
-        st = _status_words.get(key)
-        if st is None:
-            st = _DeviceStatus(key)
-            _status_words[key] = st
-        return st
+    key = device.index if isinstance(device, torch.device) else torch.device(device).index
+    if key is None:
+        key = torch.cuda.current_device()
+    st = _status_words.get(key)
+    if st is None:
+        with _lock:
+            st = _status_words.get(key)
+            if st is None:
+                st = _DeviceStatus(key)
+                _status_words[key] = st
+    return st
 
 
 def status_word(device):
@@ -192,13 +202,11 @@ def pre_call(device):
     if getattr(_batched, "depth", 0) > 0:
         return
     st = _status(device)
-    if st.event is not None and st.event.query():
-        v = int(st.mirror[0])
-        if v != 0:
-            st.mirror.zero_()
-            st.word.zero_()
-            st.event = None
-            raise RuntimeError("corope_b200: an earlier kernel reported device status 0x%x: %s" % (v, _status_message(v)))
+    v = st.mirror_view[0]
+    if v != 0:
+        with torch.cuda.device(st.index):
+            lib().corope_status_mirror_clear(st.word_ptr, st.mirror_ptr, torch.cuda.current_stream(st.index).cuda_stream)
+        raise RuntimeError("corope_b200: an earlier kernel reported device status 0x%x: %s" % (v, _status_message(v)))
 
 
 _batched = threading.local()
@@ -223,19 +231,21 @@ class batched_status:
         return False
 
 
-def post_call(device):
-    """Called after a launch: a side stream copies the status word to its pinned mirror once the caller's stream gets there
-    (the caller's stream itself is not delayed)."""
+def post_call(device, stream=None):
+    """Called after a launch: the library's side stream copies the status word to its pinned mirror once the caller's stream
+    gets there (the caller's stream itself only records an event).  The caller has the device current."""
     if getattr(_batched, "depth", 0) > 0:
         return
-    st = _status(device)
     if torch.cuda.is_current_stream_capturing():
         return
-    done = torch.cuda.current_stream(device).record_event()
-    st.stream.wait_event(done)
-    with torch.cuda.stream(st.stream):
-        st.mirror.copy_(st.word, non_blocking=True)
-        st.event = st.stream.record_event()
+    st = _status(device)
+    if stream is None:
+        stream = torch.cuda.current_stream(st.index).cuda_stream
+    if torch.cuda.current_device() == st.index:
+        lib().corope_status_mirror_refresh(st.word_ptr, st.mirror_ptr, stream)
+    else:   # the library's side stream belongs to the current device
+        with torch.cuda.device(st.index):
+            lib().corope_status_mirror_refresh(st.word_ptr, st.mirror_ptr, stream)
 
 
 def check_status(device=None):
@@ -244,9 +254,9 @@ def check_status(device=None):
     st = _status(dev)
     v = int(st.word.item())
     if v != 0:
-        st.word.zero_()
-        st.mirror.zero_()
-        st.event = None
+        with torch.cuda.device(st.index):
+            lib().corope_status_mirror_clear(st.word_ptr, st.mirror_ptr, torch.cuda.current_stream(st.index).cuda_stream)
+        torch.cuda.synchronize(st.index)
         raise RuntimeError("corope_b200 kernel reported device status 0x%x: %s" % (v, _status_message(v)))
 
 

@@ -1,5 +1,6 @@
 // extern "C" entry points of libcorope_b200.so: argument validation, workspace carving, kernel selection.
 #include <atomic>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -116,6 +117,52 @@ using namespace corope;
 extern "C" {
 
 int corope_abi_version(void) { return 1; }
+
+// ---- host mirror of the status word -----------------------------------------------------------------------------------
+// A side stream per device copies the word to a pinned host location whenever the caller's stream reaches the point of the
+// call; the caller's stream is not delayed (it only records an event) and the host never synchronises.
+namespace {
+struct MirrorState {
+    cudaStream_t side = nullptr;
+    cudaEvent_t reached = nullptr;
+};
+MirrorState g_mirror[64];
+std::mutex g_mirror_mutex;
+int mirror_state(MirrorState** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return COROPE_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_mirror_mutex);
+    MirrorState& m = g_mirror[dev];
+    if (!m.side) {
+        if ((e = cudaStreamCreateWithFlags(&m.side, cudaStreamNonBlocking)) != cudaSuccess) return (int)e;
+        if ((e = cudaEventCreateWithFlags(&m.reached, cudaEventDisableTiming)) != cudaSuccess) return (int)e;
+    }
+    *out = &m;
+    return COROPE_OK;
+}
+}  // namespace
+
+int corope_status_mirror_refresh(const int* status_word, int* host_mirror, void* stream) {
+    if (!status_word || !host_mirror) return COROPE_ERR_NULL_POINTER;
+    MirrorState* m = nullptr;
+    if (int e = mirror_state(&m)) return e;
+    cudaError_t e = cudaEventRecord(m->reached, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(m->side, m->reached, 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host_mirror, status_word, sizeof(int), cudaMemcpyDeviceToHost, m->side);
+    return (int)e;
+}
+
+int corope_status_mirror_clear(int* status_word, int* host_mirror, void* stream) {
+    if (!status_word || !host_mirror) return COROPE_ERR_NULL_POINTER;
+    MirrorState* m = nullptr;
+    if (int e = mirror_state(&m)) return e;
+    cudaError_t e = cudaStreamSynchronize(m->side);   // no copy of the old value may land after the mirror is reset
+    if (e == cudaSuccess) e = cudaMemsetAsync(status_word, 0, sizeof(int), (cudaStream_t)stream);
+    *host_mirror = 0;
+    return (int)e;
+}
 
 const char* corope_status_string(int status) {
     switch (status) {

@@ -16,15 +16,16 @@
 //     dK~ += dS^T Q~                      [128 keys x 128]  accumulated in TMEM over the sweep
 //     dQ~^T = K~^T dS^T                   [128 (head dim) x 64 queries]  -> added to a global fp32 accumulator
 // i.e. five tile products per pair (the reference's Triton kernel spends seven, fused_rope_attn.py:341-470).
-// dS^T is written once to shared memory (fp16, 128-byte swizzle) and is read both as the K-major A operand of
-// dK~ and as the MN-major B operand of dQ~^T; K~, Q~ and dO likewise serve two MMAs each from one buffer.
+// dS^T is written to shared memory (fp16, 128-byte swizzle) as the MN-major B operand of dQ~^T and to TMEM (behind P^T, over
+// S^T columns its group has already read) as the A operand of dK~ -- the TMEM copy takes 16 KiB per step off the
+// shared-memory port, which bounds the step (0.933 -> 0.917 ms at Llama-7B-4K); K~, Q~ and dO serve two MMAs each from one buffer.
 //
 // Warp roles (768 threads = 6 warpgroups, registers re-divided with setmaxnreg): warp 0 TMA producer; warp 1 MMA
 // issuer + TMEM owner (warps 2-3 spare); warps 4-11 two rotation groups (half of the K block once, half of every Q
 // tile); warps 12-15 / 16-19 two softmax groups, each taking 32 of the 64 query columns of every step; warps 20-23
 // drain dQ~^T from TMEM and add it to the fp32 accumulator with reductions.  After the sweep the softmax groups write
 // dV and dK (inverse rotation and the ln2 factor applied in registers).
-// TMEM columns: S^T/P^T buffers [0,64) [64,128) (P^T of queries 0-31 in columns 0-15, of queries 32-63 in columns 32-47); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
+// TMEM columns: S^T/P^T/dS^T buffers [0,64) [64,128) (P^T of queries 0-31 in columns 0-15 and their dS^T in 16-31, of queries 32-63 in columns 32-47 / 48-63); dP^T/dQ~^T buffers [128,192) [192,256); dV [256,384); dK~ [384,512).
 // A separate small kernel turns the fp32 dQ~ accumulator into dQ (inverse rotation, * sm_scale).
 //
 // Replaces _attn_bwd / _attn_bwd_dkdv / _attn_bwd_dq of the reference (fused-rope/fused_rope_attn.py:341-649).
@@ -301,8 +302,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int kk = 0; kk < kBQ / 16; ++kk)   // dV += P^T dO : K = 64 queries
                     if (leader) umma_ts2(tmem + TDV, tmem + TS0 + b * 64 + (kk >> 1) * 32 + (kk & 1) * 8, dob + kk * (2048 >> 4), kHi, id_dv, (acc || kk > 0) ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~
-                    if (leader) umma_ss2(tmem + TDK, dsb + kk * (32 >> 4), kHi, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < kBQ / 16; ++kk)   // dK~ += dS^T Q~ : A = dS^T from TMEM (columns 16-31 / 48-63 of the S^T buffer)
+                    if (leader) umma_ts2(tmem + TDK, tmem + TS0 + b * 64 + (kk >> 1) * 32 + 16 + (kk & 1) * 8, qb + kk * (2048 >> 4), kHi, id_dk, (acc || kk > 0) ? 1u : 0u);
             };
             // Q tiles that arrive rotated (pre-pass) are ready as they land; otherwise the rotation groups pass them on
             const int q_bar = p.q_rot != nullptr ? QDO_FULL : Q_ROT;
@@ -446,6 +447,7 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     dd[i] = pack_half2_sat(s0, s1);
                 }
                 COROPE_TMEM_ST16(tS + c * 32, pp);   // each group writes P^T over the start of its own 32 S^T columns: the other group's S^T may still be unread
+                COROPE_TMEM_ST16(tS + c * 32 + 16, dd);   // dS^T behind it, as the A operand of dK~ (TMEM, not shared memory: 16 KiB less through the port per step)
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
                     const int chunk = (c * 4 + w) ^ (row & 7);
@@ -535,7 +537,8 @@ rope_bwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             tc_fence_before();
             mbar_arrive_warp(&bars[DQ_EMPTY + b], lane);
             // stage the tile as [query][head dim] (lanes = consecutive head-dim indices: conflict-free), then one thread
-            // adds it to the fp32 accumulator with a single bulk reduce instead of 8192 scalar reductions
+            // adds it to the fp32 accumulator with a single bulk reduce.  (256 warp-wide red.global.add.f32 per step straight
+            // from the registers, one 128-byte line each, skip the staging tile but measured 8 % slower: 0.992 against 0.917 ms)
             if (threadIdx.x == kDrainWarp0 * 32) bulk_wait_group_read0();   // the previous reduce has finished reading the tile
             named_bar_sync(1, 128);
             float* tile = sDQ + dcol;

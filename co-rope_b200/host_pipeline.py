@@ -31,11 +31,19 @@ def _unit_view(t, n_units):
     return t.view(n_units, (B * H) // n_units, N, D)
 
 
-def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=None, theta=None, out=None, chunks=16):
+def auto_chunks(total_bytes, n_units):
+    """Chunk count of the pipeline when the caller names none: about 32 MB of traffic per chunk, between 2 and 16 chunks.  More
+    chunks hide more of the first copy-in and the last copy-out behind the kernels, but every chunk costs about 0.1 ms of host
+    work (two library calls and a dozen stream operations), which a small call would not earn back."""
+    return max(1, min(n_units, 16, max(2, int(total_bytes // (32 << 20)))))
+
+
+def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=None, theta=None, out=None, chunks=None):
     """o, dq, dk, dv for pinned host tensors q [B,Hq,N,D], k / v [B,Hkv,N,D], d_o like q (causal attention).
 
     With `freqs_cos` / `freqs_sin` (device tensors) this is the fused-RoPE attention (Hq == Hkv); with `theta` it is
     the Co-RoPE GQA attention.  `out` = (o, dq, dk, dv) preallocated pinned host tensors, or None to allocate them.
+    `chunks` = number of pipeline chunks (None: chosen from the size, see auto_chunks).
     Results are complete when the current stream has finished (the call does not synchronise).
     """
     if (theta is None) == (freqs_cos is None):
@@ -46,6 +54,8 @@ def attention_fwd_bwd_host(q, k, v, d_o, sm_scale, *, freqs_cos=None, freqs_sin=
     B, Hq, N, D = q.shape
     Hkv = k.shape[1]
     n_units = B * Hkv
+    if chunks is None:
+        chunks = auto_chunks(2 * sum(t.numel() * t.element_size() for t in (q, k, v, d_o)), n_units)
     chunks = max(1, min(int(chunks), n_units))
     if out is None:
         out = tuple(torch.empty_like(t).pin_memory() for t in (q, q, k, v))

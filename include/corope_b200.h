@@ -68,6 +68,16 @@ extern "C" {
 #define COROPE_DEV_RANGE 0x2000        /* a gradient term left the range of the 16-bit Co-RoPE backward and was clamped */
 
 int corope_abi_version(void);
+
+/*
+ * Host mirror of a status word, for callers that want to learn of a device-side error without ever synchronising:
+ * `_refresh` makes a side stream of the library copy *status_word to *host_mirror (pinned host memory) once `stream` has
+ * executed everything enqueued so far -- `stream` itself only records an event -- so that reading *host_mirror on the host
+ * before a later call shows whether an earlier call failed.  `_clear` resets both (it waits for the side stream first).
+ * No counterpart in the reference, whose kernels report nothing.
+ */
+int corope_status_mirror_refresh(const int* status_word, int* host_mirror, void* stream);
+int corope_status_mirror_clear(int* status_word, int* host_mirror, void* stream);
 const char* corope_status_string(int status);
 
 /* Bytes of caller-provided scratch (device memory, 256-byte aligned) an op needs.  Contents
