@@ -361,23 +361,14 @@ def run_triton_baseline(args):
                     res["error"] = "%s: %s" % (type(e).__name__, str(e)[:300])
                 out["ws%d" % ws] = res
         else:
-            sys.path.insert(0, os.path.join(REF_COPY, "corope-exp"))
-            import flash_attn_co_rope_gqa_triton as ref_kernels
-            gen = torch.Generator(device="cpu").manual_seed(7)
-            q = torch.randn((B, H, N, D), generator=gen).to(torch.float16).to(dev)
-            k, v = (torch.randn((B, Hkv, N, D), generator=gen).to(torch.float16).to(dev) for _ in range(2))
-            res = {}
-            try:
-                fn = lambda: ref_kernels.attention(q, k, v, True, D ** -0.5, THETA)
-                fn()
-                torch.cuda.synchronize()
-                f_ms = timed_like_do_bench(fn, reps, flush)
-                res["fwd_ms"] = f_ms[len(f_ms) // 2]
-                res["fwd_tflops"] = F / res["fwd_ms"] / 1e9
-                res["bwd_ms"] = None   # the reference's Co-RoPE backward is dense PyTorch: 68.7 GB of temporaries at this shape
-            except Exception as e:
-                res["error"] = "%s: %s" % (type(e).__name__, str(e)[:300])
-            out["fwd"] = res
+            # Not run: the reference's Co-RoPE Triton forward (corope-exp/flash_attn_co_rope_gqa_triton.py) did not return on
+            # B200 with triton 3.6.0 at group size 4, D = 128 -- 900 s at N = 2048 and 150 s each at N = 128, 256, 512 passed
+            # without the first call finishing (the GPU stayed usable; its own comparison script's small case does run and is
+            # part of the tests).  Its backward is dense PyTorch (68.7 GB of temporaries at this shape).
+            out = {"unavailable": "the reference's Co-RoPE Triton forward did not finish its first call within 900 s at this shape "
+                                  "(nor within 150 s at N = 128) on B200 with triton 3.6.0; not run again"}
+            print("TRITON_BASELINE " + json.dumps(out), flush=True)
+            return
         out.update({"dtype": "f16", "shape": [B, H, Hkv, N, D], "sm_scale": 0.5 if kind == "rope" else D ** -0.5, "reps": reps,
                     "method": "L2 flushed before every call, CUDA events per call, median"})
         import triton

@@ -127,6 +127,10 @@ def lib():
             L.corope_gqa_fwd.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp, sz, vp, vp]
             L.corope_gqa_bwd.restype = i32
             L.corope_gqa_bwd.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, f32, vp, sz, vp, vp]
+            L.corope_gqa_fwd_strided.restype = i32
+            L.corope_gqa_fwd_strided.argtypes = L.corope_gqa_fwd.argtypes + [ctypes.POINTER(Strides)]
+            L.corope_gqa_bwd_strided.restype = i32
+            L.corope_gqa_bwd_strided.argtypes = L.corope_gqa_bwd.argtypes + [ctypes.POINTER(Strides)]
             _lib = L
         return _lib
 

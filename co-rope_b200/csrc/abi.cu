@@ -236,6 +236,22 @@ void set_strides(RopeParams& p, const corope_strides_t* st, int Hq, int Hkv, int
     p.sdk = st ? conv(st->dk) : ckv;
     p.sdv = st ? conv(st->dv) : ckv;
 }
+void set_gqa_strides(GqaParams& p, const corope_strides_t* st) {
+    auto conv = [](const int64_t (&a)[3]) {
+        Strides r;
+        r.b = a[0]; r.h = a[1]; r.n = a[2];
+        return r;
+    };
+    const Strides cq = contiguous_strides(p.Hq, p.N, p.D), ckv = contiguous_strides(p.Hkv, p.N, p.D);
+    p.sq = st ? conv(st->q) : cq;
+    p.sk = st ? conv(st->k) : ckv;
+    p.sv = st ? conv(st->v) : ckv;
+    p.so = st ? conv(st->o) : cq;
+    p.sdo = st ? conv(st->d_o) : cq;
+    p.sdq = st ? conv(st->dq) : cq;
+    p.sdk = st ? conv(st->dk) : ckv;
+    p.sdv = st ? conv(st->dv) : ckv;
+}
 // The tensor-core paths move rows with TMA and 16-byte vector accesses: base pointers and all strides must be multiples of 16 bytes.
 bool vec_ok(const void* ptr, const Strides& st) {
     return ((uintptr_t)ptr % 16) == 0 && st.b % 8 == 0 && st.h % 8 == 0 && st.n % 8 == 0 && st.n > 0;
@@ -490,6 +506,13 @@ static int check_gqa(int B, int Hq, int Hkv, int N, int D, int dtype) {
 
 int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* lse2, float* a_diag, int B, int Hq, int Hkv, int N, int D,
                    int dtype, float sm_scale, float theta, void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    return corope_gqa_fwd_strided(q, k, v, o, lse2, a_diag, B, Hq, Hkv, N, D, dtype, sm_scale, theta, workspace, workspace_bytes, status_word,
+                                  stream, nullptr);
+}
+
+int corope_gqa_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse2, float* a_diag, int B, int Hq, int Hkv, int N,
+                           int D, int dtype, float sm_scale, float theta, void* workspace, size_t workspace_bytes, int* status_word,
+                           void* stream, const corope_strides_t* strides) {
     if (!q || !k || !v || !o || !lse2 || !a_diag) return COROPE_ERR_NULL_POINTER;
     if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
     GqaWorkspace w = gqa_workspace_layout(false, B, Hq, Hkv, N, D, dtype);
@@ -497,7 +520,10 @@ int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* 
     GqaParams p{};
     p.q = q; p.k = k; p.v = v; p.out_o = o; p.lse2 = lse2; p.a_diag = a_diag;
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
-    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype)) {
+    set_gqa_strides(p, strides);
+    if (!strides_positive(p.sq, D) || !strides_positive(p.sk, D) || !strides_positive(p.sv, D) || !strides_positive(p.so, D)) return COROPE_ERR_BAD_STRIDE;
+    // the tensor-core kernels read K and V in 16-byte vectors and store O in element pairs
+    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype) && vec_ok(q, p.sq) && vec_ok(k, p.sk) && vec_ok(v, p.sv) && vec_ok(o, p.so)) {
         p.k_pairs = reinterpret_cast<uint32_t*>((char*)workspace + w.k_pairs);
         p.v_half = reinterpret_cast<__half*>((char*)workspace + w.v_half);
         g_last_family[COROPE_OP_GQA_FWD] = 1;
@@ -510,6 +536,14 @@ int corope_gqa_fwd(const void* q, const void* k, const void* v, void* o, float* 
 int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2, const float* a_diag,
                    void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
                    void* workspace, size_t workspace_bytes, int* status_word, void* stream) {
+    return corope_gqa_bwd_strided(q, k, v, o, d_o, lse2, a_diag, dq, dk, dv, B, Hq, Hkv, N, D, dtype, sm_scale, theta, workspace,
+                                  workspace_bytes, status_word, stream, nullptr);
+}
+
+int corope_gqa_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse2,
+                           const float* a_diag, void* dq, void* dk, void* dv, int B, int Hq, int Hkv, int N, int D, int dtype,
+                           float sm_scale, float theta, void* workspace, size_t workspace_bytes, int* status_word, void* stream,
+                           const corope_strides_t* strides) {
     if (!q || !k || !v || !o || !d_o || !lse2 || !a_diag || !dq || !dk || !dv) return COROPE_ERR_NULL_POINTER;
     if (int e = check_gqa(B, Hq, Hkv, N, D, dtype)) return e;
     GqaWorkspace w = gqa_workspace_layout(true, B, Hq, Hkv, N, D, dtype);
@@ -521,7 +555,12 @@ int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, c
     p.dk_acc = reinterpret_cast<float*>((char*)workspace + w.dk_acc);
     p.dv_acc = reinterpret_cast<float*>((char*)workspace + w.dv_acc);
     p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = Hq / Hkv; p.N = N; p.D = D; p.sm_scale = sm_scale; p.theta = theta; p.status = status_word;
-    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype)) {
+    set_gqa_strides(p, strides);
+    for (const Strides* st : {&p.sq, &p.sk, &p.sv, &p.so, &p.sdo, &p.sdq, &p.sdk, &p.sdv})
+        if (!strides_positive(*st, D)) return COROPE_ERR_BAD_STRIDE;
+    const bool vec = vec_ok(q, p.sq) && vec_ok(k, p.sk) && vec_ok(v, p.sv) && vec_ok(o, p.so) && vec_ok(d_o, p.sdo) && vec_ok(dq, p.sdq) &&
+                     vec_ok(dk, p.sdk) && vec_ok(dv, p.sdv);
+    if (g_policy.load() == 0 && gqa_fwd_mma_supported(N, D, dtype) && vec) {
         p.k_pairs = reinterpret_cast<uint32_t*>((char*)workspace + w.k_pairs);
         p.v_half = reinterpret_cast<__half*>((char*)workspace + w.v_half);
         p.use_mma = 1;

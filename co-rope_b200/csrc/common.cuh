@@ -57,6 +57,26 @@ __host__ __device__ inline int64_t row_offset(const Strides& st, int H, int bh, 
     return (int64_t)(bh / H) * st.b + (int64_t)(bh % H) * st.h + (int64_t)n * st.n;
 }
 
+// Addressing of flat row index `row` (= (b * H + h) * N + n) of a strided [B, H, N, D] tensor in the elementwise kernels.  The
+// host decides once whether the rows are evenly spaced (every contiguous tensor): then the offset is one multiply; the general
+// form costs two integer divisions per thread, which these memory-bound kernels (a few 16-byte accesses per thread) would feel.
+struct RowAddr {
+    Strides st;
+    int H, N;
+    int flat;
+};
+inline RowAddr row_addr(const Strides& st, int H, int N) {
+    RowAddr a;
+    a.st = st; a.H = H; a.N = N;
+    a.flat = rows_collapse(st, H, N) ? 1 : 0;
+    return a;
+}
+__host__ __device__ inline int64_t flat_row_offset(const RowAddr& a, size_t row) {
+    if (a.flat) return (int64_t)row * a.st.n;
+    const unsigned r = (unsigned)row, bh = r / (unsigned)a.N;   // row counts stay below 2^31 (checked at the entry points)
+    return row_offset(a.st, a.H, (int)bh, (int)(r - bh * (unsigned)a.N));
+}
+
 // Launch parameters common to the fused-RoPE kernels.
 struct RopeParams {
     const void* q;
@@ -111,6 +131,7 @@ struct GqaParams {
     float sm_scale;
     float theta;
     int* status;
+    Strides sq, sk, sv, so, sdo, sdq, sdk, sdv;   // strides of q, k, v, o (forward output or backward input), dO, dq, dk, dv
 };
 
 #ifdef __CUDACC__

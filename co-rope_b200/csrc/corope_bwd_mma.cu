@@ -53,21 +53,10 @@ constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs *
                               64 * kPsRowBytes + 64 * kVRowBytes + kKT * kDkStride * 4 + kRows * kKT * 4 + 16 * kGrRowBytes + 16 * kVRowBytes;
 static_assert(kSmemBytes <= 232448 - 1024, "shared memory budget");
 
-__device__ __forceinline__ void mma16816_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* smem_row) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(smem_u32(smem_row)));
-}
-// transpose of an 8x8 matrix of 16-bit values held one register per lane (row = lane / 4, columns 2 (lane % 4), +1)
-__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
-    uint32_t d;
-    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
-    return d;
 }
 __device__ __forceinline__ void red_add_v2(float* gptr, float a, float b) {
     asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(gptr), "f"(a), "f"(b) : "memory");
@@ -127,7 +116,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
     // ---- per-CTA and per-lane constants
     for (int idx = tid; idx < kRows * kPairs; idx += kThreads) {
         const int r = idx >> 6, pp = idx & 63;
-        const T* row = Q + (q_head0 * N + i0 + r) * kD;
+        const T* row = Q + row_offset(p.sq, p.Hq, (int)q_head0, i0 + r);
         qls[r * kPairs + perm_slot(pp)] = to_half2<T>(row[pp], row[pp + kPairs]);
     }
     for (int d = tid; d < kPairs; d += kThreads) {
@@ -139,7 +128,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         const int r = idx >> 6, d2 = idx & 63;
         uint32_t val = 0u;
         if (r < kKG) {
-            const T* row = DO + ((q_head0 + r % G) * N + i0 + r / G) * kD;
+            const T* row = DO + row_offset(p.sdo, p.Hq, (int)q_head0 + r % G, i0 + r / G);
             val = to_half2<T>(row[2 * d2], row[2 * d2 + 1]);
         }
         *reinterpret_cast<uint32_t*>(dos + r * kVRowBytes + d2 * 4) = val;
@@ -150,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         const int r = idx >> 6, d2 = idx & 63;
         uint32_t val = 0u;
         if (r < kRows) {
-            const T* row = Q + (q_head0 * N + i0 + r) * kD;
+            const T* row = Q + row_offset(p.sq, p.Hq, (int)q_head0, i0 + r);
             val = to_half2<T>(row[2 * d2], row[2 * d2 + 1]);
         }
         *reinterpret_cast<uint32_t*>(qlr + r * kVRowBytes + d2 * 4) = val;
@@ -158,11 +147,11 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
     __syncthreads();
     {
         const bool valid = h < G;
-        const T* qrow = Q + ((q_head0 + (valid ? h : 0)) * N + i) * kD;
-        const T* dorow = DO + ((q_head0 + (valid ? h : 0)) * N + i) * kD;
+        const T* qrow = Q + row_offset(p.sq, p.Hq, (int)q_head0 + (valid ? h : 0), i);
+        const T* dorow = DO + row_offset(p.sdo, p.Hq, (int)q_head0 + (valid ? h : 0), i);
         const int ha = 2 * c, hb = 2 * c + 1;   // the two heads of the lane's B-operand entries
-        const T* qa = Q + ((q_head0 + (ha < G ? ha : 0)) * N + i) * kD;
-        const T* qb = Q + ((q_head0 + (hb < G ? hb : 0)) * N + i) * kD;
+        const T* qa = Q + row_offset(p.sq, p.Hq, (int)q_head0 + (ha < G ? ha : 0), i);
+        const T* qb = Q + row_offset(p.sq, p.Hq, (int)q_head0 + (hb < G ? hb : 0), i);
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
             uint32_t a[4], aw[4], ad[4], bq[4];
@@ -486,7 +475,7 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
     }
     if (__any_sync(0xffffffffu, range_clamped) && lane == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_RANGE);
     if (valid) {
-        T* DQ = reinterpret_cast<T*>(p.dq) + ((q_head0 + h) * N + i) * kD;
+        T* DQ = reinterpret_cast<T*>(p.dq) + row_offset(p.sdq, p.Hq, (int)q_head0 + h, i);
 #pragma unroll
         for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -502,7 +491,8 @@ template <typename T, int G>
 int launch_g(const GqaParams& p, cudaStream_t s) {
     dim3 grid(p.N / kRows, p.B * p.Hkv);
     const size_t rows = (size_t)p.B * p.Hkv * p.N;
-    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows);
+    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows,
+                                                                                  row_addr(p.sk, p.Hkv, p.N), row_addr(p.sv, p.Hkv, p.N));
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;

@@ -10,10 +10,13 @@
 //   1. leader scores of the CTA's 8 rows against the 64 keys: warp w takes keys 8w..8w+7 (8 MMAs, rows of the A
 //      operand = the 8 query rows), sigmoid, causal mask -> z in shared memory;
 //   2. each warp turns its row of z into Delta (suffix sums inside the tile + carry from the tiles above);
-//   3. for every block of 8 keys: lane (key = lane/4, c = lane%4) rotates the 16 (k1, k2) pairs p = c mod 4 of its key
-//      by Delta_ij w_p -- these are exactly the B-operand registers of 8 MMAs whose A operand holds the G heads of
-//      the row (rows >= G are zero) -> S[h][key];
-//   4. online softmax per head (log2 domain), P as fp16 A operand, V through ldmatrix.trans, O in registers.
+//   3. for every block of 16 keys the scores come out transposed, S^T = K' Q^T: the keys are the 16 rows of the A operand
+//      (all in use) and the G heads the columns; lane (r = lane/4, c = lane%4) rotates the 16 (k1, k2) pairs p = c mod 4 of
+//      keys r and r + 8 by Delta_ij w_p, and the rotated pairs are the A-operand registers as they stand;
+//   4. online softmax per head (log2 domain); O^T += V^T P^T with V through ldmatrix.trans (A) and P transposed in
+//      registers (movmatrix) as B; O^T [d][head] stays in registers.
+// (With the heads as the rows of A, as a first version had them, half of every operand quad was zero padding that had to be
+// rebuilt in registers per MMA: 19.9 instead of 14.7 instructions per (query, key, pair) and twice the MMAs.)
 // The K dimension of the score MMAs is ordered (pair, component): index 2p is the first half of pair p, 2p+1 the
 // second; Q and K use the same order, so dot products are unchanged.  Shared-memory rows of K / leader Q are stored
 // permuted so that a lane's 16 pairs are four 16-byte loads without bank conflicts (see perm_slot).
@@ -64,11 +67,11 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
         }
         cp_async_commit();
     };
-    const T* QL = reinterpret_cast<const T*>(p.q) + q_head0 * N * kD;
+    const T* QL = reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.Hq, (int)q_head0, 0);   // leader head of the group
 
     for (int idx = tid; idx < kRows * kPairs; idx += kThreads) {
         const int r = idx >> 6, pp = idx & 63;
-        const T* row = QL + (size_t)(i0 + r) * kD;
+        const T* row = QL + (int64_t)(i0 + r) * p.sq.n;
         qls[r * kPairs + perm_slot(pp)] = to_half2<T>(row[pp], row[pp + kPairs]);
     }
     for (int d = tid; d < kPairs; d += kThreads) {
@@ -80,7 +83,7 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
     // per-lane constants: the 16 pairs of this lane (p = c mod 4), their frequencies, and the query operand of head h
     {
         uint32_t aq[16];
-        const T* qrow = reinterpret_cast<const T*>(p.q) + ((q_head0 + (h < G ? h : 0)) * N + i) * kD;
+        const T* qrow = reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.Hq, (int)q_head0 + (h < G ? h : 0), i);
 #pragma unroll
         for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -93,10 +96,14 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
         __syncwarp();
     }
 
-    float m = -INFINITY, l = 0.f;   // of head h (the 4 lanes of a head agree on m; l is a per-lane partial sum)
-    float o[16][2];
+    // From here on the MMAs are "transposed": keys are the M rows (16 per MMA, all used), the group's heads the 8 N columns.
+    // A lane (r = lane / 4, c = lane % 4) owns keys r and r + 8 of a 16-key block on the A side and heads 2c, 2c + 1 on the
+    // result side; the query operand above (head r, pairs of class c) is the B operand as it stands.
+    const int r = h;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // heads 2c, 2c + 1 (l: partial sums over this lane's keys)
+    float o[8][4];   // O^T: [db] rows d = 16 db + r (+ 8 for entries 2, 3), columns heads 2c, 2c + 1
 #pragma unroll
-    for (int db = 0; db < 16; ++db) o[db][0] = o[db][1] = 0.f;
+    for (int db = 0; db < 8; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
     float carry = 0.f;              // sum of z_ik over the keys of the tiles already swept
     const float sc2 = p.sm_scale * kLog2e;
 
@@ -144,89 +151,99 @@ __global__ void __launch_bounds__(kThreads, 2) corope_fwd_mma_kernel(GqaParams p
         }
         __syncwarp();
 
-        // 3. scores of the G heads for this row, 8 keys at a time
-        float sc[8][2];
+        // 3. S^T of the row: 16 keys x 8 heads per block; the lane rotates the 16 pairs of its two keys, which are the A
+        //    operand registers as they stand (a0 / a2: key r, a1 / a3: key r + 8)
+        float sc[4][4];
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb) {
-            sc[nb][0] = sc[nb][1] = -INFINITY;
-            if (j0 + nb * 8 > i) continue;   // every key of the block is above the diagonal (warp-uniform)
-            const float delta = dl[warp * kKT + nb * 8 + h];
-            const uint4* kp = reinterpret_cast<const uint4*>(ks + (nb * 8 + h) * kKRow) + c;
-            float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
+        for (int kb = 0; kb < 4; ++kb) {
+            sc[kb][0] = sc[kb][1] = sc[kb][2] = sc[kb][3] = -INFINITY;
+            if (j0 + kb * 16 > i) continue;   // every key of the block is above the diagonal (warp-uniform)
+            const float dA = dl[warp * kKT + kb * 16 + r], dB = dl[warp * kKT + kb * 16 + r + 8];
+            const uint4* kpA = reinterpret_cast<const uint4*>(ks + (kb * 16 + r) * kKRow) + c;
+            const uint4* kpB = reinterpret_cast<const uint4*>(ks + (kb * 16 + r + 8) * kKRow) + c;
+            float accE[4] = {0.f, 0.f, 0.f, 0.f}, accO[4] = {0.f, 0.f, 0.f, 0.f};   // two accumulator chains
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                const uint4 kv = kp[4 * s];
+                const uint4 kva = kpA[4 * s], kvb = kpB[4 * s];
                 const float4 wv = *reinterpret_cast<const float4*>(ws + c * kWStride + s * 4);
-                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
                 const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
-                uint32_t bf[4];
+                const uint32_t kwa[4] = {kva.x, kva.y, kva.z, kva.w}, kwb[4] = {kvb.x, kvb.y, kvb.z, kvb.w};
+                uint32_t ra[4], rb[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float sn, cs;
-                    sincos_fast<DIRECT>(delta * wq[e], &sn, &cs);
-                    // (K'1, K'2) = (k1, k2) (c, c) + (k2, k1) (s, -s) in packed fp16 arithmetic
-                    const __half2 kk = *reinterpret_cast<const __half2*>(&kw[e]);
-                    const uint32_t sw = __byte_perm(kw[e], 0, 0x1032);
-                    const __half2 ksw = *reinterpret_cast<const __half2*>(&sw);
-                    const __half2 r = __hfma2(kk, __floats2half2_rn(cs, cs), __hmul2(ksw, __floats2half2_rn(sn, -sn)));
-                    bf[e] = *reinterpret_cast<const uint32_t*>(&r);
+                    ra[e] = rotate_pair<DIRECT>(kwa[e], dA * wq[e]);
+                    rb[e] = rotate_pair<DIRECT>(kwb[e], dB * wq[e]);
                 }
-                const uint4 av = aqs[s * 32 + lane];
-                mma16816(s0, s1, av.x, av.y, bf[0], bf[1], s0, s1);
-                mma16816(t0, t1, av.z, av.w, bf[2], bf[3], t0, t1);   // two accumulator chains
+                const uint32_t a_even[4] = {ra[0], rb[0], ra[1], rb[1]}, a_odd[4] = {ra[2], rb[2], ra[3], rb[3]};
+                const uint4 av = aqs[s * 32 + lane];   // the query operand (re-read per block: registers are short)
+                mma16816_full(accE, a_even, av.x, av.y);
+                mma16816_full(accO, a_odd, av.z, av.w);
             }
-            const int key = j0 + nb * 8 + 2 * c;
-            sc[nb][0] = key <= i ? (s0 + t0) * sc2 : -INFINITY;
-            sc[nb][1] = key + 1 <= i ? (s1 + t1) * sc2 : -INFINITY;
+            const int keyA = j0 + kb * 16 + r;
+            if (keyA <= i) sc[kb][0] = (accE[0] + accO[0]) * sc2, sc[kb][1] = (accE[1] + accO[1]) * sc2;
+            if (keyA + 8 <= i) sc[kb][2] = (accE[2] + accO[2]) * sc2, sc[kb][3] = (accE[3] + accO[3]) * sc2;
         }
 
-        // 4. online softmax of head h (lanes 4h .. 4h+3 hold its 64 scores), then O += P V
-        float mx = m;
+        // 4. online softmax of heads 2c, 2c + 1 (their 64 scores sit in the 8 lanes of class c), then O^T += V^T P^T
+        float mx0 = m0, mx1 = m1;
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb) mx = fmax3(mx, sc[nb][0], sc[nb][1]);
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float alpha = fast_exp2(m - mx);   // the first tile holds the diagonal, so mx is finite
-        m = mx;
-        float psum = 0.f;
-        uint32_t pa[8];
-#pragma unroll
-        for (int nb = 0; nb < 8; ++nb) {
-            const float p0 = fast_exp2(sc[nb][0] - mx), p1 = fast_exp2(sc[nb][1] - mx);
-            pa[nb] = pack_half2(p0, p1);
-            const float2 pr = unpack_half2(pa[nb]);   // row sums from the rounded P
-            psum += pr.x + pr.y;
+        for (int kb = 0; kb < 4; ++kb) {
+            mx0 = fmax3(mx0, sc[kb][0], sc[kb][2]);
+            mx1 = fmax3(mx1, sc[kb][1], sc[kb][3]);
         }
-        l = l * alpha + psum;
 #pragma unroll
-        for (int db = 0; db < 16; ++db) {
-            o[db][0] *= alpha;
-            o[db][1] *= alpha;
+        for (int off = 4; off < 32; off <<= 1) {
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, off));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, off));
         }
-        const int n_kc = min(4, (i - j0) / 16 + 1);   // 16-key chunks that hold visible keys (warp-uniform)
+        const float alpha0 = fast_exp2(m0 - mx0), alpha1 = fast_exp2(m1 - mx1);   // the first tile holds the diagonal: mx is finite
+        m0 = mx0, m1 = mx1;
 #pragma unroll
-        for (int kc = 0; kc < 4; ++kc) {
-            if (kc >= n_kc) break;
-            const uint8_t* vrow = vs + (kc * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kVRowBytes + (lane >> 4) * 16;
+        for (int db = 0; db < 8; ++db) {
+            o[db][0] *= alpha0, o[db][1] *= alpha1;
+            o[db][2] *= alpha0, o[db][3] *= alpha1;
+        }
+        float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-            for (int dp = 0; dp < 8; ++dp) {
-                uint32_t r0, r1, r2, r3;
-                ldmatrix_x4_trans(r0, r1, r2, r3, vrow + dp * 32);
-                mma16816(o[2 * dp][0], o[2 * dp][1], pa[2 * kc], pa[2 * kc + 1], r0, r1, o[2 * dp][0], o[2 * dp][1]);
-                mma16816(o[2 * dp + 1][0], o[2 * dp + 1][1], pa[2 * kc], pa[2 * kc + 1], r2, r3, o[2 * dp + 1][0], o[2 * dp + 1][1]);
+        for (int kb = 0; kb < 4; ++kb) {
+            if (j0 + kb * 16 > i) continue;   // nothing visible in this block (warp-uniform)
+            const uint32_t pa = pack_half2(fast_exp2(sc[kb][0] - mx0), fast_exp2(sc[kb][1] - mx1));   // key r
+            const uint32_t pb = pack_half2(fast_exp2(sc[kb][2] - mx0), fast_exp2(sc[kb][3] - mx1));   // key r + 8
+            const float2 fa = unpack_half2(pa), fb = unpack_half2(pb);   // row sums from the rounded P
+            ps0 += fa.x + fb.x;
+            ps1 += fa.y + fb.y;
+            // P^T as B operand: (keys 2c, 2c + 1 | head r) is the transpose of what the lane holds (key r | heads 2c, 2c + 1)
+            const uint32_t b0 = movmatrix_trans(pa), b1 = movmatrix_trans(pb);
+            // V^T as A operand: four transposed 8x8 blocks (d 0-7 | 8-15) x (keys 0-7 | 8-15) of the block's V rows
+            const uint8_t* vrow = vs + (kb * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * kVRowBytes + ((lane >> 3) & 1) * 16;
+#pragma unroll
+            for (int db = 0; db < 8; ++db) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a[0], a[1], a[2], a[3], vrow + db * 32);
+                mma16816_full(o[db], a, b0, b1);
             }
         }
+        l0 = l0 * alpha0 + ps0;
+        l1 = l1 * alpha1 + ps1;
     }
 
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (h < G) {
-        const float inv = 1.f / l;
-        T* O = reinterpret_cast<T*>(p.out_o) + ((q_head0 + h) * N + i) * kD;
 #pragma unroll
-        for (int db = 0; db < 16; ++db)
-            *reinterpret_cast<uint32_t*>(O + db * 8 + 2 * c) = pack2<T>(o[db][0] * inv, o[db][1] * inv);
-        if (c == 0) p.lse2[(q_head0 + h) * N + i] = m + log2f(l);
+    for (int off = 4; off < 32; off <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, off);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, off);
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const int head = 2 * c + x;
+        if (head >= G) continue;
+        const float inv = 1.f / (x ? l1 : l0);
+        T* O = reinterpret_cast<T*>(p.out_o) + row_offset(p.so, p.Hq, (int)q_head0 + head, i);
+#pragma unroll
+        for (int db = 0; db < 8; ++db) {
+            O[db * 16 + r] = Elem<T>::from_f32(o[db][x] * inv);
+            O[db * 16 + r + 8] = Elem<T>::from_f32(o[db][2 + x] * inv);
+        }
+        if (r == 0) p.lse2[(q_head0 + head) * N + i] = (x ? m1 : m0) + log2f(x ? l1 : l0);
     }
     if (lane == 0) p.a_diag[(size_t)bg * N + i] = carry;
 }
@@ -235,7 +252,8 @@ template <typename T, int G>
 int launch_g(const GqaParams& p, cudaStream_t s) {
     dim3 grid(p.N / kRows, p.B * p.Hkv);
     const size_t rows = (size_t)p.B * p.Hkv * p.N;
-    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows);
+    gqa_pack_kv_kernel<T><<<(unsigned)((rows * 16 + 255) / 256), 256, 0, s>>>((const T*)p.k, (const T*)p.v, p.k_pairs, p.v_half, rows,
+                                                                                  row_addr(p.sk, p.Hkv, p.N), row_addr(p.sv, p.Hkv, p.N));
     count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;

@@ -77,11 +77,11 @@ __device__ __forceinline__ void sincos_phase(float x, float* s, float* c, bool d
 }
 
 template <typename T, int D>
-__device__ __forceinline__ void stage_plain(float* dst, int ld, const T* X, int r0, int rows, int N) {
+__device__ __forceinline__ void stage_plain(float* dst, int ld, const T* X, int64_t xs, int r0, int rows, int N) {   // xs: row stride of X
     for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
         int r = idx / D, d = idx % D;
         int pos = r0 + r;
-        dst[r * ld + d] = pos < N ? Elem<T>::to_f32(X[(size_t)pos * D + d]) : 0.f;
+        dst[r * ld + d] = pos < N ? Elem<T>::to_f32(X[(int64_t)pos * xs + d]) : 0.f;
     }
 }
 
@@ -105,11 +105,11 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i = i0 + warp;
     const size_t q_head0 = ((size_t)b * p.Hq + (size_t)g * G);
-    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bg * N * D;
-    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bg * N * D;
+    const T* K = reinterpret_cast<const T*>(p.k) + row_offset(p.sk, p.Hkv, bg, 0);
+    const T* V = reinterpret_cast<const T*>(p.v) + row_offset(p.sv, p.Hkv, bg, 0);
 
     for (int h = 0; h < G; ++h)
-        stage_plain<T, D>(q_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.q) + (q_head0 + h) * N * D, i0, kWarps, N);
+        stage_plain<T, D>(q_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.Hq, (int)q_head0 + h, 0), p.sq.n, i0, kWarps, N);
     for (int d = threadIdx.x; d < H2; d += kThreads) w_s[d] = 1.0f / powf(p.theta, (float)(2 * d) / (float)D);
 
     float m[G], l[G], acc[G][NC];
@@ -126,8 +126,8 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
     const int i_last = min(N - 1, i0 + kWarps - 1);
     for (int j0 = (i_last / kTile) * kTile; j0 >= 0; j0 -= kTile) {
         __syncthreads();
-        stage_plain<T, D>(k_s, D + kPad, K, j0, kTile, N);
-        stage_plain<T, D>(v_s, D, V, j0, kTile, N);
+        stage_plain<T, D>(k_s, D + kPad, K, p.sk.n, j0, kTile, N);
+        stage_plain<T, D>(v_s, D, V, p.sv.n, j0, kTile, N);
         __syncthreads();
         if (i >= N) continue;
         const int j = j0 + lane;
@@ -211,7 +211,7 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
     if (i < N) {
 #pragma unroll
         for (int h = 0; h < G; ++h) {
-            T* O = reinterpret_cast<T*>(p.out_o) + ((q_head0 + h) * N + i) * D;
+            T* O = reinterpret_cast<T*>(p.out_o) + row_offset(p.so, p.Hq, (int)q_head0 + h, i);
             float inv = 1.f / l[h];
 #pragma unroll
             for (int c = 0; c < NC; ++c) O[lane + 32 * c] = Elem<T>::from_f32(acc[h][c] * inv);
@@ -225,20 +225,23 @@ __global__ void __launch_bounds__(kThreads) corope_fwd_general_kernel(GqaParams 
 // backward
 // ------------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void gqa_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D) {
+__global__ void gqa_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, size_t rows, int D, RowAddr ao,
+                                 RowAddr ado) {
     size_t row = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     int lane = threadIdx.x & 31;
     if (row >= rows) return;
     float s = 0.f;
-    for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(o[row * D + d]) * Elem<T>::to_f32(d_o[row * D + d]);
+    const T* orow = o + flat_row_offset(ao, row);
+    const T* drow = d_o + flat_row_offset(ado, row);
+    for (int d = lane; d < D; d += 32) s += Elem<T>::to_f32(orow[d]) * Elem<T>::to_f32(drow[d]);
     s = warp_sum(s);
     if (lane == 0) delta[row] = s;
 }
 
 template <typename T>
-__global__ void gqa_finalize_kernel(const float* __restrict__ acc, T* __restrict__ out, size_t n) {
-    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = Elem<T>::from_f32(acc[i]);
+__global__ void gqa_finalize_kernel(const float* __restrict__ acc, T* __restrict__ out, size_t n, int D, RowAddr aout) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // over the contiguous fp32 accumulator [rows, D]
+    if (i < n) out[flat_row_offset(aout, i / (size_t)D) + (int)(i % (size_t)D)] = Elem<T>::from_f32(acc[i]);
 }
 
 template <typename T, int D, int G, bool ACCURATE>
@@ -264,8 +267,8 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int i = i0 + warp;
     const size_t q_head0 = ((size_t)b * p.Hq + (size_t)g * G);
-    const T* K = reinterpret_cast<const T*>(p.k) + (size_t)bg * N * D;
-    const T* V = reinterpret_cast<const T*>(p.v) + (size_t)bg * N * D;
+    const T* K = reinterpret_cast<const T*>(p.k) + row_offset(p.sk, p.Hkv, bg, 0);
+    const T* V = reinterpret_cast<const T*>(p.v) + row_offset(p.sv, p.Hkv, bg, 0);
     float* dk_acc = p.dk_acc + (size_t)bg * N * D;
     float* dv_acc = p.dv_acc + (size_t)bg * N * D;
     float* xg = xch + warp * kXch;                // g[G][32]
@@ -274,8 +277,8 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     float* xr = xd + kTile;                       // graw[32]
 
     for (int h = 0; h < G; ++h) {
-        stage_plain<T, D>(q_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.q) + (q_head0 + h) * N * D, i0, kWarps, N);
-        stage_plain<T, D>(do_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.d_o) + (q_head0 + h) * N * D, i0, kWarps, N);
+        stage_plain<T, D>(q_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.q) + row_offset(p.sq, p.Hq, (int)q_head0 + h, 0), p.sq.n, i0, kWarps, N);
+        stage_plain<T, D>(do_s + h * kWarps * D, D, reinterpret_cast<const T*>(p.d_o) + row_offset(p.sdo, p.Hq, (int)q_head0 + h, 0), p.sdo.n, i0, kWarps, N);
     }
     for (int d = threadIdx.x; d < H2; d += kThreads) w_s[d] = 1.0f / powf(p.theta, (float)(2 * d) / (float)D);
     for (int idx = threadIdx.x; idx < kTile * D; idx += kThreads) dk_t[idx] = dv_t[idx] = 0.f;
@@ -295,8 +298,8 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     const int i_last = min(N - 1, i0 + kWarps - 1);
     for (int j0 = 0; j0 <= i_last; j0 += kTile) {
         __syncthreads();   // previous tile's flush done, accumulators are zero
-        stage_plain<T, D>(k_s, D + kPad, K, j0, kTile, N);
-        stage_plain<T, D>(v_s, D + kPad, V, j0, kTile, N);
+        stage_plain<T, D>(k_s, D + kPad, K, p.sk.n, j0, kTile, N);
+        stage_plain<T, D>(v_s, D + kPad, V, p.sv.n, j0, kTile, N);
         __syncthreads();
         if (i < N && j0 <= i) {
             // ---------------- phase A: lane = key
@@ -435,7 +438,7 @@ __global__ void __launch_bounds__(kThreads) corope_bwd_general_kernel(GqaParams 
     if (i < N) {
 #pragma unroll
         for (int h = 0; h < G; ++h) {
-            T* DQ = reinterpret_cast<T*>(p.dq) + ((q_head0 + h) * N + i) * D;
+            T* DQ = reinterpret_cast<T*>(p.dq) + row_offset(p.sdq, p.Hq, (int)q_head0 + h, i);
 #pragma unroll
             for (int pi = 0; pi < NPI; ++pi) {
                 const int pd = lane + 32 * pi;
@@ -501,14 +504,15 @@ template <typename T>
 int bwd_all(const GqaParams& p, cudaStream_t s) {
     const size_t rows = (size_t)p.B * p.Hq * p.N;
     const size_t kv_elems = (size_t)p.B * p.Hkv * p.N * p.D;
-    gqa_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)p.o, (const T*)p.d_o, p.delta, rows, p.D); count_launch();
+    gqa_delta_kernel<T><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>((const T*)p.o, (const T*)p.d_o, p.delta, rows, p.D, row_addr(p.so, p.Hq, p.N),
+                                                                           row_addr(p.sdo, p.Hq, p.N)); count_launch();
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dk_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
     if ((e = cudaMemsetAsync(p.dv_acc, 0, kv_elems * sizeof(float), s)) != cudaSuccess) return (int)e;
     if (int r = p.use_mma ? launch_gqa_bwd_mma(p, Elem<T>::kDtype, s) : dispatch_gd<T>(p, s, true)) return r;
-    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dk_acc, (T*)p.dk, kv_elems); count_launch();
-    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dv_acc, (T*)p.dv, kv_elems); count_launch();
+    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dk_acc, (T*)p.dk, kv_elems, p.D, row_addr(p.sdk, p.Hkv, p.N)); count_launch();
+    gqa_finalize_kernel<T><<<(unsigned)((kv_elems + 255) / 256), 256, 0, s>>>(p.dv_acc, (T*)p.dv, kv_elems, p.D, row_addr(p.sdv, p.Hkv, p.N)); count_launch();
     return (int)cudaGetLastError();
 }
 

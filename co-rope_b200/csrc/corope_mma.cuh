@@ -54,6 +54,30 @@ __device__ __forceinline__ void sincos_fast(float x, float* s, float* c) {
     }
 }
 
+// m16n8k16 with all four A registers, both B registers and all four accumulators in use
+__device__ __forceinline__ void mma16816_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// transpose of an 8x8 matrix of 16-bit values held one register per lane (row = lane / 4, columns 2 (lane % 4), +1)
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// One (k1, k2) pair of a key as packed fp16, rotated by `angle`: (K'1, K'2) = (k1 cos + k2 sin, k2 cos - k1 sin), in packed
+// fp16 arithmetic: k1 (c, -s) + k2 (s, c), the broadcasts of k1 / k2 being operand selectors of the packed instructions.
+template <bool DIRECT>
+__device__ __forceinline__ uint32_t rotate_pair(uint32_t kpair, float angle) {
+    float sn, cs;
+    sincos_fast<DIRECT>(angle, &sn, &cs);
+    const __half2 kk = *reinterpret_cast<const __half2*>(&kpair);
+    const __half2 rr = __hfma2(__low2half2(kk), __floats2half2_rn(cs, -sn), __hmul2(__high2half2(kk), __floats2half2_rn(sn, cs)));
+    return *reinterpret_cast<const uint32_t*>(&rr);
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t to_half2(T a, T b) {
     return pack_half2(Elem<T>::to_f32(a), Elem<T>::to_f32(b));
@@ -64,13 +88,13 @@ __device__ __forceinline__ uint32_t to_half2(T a, T b) {
 // every tile once per 8 query rows.
 template <typename T>
 __global__ void __launch_bounds__(256) gqa_pack_kv_kernel(const T* __restrict__ K, const T* __restrict__ V, uint32_t* __restrict__ kp,
-                                                          __half* __restrict__ vh, size_t rows) {
+                                                          __half* __restrict__ vh, size_t rows, RowAddr ak, RowAddr av) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16: 8 K chunks + 8 V double-chunks
     if (idx >= rows * 16) return;
     const size_t r = idx >> 4;
     const int ch = (int)(idx & 15);
     if (ch < 8) {
-        const T* src = K + r * kD + ch * 8;
+        const T* src = K + flat_row_offset(ak, r) + ch * 8;
         const uint4 x1 = *reinterpret_cast<const uint4*>(src);
         const uint4 x2 = *reinterpret_cast<const uint4*>(src + kPairs);
         const uint32_t a[4] = {x1.x, x1.y, x1.z, x1.w}, bb[4] = {x2.x, x2.y, x2.z, x2.w};
@@ -84,7 +108,7 @@ __global__ void __launch_bounds__(256) gqa_pack_kv_kernel(const T* __restrict__ 
         const int c2 = ch - 8;   // 16 elements of V
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            uint4 x = *reinterpret_cast<const uint4*>(V + r * kD + c2 * 16 + u * 8);
+            uint4 x = *reinterpret_cast<const uint4*>(V + flat_row_offset(av, r) + c2 * 16 + u * 8);
             if (Elem<T>::kDtype == COROPE_DTYPE_BF16) {
                 uint32_t w4[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll

@@ -16,26 +16,6 @@
 namespace corope {
 namespace {
 
-// Addressing of flat row index `row` (= (b * H + h) * N + n) of a strided [B, H, N, D] tensor in the elementwise kernels.  The
-// host decides once whether the rows are evenly spaced (every contiguous tensor): then the offset is one multiply; the general
-// form costs two integer divisions per thread, which these memory-bound kernels (a few 16-byte accesses per thread) would feel.
-struct RowAddr {
-    Strides st;
-    int H, N;
-    int flat;
-};
-inline RowAddr row_addr(const Strides& st, int H, int N) {
-    RowAddr a;
-    a.st = st; a.H = H; a.N = N;
-    a.flat = rows_collapse(st, H, N) ? 1 : 0;
-    return a;
-}
-__device__ __forceinline__ int64_t flat_row_offset(const RowAddr& a, size_t row) {
-    if (a.flat) return (int64_t)row * a.st.n;
-    const unsigned r = (unsigned)row, bh = r / (unsigned)a.N;   // row counts stay below 2^31 (checked at the entry points)
-    return row_offset(a.st, a.H, (int)bh, (int)(r - bh * (unsigned)a.N));
-}
-
 constexpr int kRows = 32;     // rows per CTA
 constexpr int kTile = 32;     // streamed rows per step
 constexpr int kThreads = 128;

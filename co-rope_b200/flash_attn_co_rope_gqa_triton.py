@@ -43,17 +43,18 @@ def _forward(q, k, v, causal, sm_scale, theta):
         raise ValueError("q, k, v must share one dtype out of float32, bfloat16, float16.")
     for t in (q, k, v):
         _ext.require_cuda(t)
-    qc, kc, vc = q.contiguous(), k.contiguous(), v.contiguous()
+    qc, kc, vc = _ext.kernel_layout(q), _ext.kernel_layout(k), _ext.kernel_layout(v)   # own strides, no copies
     o = torch.empty_like(qc)
     lse2 = torch.empty((BATCH, H_Q, N_CTX), device=q.device, dtype=torch.float32)
     a_diag = torch.empty((BATCH, H_KV, N_CTX), device=q.device, dtype=torch.float32)
     ws, ws_bytes = _ext.workspace(_ext.OP_GQA_FWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    st = _ext.strides_of(q=qc, k=kc, v=vc, o=o)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_gqa_fwd(
+        rc = _ext.lib().corope_gqa_fwd_strided(
             qc.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), lse2.data_ptr(), a_diag.data_ptr(),
             BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
-            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_gqa_fwd")
     _ext.post_call(q.device)
     return qc, kc, vc, o, lse2, a_diag
@@ -61,20 +62,21 @@ def _forward(q, k, v, causal, sm_scale, theta):
 
 def _backward(q, k, v, o, lse2, a_diag, grad_output, sm_scale, theta):
     """One corope_gqa_bwd call on what _forward returned.  Returns (dq, dk, dv); dk / dv are summed over each group."""
-    grad_output = grad_output.contiguous()
+    grad_output = _ext.kernel_layout(grad_output)
     BATCH, H_Q, N_CTX, HEAD_DIM = q.shape
     H_KV = k.shape[1]
     dq = torch.empty_like(q)
     dk = torch.empty_like(k)
     dv = torch.empty_like(v)
     ws, ws_bytes = _ext.workspace(_ext.OP_GQA_BWD, BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, q.dtype, q.device)
+    st = _ext.strides_of(q=q, k=k, v=v, o=o, d_o=grad_output, dq=dq, dk=dk, dv=dv)
     _ext.pre_call(q.device)
     with torch.cuda.device(q.device):
-        rc = _ext.lib().corope_gqa_bwd(
+        rc = _ext.lib().corope_gqa_bwd_strided(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), grad_output.data_ptr(), lse2.data_ptr(),
             a_diag.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
             BATCH, H_Q, H_KV, N_CTX, HEAD_DIM, _ext.DTYPE_CODES[q.dtype], float(sm_scale), float(theta),
-            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device))
+            ws.data_ptr(), ws_bytes, _ext.status_word(q.device).data_ptr(), _ext.stream_ptr(q.device), st)
     _ext.raise_for_status(rc, "corope_gqa_bwd")
     _ext.post_call(q.device)
     return dq, dk, dv

@@ -230,6 +230,15 @@ int corope_gqa_fwd(const void* q, const void* k, const void* v,
                    void* workspace, size_t workspace_bytes,
                    int* status_word, void* stream);
 
+/* corope_gqa_fwd with every tensor's own {batch, head, row} strides (the q, k, v, o fields of `strides`, in elements; NULL =
+ * contiguous).  Replaces the stride arguments of the reference's kernel launch (flash_attn_co_rope_gqa_triton.py:439-442).
+ * The tensor-core kernels run when all pointers and strides are multiples of 16 bytes, the CUDA-core kernels otherwise. */
+int corope_gqa_fwd_strided(const void* q, const void* k, const void* v,
+                           void* o, float* lse2, float* a_diag,
+                           int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
+                           void* workspace, size_t workspace_bytes,
+                           int* status_word, void* stream, const corope_strides_t* strides);
+
 /*
  * Co-RoPE GQA attention backward.  Replaces _attention.backward
  * (corope-exp/flash_attn_co_rope_gqa_triton.py:459-577, dense PyTorch there); the math is that of
@@ -241,6 +250,14 @@ int corope_gqa_bwd(const void* q, const void* k, const void* v, const void* o, c
                    int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
                    void* workspace, size_t workspace_bytes,
                    int* status_word, void* stream);
+
+/* corope_gqa_bwd with every tensor's own strides (all eight fields of `strides`; NULL = contiguous). */
+int corope_gqa_bwd_strided(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                           const float* lse2, const float* a_diag,
+                           void* dq, void* dk, void* dv,
+                           int B, int Hq, int Hkv, int N, int D, int dtype, float sm_scale, float theta,
+                           void* workspace, size_t workspace_bytes,
+                           int* status_word, void* stream, const corope_strides_t* strides);
 
 #ifdef __cplusplus
 }

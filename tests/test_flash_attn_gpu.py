@@ -233,6 +233,51 @@ def test_flash_attention_strided_gqa_views():
         check16(_label() + " " + name, got.float().cpu(), ref, TOL_BWD_16, torch.bfloat16)
 
 
+@pytest.mark.parametrize("dtype,cfg", [(torch.bfloat16, (2, 8, 2, 256, 128)), (torch.float16, (1, 3, 1, 192, 128)),
+                                       (torch.float32, (1, 4, 2, 100, 64)), (torch.bfloat16, (1, 2, 1, 96, 64))])
+@pytest.mark.parametrize("layout", ["bnhd", "padded8", "padded2"])
+def test_corope_strided_views_need_no_copies(dtype, cfg, layout):
+    # Co-RoPE through its drop-in entry point on transposed and row-padded views: the results of contiguous tensors, the
+    # same kernel family and launch count (no copy kernels), outputs laid out like the inputs.  A K / V row stride that
+    # is not a multiple of 16 bytes ("padded2" in 16 bits) keeps D = 128 off the tensor-core kernels, whose pre-pass
+    # reads 16-byte vectors.
+    from helpers import corope_attention
+    B, Hq, Hkv, N, D = cfg
+    q, do = (draw((B, Hq, N, D), 120 + i, dtype).cuda() for i in range(2))
+    k, v = (draw((B, Hkv, N, D), 122 + i, dtype).cuda() for i in range(2))
+    view = {"bnhd": _as_bnhd_view, "padded8": lambda t: _padded_rows_view(t, 8), "padded2": lambda t: _padded_rows_view(t, 2)}[layout]
+
+    def run(make):
+        qq, kk, vv = (make(t).detach().requires_grad_(True) for t in (q, k, v))
+        n0 = ext.lib().corope_launch_count()
+        o = corope_attention(qq, kk, vv, True, D ** -0.5, 10000.0)
+        o.backward(make(do))
+        ext.check_status()
+        fam = (ext.lib().corope_last_kernel_family(ext.OP_GQA_FWD), ext.lib().corope_last_kernel_family(ext.OP_GQA_BWD))
+        return (o, qq.grad, kk.grad, vv.grad), (qq, kk, vv), ext.lib().corope_launch_count() - n0, fam
+
+    ref, _, launches_contig, fam_contig = run(lambda t: t.clone())
+    got, (qq, kk, vv), launches, fam = run(view)
+    assert not qq.is_contiguous()
+    assert got[0].stride() == torch.empty_like(qq).stride() and got[2].stride() == torch.empty_like(kk).stride()
+    if layout == "bnhd":
+        assert got[0].stride() == qq.stride() and not got[0].is_contiguous()
+    tolf, tolb = (1e-4, 1e-3) if dtype == torch.float32 else (TOL_FWD_16, TOL_BWD_16)
+    if dtype == torch.float32 or D != 128 or layout != "padded2":
+        assert fam == fam_contig and launches == launches_contig
+        assert torch.equal(got[0], ref[0])
+        for a, b in zip(got[1:], ref[1:]):      # dK / dV are summed with atomics: order varies from run to run
+            assert maxdiff(a, b) <= tolb
+    else:
+        assert fam_contig == (1, 1) and fam == (0, 0)
+        for a, b, tol in zip(got, ref, (tolf, tolb, tolb, tolb)):
+            assert maxdiff(a, b) <= 2 * tol
+    # and against the oracle on the same values
+    qc, kc, vc, dc = (t.float().cpu() for t in (q, k, v, do))
+    ro = oracle.corope_gqa_fwd(qc, kc, vc, True, D ** -0.5, 10000.0)
+    assert maxdiff(got[0].float().cpu(), ro) <= (tolf if dtype == torch.float32 else 2 * tolf)
+
+
 def test_strided_entry_point_rejects_bad_strides():
     lib = ext.lib()
     t = torch.zeros(1, 1, 128, 128, device="cuda", dtype=torch.bfloat16)
@@ -243,3 +288,8 @@ def test_strided_entry_point_rejects_bad_strides():
     rc = lib.corope_rope_attn_fwd_strided(t.data_ptr(), t.data_ptr(), t.data_ptr(), f.data_ptr(), f.data_ptr(), 64, t.data_ptr(), f.data_ptr(),
                                           1, 1, 128, 128, 1, 1, 0.1, ws.data_ptr(), nbytes, None, None, st)
     assert rc == -11 and b"stride" in lib.corope_status_string(rc)
+    ws, nbytes = ext.workspace(ext.OP_GQA_FWD, 1, 1, 1, 128, 128, torch.bfloat16, t.device)
+    g = torch.zeros(128, device="cuda")
+    rc = lib.corope_gqa_fwd_strided(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), g.data_ptr(), g.data_ptr(), 1, 1, 1, 128, 128, 1,
+                                    0.1, 10000.0, ws.data_ptr(), nbytes, None, None, st)
+    assert rc == -11
