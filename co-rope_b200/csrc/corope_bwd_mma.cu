@@ -11,11 +11,16 @@
 //     gD_ij   = - sum_h g_hij sum_p w_p (q2 K'1 - q1 K'2)           (mileage gradient)
 //     gz_ik   = sum_{j<k} gD_ij   graw_ik = gz_ik z_ik (1 - z_ik) s    dqL_i += sum_k graw_ik k_k    dk_k += sum_i graw_ik qL_i
 // One CTA = 8 consecutive query rows of one (batch, KV head), one warp per row, key tiles of 64 swept upward (gz is a
-// prefix sum in j).  Per block of 8 keys a warp runs, with lane = (key or head: lane / 4, c = lane % 4):
-//   K' for the lane's 16 pairs (B operand)            -> S (A = q pairs) and the mileage term (A = w (q2, -q1))
-//   dO.V (A = dO of the row, B = V via ldmatrix)      -> P, g, gD (summed over heads with shuffles, kept per key)
-//   u = g^T q (A = g transposed with movmatrix)       -> inverse rotation on the CUDA cores, added to a shared dK tile
-//   dq += g K'^T (B = movmatrix of the K' registers): accumulators in registers for the whole row
+// prefix sum in j).  The per-row products are transposed: the 16 keys of a block are the rows of the A operand (all in use),
+// the group's heads the 8 columns; lane (r = lane / 4, c = lane % 4) owns keys r, r + 8 on the operand side and heads 2c,
+// 2c + 1 on the result side.  Per block of 16 keys a warp runs
+//   K' for the 16 pairs of its two keys (A operand)     -> S^T (B = q pairs of head r) and the mileage term (B = w (q2, -q1))
+//   (dO.V)^T (A = V via ldmatrix, B = dO of head r)     -> P, g, gD (summed over heads with shuffles, kept per key)
+//   u = g^T q, one m16n8k8 per pair slot (K = 8 heads; g's result registers are its A operand as they stand)
+//                                                       -> inverse rotation on the CUDA cores, added to a shared dK tile
+//   dq^T += K'^T g^T (A = movmatrix of the K' registers, B = movmatrix of g): accumulators in registers for the whole row
+// (A first version had the heads as the rows of A: half of every operand quad was zero padding rebuilt in registers per MMA
+// and the MMA count was 2.3 times higher: 52 instead of 37 instructions per (query, key, pair).)
 // Once per tile: each warp turns its row of gD into gz (prefix over the keys) and graw; then, summed over the CTA's rows
 // by the tensor cores, dV (K dimension = (row, head)), the leader terms dk += graw^T qL and dqL += graw k (K dimension
 // = row / key); dV and the shared dK tile go to the fp32 global accumulators with vector reductions.
@@ -34,19 +39,22 @@ constexpr int kDkStride = 132;                  // words per row of the shared d
 // The shared dK tile is summed in 32-bit fixed point (2^-14 units): integer shared-memory atomics are single
 // instructions, fp32 ones are compare-and-swap loops, and the sum no longer depends on the order of the warps.  The
 // rounding error of one contribution, 3e-5, is far below the 16-bit output resolution.
-// Fast form: x * 2^14 + 1.5 * 2^23 holds round(x * 2^14) in its low mantissa bits -- valid for |x| < 256 only.  Per block
-// of 8 keys a warp therefore bounds its contributions (|x| <= sqrt(2) G max|g| max|q_row|, one vote instruction) and takes
-// the range-safe form when the bound is not below 256: a real float -> int conversion of x clamped to +-4096 (the tile sum
-// of 9 such terms still fits 32 bits).  A contribution that had to be clamped is reported in the status word
+// Fast form: a float in [512, 1024) has a last-place unit of 2^-14, so 768 + x, for |x| < 256, holds round(x 2^14) in its
+// low mantissa bits: its bit pattern is kDkBias + round(x 2^14).  The 768 is the addend of the inverse rotation's last
+// multiply-add, the raw bit pattern goes to the atomic, and the bias is taken off when the tile is flushed: every (row, 16-key
+// block) that is not skipped adds exactly once to each of the block's slots, so a slot holds count x kDkBias too much.
+// Per block a warp bounds its contributions (|x| <= sqrt(2) G max|g| max|q_row|, one vote instruction) and takes the
+// range-safe form when the bound is not below 256: a real float -> int conversion of x clamped to +-4096 (the tile sum
+// of 9 such terms still fits 32 bits), plus the bias.  A contribution that had to be clamped is reported in the status word
 // (COROPE_DEV_RANGE): the result is then inaccurate, never wrapped around.
-constexpr float kDkScale = 16384.f, kDkMagic = 12582912.f, kDkFastLimit = 250.f, kDkClamp = 4096.f;
-__device__ __forceinline__ void dk_add(int* slot, float x) {
-    atomicAdd(slot, __float_as_int(fmaf(x, kDkScale, kDkMagic)) - 0x4B400000);
-}
-__device__ __forceinline__ void dk_add_safe(int* slot, float x, bool& clamped) {
+constexpr float kDkScale = 16384.f, kDkMagic = 768.f, kDkFastLimit = 250.f, kDkClamp = 4096.f;
+constexpr int kDkBias = 0x44400000;   // bit pattern of 768.f
+// x_plus_magic = kDkMagic + x, computed by the caller's last multiply-add
+__device__ __forceinline__ void dk_add_biased(int* slot, float x_plus_magic) { atomicAdd(slot, __float_as_int(x_plus_magic)); }
+__device__ __forceinline__ void dk_add_safe(int* slot, float x, bool& clamped, int bias = 0) {
     const float xc = fminf(fmaxf(x, -kDkClamp), kDkClamp);
     clamped |= xc != x;
-    atomicAdd(slot, __float2int_rn(xc * kDkScale));
+    atomicAdd(slot, __float2int_rn(xc * kDkScale) + bias);
 }
 constexpr int kGrRowBytes = 144;                // rows of the leader-term operand graw (64 keys fp16 + padding)
 constexpr size_t kSmemBytes = 2 * (kKTileBytes + kVTileBytes) + kRows * kPairs * 4 + 2 * kRows * kKT * 4 + 4 * kWStride * 4 + 4 * kTabBytes +
@@ -184,7 +192,6 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         aq[4 * s] = a.x; aq[4 * s + 1] = a.y; aq[4 * s + 2] = a.z; aq[4 * s + 3] = a.w;
         aw[4 * s] = w4.x; aw[4 * s + 1] = w4.y; aw[4 * s + 2] = w4.z; aw[4 * s + 3] = w4.w;
     }
-    const bool valid = h < G;
     // largest |g| for which every dK contribution of a block stays inside the fast fixed-point form (see dk_add)
     float g_fast_limit;
     {
@@ -199,13 +206,24 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         g_fast_limit = kDkFastLimit / (1.4143f * (float)G * fmaxf(qmax, 1e-20f));
     }
     bool range_clamped = false;
-    const float lse = valid ? p.lse2[(q_head0 + h) * N + i] : 0.f;
-    const float dlt = valid ? p.delta[(q_head0 + h) * N + i] : 0.f;
+    // From here on the per-row MMAs are "transposed": the 16 keys of a block are the rows of the A operand (all in use), the
+    // group's heads the 8 columns.  Lane (r = lane / 4, c = lane % 4): keys r and r + 8 on the operand side, heads 2c and
+    // 2c + 1 on the result side.  The per-head operands above (head = lane / 4) are the B operands as they stand.
+    const int r = h;
+    float lse[2], dlt[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        const bool ok = 2 * c + x < G;
+        lse[x] = ok ? p.lse2[(q_head0 + 2 * c + x) * N + i] : 0.f;
+        dlt[x] = ok ? p.delta[(q_head0 + 2 * c + x) * N + i] : 0.f;
+    }
     const float a_ii = p.a_diag[(size_t)bg * N + i];
     const float sc2 = p.sm_scale * kLog2e;
-    float dq[16][2];
+    // dq^T: [xb] rows = (pair class r / 2, component r % 2) of slots 2 xb (entries 0, 1) and 2 xb + 1 (entries 2, 3),
+    // columns = heads 2c, 2c + 1
+    float dq[8][4];
 #pragma unroll
-    for (int x = 0; x < 16; ++x) dq[x][0] = dq[x][1] = 0.f;
+    for (int x = 0; x < 8; ++x) dq[x][0] = dq[x][1] = dq[x][2] = dq[x][3] = 0.f;
     float carry_a = 0.f, carry_g = 0.f;
     float dql[2][4];   // leader-term dq of the CTA's 8 rows, operand-order columns 16 warp .. 16 warp + 15 (summed into dq at the end)
 #pragma unroll
@@ -252,75 +270,82 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
         }
         __syncwarp();
 
-        // 3. blocks of 8 keys
+        // 3. blocks of 16 keys
 #pragma unroll 1
-        for (int nb = 0; nb < 8; ++nb) {
-            uint32_t* ps_out = reinterpret_cast<uint32_t*>(ps + (warp * G + h) * kPsRowBytes + (nb * 8 + 2 * c) * 2);
-            float* gd_out = gds + warp * kKT + nb * 8 + 2 * c;
-            if (j0 + nb * 8 > i) {   // every key of the block is above the diagonal (warp-uniform)
-                if (valid) *ps_out = 0u;
-                if (h == 0) gd_out[0] = gd_out[1] = 0.f;
+        for (int kb = 0; kb < 4; ++kb) {
+            // P^T of the row for the dV product: [(row, head)][key]; the lane writes head r, keys 2c, 2c + 1 (and + 8)
+            uint32_t* ps_out = reinterpret_cast<uint32_t*>(ps + (warp * G + r) * kPsRowBytes + (kb * 16 + 2 * c) * 2);
+            float* gd_out = gds + warp * kKT + kb * 16 + r;
+            if (j0 + kb * 16 > i) {   // every key of the block is above the diagonal (warp-uniform)
+                if (r < G) ps_out[0] = 0u, ps_out[4] = 0u;
+                if (c == 0) gd_out[0] = gd_out[8] = 0.f;
                 continue;
             }
-            const float delta = dl[warp * kKT + nb * 8 + h];
-            const uint4* kp = reinterpret_cast<const uint4*>(ks + (nb * 8 + h) * kKRow) + c;
-            uint32_t kpr[16], csr[16];
+            const float dA = dl[warp * kKT + kb * 16 + r], dB = dl[warp * kKT + kb * 16 + r + 8];
+            const uint4* kpA = reinterpret_cast<const uint4*>(ks + (kb * 16 + r) * kKRow) + c;
+            const uint4* kpB = reinterpret_cast<const uint4*>(ks + (kb * 16 + r + 8) * kKRow) + c;
+            uint32_t kprA[16], kprB[16], csrA[16], csrB[16];   // rotated pairs (A-operand registers) and packed (cos, sin)
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
-                const uint4 kv = kp[4 * s];
+                const uint4 kva = kpA[4 * s], kvb = kpB[4 * s];
                 const float4 wv = *reinterpret_cast<const float4*>(ws + c * kWStride + s * 4);
-                const uint32_t kw[4] = {kv.x, kv.y, kv.z, kv.w};
+                const uint32_t kwa[4] = {kva.x, kva.y, kva.z, kva.w}, kwb[4] = {kvb.x, kvb.y, kvb.z, kvb.w};
                 const float wq[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float sn, cs;
-                    sincos_fast<DIRECT>(delta * wq[e], &sn, &cs);
-                    const __half2 kk = *reinterpret_cast<const __half2*>(&kw[e]);
-                    const uint32_t sw = __byte_perm(kw[e], 0, 0x1032);
-                    const __half2 ksw = *reinterpret_cast<const __half2*>(&sw);
-                    const __half2 r = __hfma2(kk, __floats2half2_rn(cs, cs), __hmul2(ksw, __floats2half2_rn(sn, -sn)));
-                    kpr[s * 4 + e] = *reinterpret_cast<const uint32_t*>(&r);
-                    csr[s * 4 + e] = pack_half2(cs, sn);
+                    kprA[s * 4 + e] = rotate_pair<DIRECT>(kwa[e], dA * wq[e], &csrA[s * 4 + e]);
+                    kprB[s * 4 + e] = rotate_pair<DIRECT>(kwb[e], dB * wq[e], &csrB[s * 4 + e]);
                 }
             }
-            // S, the mileage term and dO.V
-            float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f, m0 = 0.f, m1 = 0.f, n0 = 0.f, n1 = 0.f, dp0 = 0.f, dp1 = 0.f, e0 = 0.f, e1 = 0.f;
+            // S^T, the mileage term and (dO.V)^T: rows = keys r (entries 0, 1) and r + 8 (entries 2, 3), columns = heads 2c, 2c + 1
+            float sE[4] = {0.f, 0.f, 0.f, 0.f}, sO[4] = {0.f, 0.f, 0.f, 0.f}, mE[4] = {0.f, 0.f, 0.f, 0.f}, mO[4] = {0.f, 0.f, 0.f, 0.f};
+            float pE[4] = {0.f, 0.f, 0.f, 0.f}, pO[4] = {0.f, 0.f, 0.f, 0.f};
+            const uint8_t* vrow = vs + (kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * kVRowBytes + ((lane >> 4) & 1) * 16;
 #pragma unroll
             for (int s = 0; s < 4; ++s) {
+                const uint32_t a_even[4] = {kprA[4 * s], kprB[4 * s], kprA[4 * s + 1], kprB[4 * s + 1]};
+                const uint32_t a_odd[4] = {kprA[4 * s + 2], kprB[4 * s + 2], kprA[4 * s + 3], kprB[4 * s + 3]};
+                mma16816_full(sE, a_even, aq[4 * s], aq[4 * s + 1]);
+                mma16816_full(sO, a_odd, aq[4 * s + 2], aq[4 * s + 3]);
+                mma16816_full(mE, a_even, aw[4 * s], aw[4 * s + 1]);
+                mma16816_full(mO, a_odd, aw[4 * s + 2], aw[4 * s + 3]);
                 const uint4 ad = ados[s * 32 + lane];
-                mma16816(s0, s1, aq[4 * s], aq[4 * s + 1], kpr[4 * s], kpr[4 * s + 1], s0, s1);
-                mma16816(t0, t1, aq[4 * s + 2], aq[4 * s + 3], kpr[4 * s + 2], kpr[4 * s + 3], t0, t1);
-                mma16816(m0, m1, aw[4 * s], aw[4 * s + 1], kpr[4 * s], kpr[4 * s + 1], m0, m1);
-                mma16816(n0, n1, aw[4 * s + 2], aw[4 * s + 3], kpr[4 * s + 2], kpr[4 * s + 3], n0, n1);
-                uint32_t r0, r1, r2, r3;   // V[key][d]: k-steps 2s and 2s+1 (16 d each)
-                ldmatrix_x4(r0, r1, r2, r3, vs + (nb * 8 + (lane & 7)) * kVRowBytes + s * 64 + (lane >> 3) * 16);
-                mma16816(dp0, dp1, ad.x, ad.y, r0, r1, dp0, dp1);
-                mma16816(e0, e1, ad.z, ad.w, r2, r3, e0, e1);
+                uint32_t v[4];   // V[key][d] of the block, d = 32 s .. 32 s + 15, then + 16
+                ldmatrix_x4(v[0], v[1], v[2], v[3], vrow + s * 64);
+                mma16816_full(pE, v, ad.x, ad.y);
+                ldmatrix_x4(v[0], v[1], v[2], v[3], vrow + s * 64 + 32);
+                mma16816_full(pO, v, ad.z, ad.w);
             }
-            // P, g, gD (rows = heads, columns = keys 2c, 2c+1 of the block)
-            const int key = j0 + nb * 8 + 2 * c;
-            const bool vis0 = valid && key <= i, vis1 = valid && key + 1 <= i;
-            const float p0 = vis0 ? fast_exp2((s0 + t0) * sc2 - lse) : 0.f;
-            const float p1 = vis1 ? fast_exp2((s1 + t1) * sc2 - lse) : 0.f;
-            const float g0 = p0 * (dp0 + e0 - dlt) * p.sm_scale, g1 = p1 * (dp1 + e1 - dlt) * p.sm_scale;
-            if (valid) *ps_out = pack_half2(p0, p1);
-            const uint32_t gp = pack_half2_sat(g0, g1);
-            const float g_abs = fmaxf(fabsf(g0), fabsf(g1));
-            const bool big = __any_sync(0xffffffffu, g_abs > g_fast_limit);   // warp-uniform: some contribution may leave the fast range
-            float gd0 = -g0 * (m0 + n0), gd1 = -g1 * (m1 + n1);
+            // P, g, gD
+            const int keyA = j0 + kb * 16 + r;
+            float pv[4], gv[4];
 #pragma unroll
-            for (int off = 4; off < 32; off <<= 1) {   // sum over the heads
-                gd0 += __shfl_xor_sync(0xffffffffu, gd0, off);
-                gd1 += __shfl_xor_sync(0xffffffffu, gd1, off);
+            for (int x = 0; x < 4; ++x) {
+                const bool vis = 2 * c + (x & 1) < G && keyA + (x >> 1) * 8 <= i;
+                pv[x] = vis ? fast_exp2((sE[x] + sO[x]) * sc2 - lse[x & 1]) : 0.f;
+                gv[x] = pv[x] * (pE[x] + pO[x] - dlt[x & 1]) * p.sm_scale;
             }
-            if (h == 0) {   // the mileage-gradient chain (prefix over the keys, leader terms) runs once per tile, below
-                gd_out[0] = gd0;
-                gd_out[1] = gd1;
+            // transposed copies: (head r | keys 2c, 2c + 1) of the first and second 8 keys
+            const uint32_t paT = movmatrix_trans(pack_half2(pv[0], pv[1])), pbT = movmatrix_trans(pack_half2(pv[2], pv[3]));
+            if (r < G) ps_out[0] = paT, ps_out[4] = pbT;
+            const uint32_t ga = pack_half2_sat(gv[0], gv[1]), gb = pack_half2_sat(gv[2], gv[3]);
+            const float g_abs = fmaxf(fmaxf(fabsf(gv[0]), fabsf(gv[1])), fmaxf(fabsf(gv[2]), fabsf(gv[3])));
+            const bool big = __any_sync(0xffffffffu, g_abs > g_fast_limit);   // warp-uniform: some contribution may leave the fast range
+            float gdA = -(gv[0] * (mE[0] + mO[0]) + gv[1] * (mE[1] + mO[1]));
+            float gdB = -(gv[2] * (mE[2] + mO[2]) + gv[3] * (mE[3] + mO[3]));
+#pragma unroll
+            for (int off = 1; off < 4; off <<= 1) {   // sum over the heads
+                gdA += __shfl_xor_sync(0xffffffffu, gdA, off);
+                gdB += __shfl_xor_sync(0xffffffffu, gdB, off);
+            }
+            if (c == 0) {   // the mileage-gradient chain (prefix over the keys, leader terms) runs once per tile, below
+                gd_out[0] = gdA;
+                gd_out[8] = gdB;
             }
 
-            // u = g^T q per pair, inverse rotation, into the shared dK tile
-            const uint32_t gT = movmatrix_trans(gp);
-            int* dkrow = dk_t + (nb * 8 + h) * kDkStride;
+            // u = g^T q per pair (one m16n8k8 per pair slot: K dimension = the 8 heads), inverse rotation, into the shared dK tile
+            int* dkA = dk_t + (kb * 16 + r) * kDkStride;
+            int* dkB = dkA + 8 * kDkStride;
             if (!big) {
 #pragma unroll
                 for (int s = 0; s < 4; ++s) {
@@ -328,12 +353,14 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                     const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        float u1 = 0.f, u2 = 0.f;
-                        mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
-                        const float2 cs = unpack_half2(csr[s * 4 + e]);
+                        float u[4];
+                        mma1688(u, ga, gb, bq[e]);
+                        const float2 ca = unpack_half2(csrA[s * 4 + e]), cb = unpack_half2(csrB[s * 4 + e]);
                         const int pp = lane_pair(c, s, e);
-                        dk_add(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y));
-                        dk_add(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y));
+                        dk_add_biased(dkA + pp, fmaf(u[0], ca.x, fmaf(-u[1], ca.y, kDkMagic)));
+                        dk_add_biased(dkA + pp + kPairs, fmaf(u[1], ca.x, fmaf(u[0], ca.y, kDkMagic)));
+                        dk_add_biased(dkB + pp, fmaf(u[2], cb.x, fmaf(-u[3], cb.y, kDkMagic)));
+                        dk_add_biased(dkB + pp + kPairs, fmaf(u[3], cb.x, fmaf(u[2], cb.y, kDkMagic)));
                     }
                 }
             } else {
@@ -344,18 +371,26 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
                     const uint32_t bq[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        float u1 = 0.f, u2 = 0.f;
-                        mma16816(u1, u2, gT, 0u, bq[e], 0u, 0.f, 0.f);
-                        const float2 cs = unpack_half2(csr[s * 4 + e]);
+                        float u[4];
+                        mma1688(u, ga, gb, bq[e]);
+                        const float2 ca = unpack_half2(csrA[s * 4 + e]), cb = unpack_half2(csrB[s * 4 + e]);
                         const int pp = lane_pair(c, s, e);
-                        dk_add_safe(dkrow + pp, fmaf(u1, cs.x, -u2 * cs.y), range_clamped);
-                        dk_add_safe(dkrow + pp + kPairs, fmaf(u2, cs.x, u1 * cs.y), range_clamped);
+                        dk_add_safe(dkA + pp, fmaf(u[0], ca.x, -u[1] * ca.y), range_clamped, kDkBias);
+                        dk_add_safe(dkA + pp + kPairs, fmaf(u[1], ca.x, u[0] * ca.y), range_clamped, kDkBias);
+                        dk_add_safe(dkB + pp, fmaf(u[2], cb.x, -u[3] * cb.y), range_clamped, kDkBias);
+                        dk_add_safe(dkB + pp + kPairs, fmaf(u[3], cb.x, u[2] * cb.y), range_clamped, kDkBias);
                     }
                 }
             }
-            // dq += g K'^T
+            // dq^T += K'^T g^T: A = the rotated pairs transposed in registers (rows = (pair class, component) of two slots,
+            // K dimension = the 16 keys), B = g transposed (keys | head r)
+            const uint32_t gaT = movmatrix_trans(ga), gbT = movmatrix_trans(gb);
 #pragma unroll
-            for (int x = 0; x < 16; ++x) mma16816(dq[x][0], dq[x][1], gp, 0u, movmatrix_trans(kpr[x]), 0u, dq[x][0], dq[x][1]);
+            for (int xb = 0; xb < 8; ++xb) {
+                const uint32_t a[4] = {movmatrix_trans(kprA[2 * xb]), movmatrix_trans(kprA[2 * xb + 1]), movmatrix_trans(kprB[2 * xb]),
+                                       movmatrix_trans(kprB[2 * xb + 1])};
+                mma16816_full(dq[xb], a, gaT, gbT);
+            }
         }
         // mileage-gradient chain of this row: gz_k = sum of gD over the keys before k, graw = gz z (1 - z) s
         {
@@ -445,7 +480,12 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             for (int idx = tid; idx < kKT * 64; idx += kThreads) {
                 const int r = idx >> 6, d2 = (idx & 63) * 2;
                 int* src = dk_t + r * kDkStride + d2;
-                if (j0 + r <= i_last) red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, (float)src[0] * (1.f / kDkScale), (float)src[1] * (1.f / kDkScale));
+                // rows of the CTA that did not skip this key's 16-key block: each left one bias in every slot of the block
+                const int cnt = min(kRows, max(0, i_last + 1 - (j0 + (r & ~15))));
+                const unsigned bias = (unsigned)cnt * (unsigned)kDkBias;   // modulo 2^32, like the sums themselves
+                if (j0 + r <= i_last)
+                    red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, (float)(int)((unsigned)src[0] - bias) * (1.f / kDkScale),
+                               (float)(int)((unsigned)src[1] - bias) * (1.f / kDkScale));
                 src[0] = 0;
                 src[1] = 0;
             }
@@ -462,27 +502,28 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             xs[h * kD + warp * 16 + n * 8 + 2 * c + 1] = dql[n][1];
         }
         __syncthreads();
-        if (h == 0) {
+        if (c == 0) {   // the lanes that hold head 0 (entries 0 and 2 of every dq^T block)
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
+            for (int xb = 0; xb < 8; ++xb)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int slot = perm_slot(lane_pair(c, s, e));
-                    dq[s * 4 + e][0] += xs[warp * kD + 2 * slot];
-                    dq[s * 4 + e][1] += xs[warp * kD + 2 * slot + 1];
+                for (int y = 0; y < 2; ++y) {
+                    const int x = 2 * xb + y;
+                    const int slot = perm_slot(lane_pair(r >> 1, x >> 2, x & 3));
+                    dq[xb][2 * y] += xs[warp * kD + 2 * slot + (r & 1)];
                 }
         }
     }
     if (__any_sync(0xffffffffu, range_clamped) && lane == 0 && p.status) atomicCAS(p.status, 0, COROPE_DEV_RANGE);
-    if (valid) {
-        T* DQ = reinterpret_cast<T*>(p.dq) + row_offset(p.sdq, p.Hq, (int)q_head0 + h, i);
 #pragma unroll
-        for (int s = 0; s < 4; ++s)
+    for (int x2 = 0; x2 < 2; ++x2) {
+        if (2 * c + x2 >= G) continue;
+        T* DQ = reinterpret_cast<T*>(p.dq) + row_offset(p.sdq, p.Hq, (int)q_head0 + 2 * c + x2, i) + (r & 1) * kPairs;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int pp = lane_pair(c, s, e);
-                DQ[pp] = Elem<T>::from_f32(dq[s * 4 + e][0]);
-                DQ[pp + kPairs] = Elem<T>::from_f32(dq[s * 4 + e][1]);
+        for (int xb = 0; xb < 8; ++xb)
+#pragma unroll
+            for (int y = 0; y < 2; ++y) {
+                const int x = 2 * xb + y;
+                DQ[lane_pair(r >> 1, x >> 2, x & 3)] = Elem<T>::from_f32(dq[xb][2 * y + x2]);
             }
     }
 }

@@ -78,6 +78,23 @@ __device__ __forceinline__ uint32_t rotate_pair(uint32_t kpair, float angle) {
     return *reinterpret_cast<const uint32_t*>(&rr);
 }
 
+// the same, and the packed (cos, sin) of the angle for the inverse rotation of the backward
+template <bool DIRECT>
+__device__ __forceinline__ uint32_t rotate_pair(uint32_t kpair, float angle, uint32_t* cos_sin) {
+    float sn, cs;
+    sincos_fast<DIRECT>(angle, &sn, &cs);
+    const __half2 kk = *reinterpret_cast<const __half2*>(&kpair);
+    const __half2 rr = __hfma2(__low2half2(kk), __floats2half2_rn(cs, -sn), __hmul2(__high2half2(kk), __floats2half2_rn(sn, cs)));
+    *cos_sin = pack_half2(cs, sn);
+    return *reinterpret_cast<const uint32_t*>(&rr);
+}
+// m16n8k8: 16 rows x 8 columns from a K dimension of 8, fresh accumulators
+__device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "f"(0.f));
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t to_half2(T a, T b) {
     return pack_half2(Elem<T>::to_f32(a), Elem<T>::to_f32(b));

@@ -269,13 +269,15 @@ def test_corope_strided_views_need_no_copies(dtype, cfg, layout):
         for a, b in zip(got[1:], ref[1:]):      # dK / dV are summed with atomics: order varies from run to run
             assert maxdiff(a, b) <= tolb
     else:
-        assert fam_contig == (1, 1) and fam == (0, 0)
-        for a, b, tol in zip(got, ref, (tolf, tolb, tolb, tolb)):
-            assert maxdiff(a, b) <= 2 * tol
+        assert fam_contig == (1, 1) and fam == (0, 0)   # the CUDA-core kernels: compared with the oracle below
     # and against the oracle on the same values
     qc, kc, vc, dc = (t.float().cpu() for t in (q, k, v, do))
-    ro = oracle.corope_gqa_fwd(qc, kc, vc, True, D ** -0.5, 10000.0)
-    assert maxdiff(got[0].float().cpu(), ro) <= (tolf if dtype == torch.float32 else 2 * tolf)
+    refs = (oracle.corope_gqa_fwd(qc, kc, vc, True, D ** -0.5, 10000.0),) + tuple(oracle.corope_gqa_bwd(qc, kc, vc, dc, True, D ** -0.5, 10000.0))
+    for name, a, b, tol in zip(("O", "dQ", "dK", "dV"), got, refs, (tolf, tolb, tolb, tolb)):
+        if dtype == torch.float32:
+            assert maxdiff(a.float().cpu(), b) <= tol, name
+        else:
+            check16(_label() + " " + name, a.float().cpu(), b, tol, dtype, strict=(name == "O"))
 
 
 def test_strided_entry_point_rejects_bad_strides():
