@@ -410,6 +410,7 @@ def main():
                     help="N > 1: strong = the workload's units are divided among the ranks; weak = every rank runs the whole workload")
     ap.add_argument("--ref-units", type=int, default=4, help="(batch, head) units per step of the CPU reference arm")
     ap.add_argument("--autograd", action="store_true", help="time the autograd entry points instead of the direct forward / backward helpers")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs of the forward and the backward")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-triton", action="store_true", help="skip the child process that times the reference's Triton kernels")
@@ -523,11 +524,39 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.tolist()
 
+    graph_note = "launched from Python every step"
     last = None
     for _ in range(args.warmup):
         last = step(dq_, dk_, dv_, ddo)   # held like in the timed loop, so that the allocator's pool has its final size before timing starts
     sync_all()
     pkg.check_status()
+
+    # ---------------------------------------------------------------- CUDA graphs of the step (one for the forward, one for the backward)
+    # The library's calls are stream-ordered and allocate nothing, so a step can be captured once and replayed: the host then
+    # spends a few microseconds per step instead of 0.1 ms, which is what a rank's share of a sharded problem needs once it
+    # takes less than that on the GPU.  Every replay launches every kernel of the step.
+    graph = None
+    if not args.no_graph and not args.autograd:
+        try:
+            torch.cuda.synchronize()
+            gf, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+            n0 = lib.corope_launch_count()
+            with pkg._ext.batched_status(dev):   # the status mirror is refreshed once, after the captures
+                with torch.cuda.graph(gf, capture_error_mode="relaxed"):
+                    g_saved = (rope_mod._forward(dq_, dk_, dv_, True, sm_scale, cos, sin) if kind == "rope"
+                               else gqa_mod._forward(dq_, dk_, dv_, True, sm_scale, THETA))
+                with torch.cuda.graph(gb, pool=gf.pool(), capture_error_mode="relaxed"):
+                    g_grads = (rope_mod._backward(*g_saved, ddo, True, sm_scale) if kind == "rope"
+                               else gqa_mod._backward(*g_saved, ddo, sm_scale, THETA))
+            per_step = lib.corope_launch_count() - n0
+            gf.replay(), gb.replay()
+            torch.cuda.synchronize()
+            pkg.check_status()
+            graph = {"fwd": gf, "bwd": gb, "launches_per_step": int(per_step)}
+        except Exception as e:   # stay on the plain loop and say so in the line
+            graph = None
+            graph_note = "no graph (%s: %s)" % (type(e).__name__, str(e)[:120])
+            torch.cuda.synchronize()
 
     # ---------------------------------------------------------------- the timed region: exactly `steps` steps
     launches0 = lib.corope_launch_count()
@@ -536,12 +565,21 @@ def main():
     sync_all()
     t_timed0 = time.time()
     e0.record()
-    for i in range(args.steps):
-        last = step(dq_, dk_, dv_, ddo, evs[i])
+    if graph:
+        for i in range(args.steps):
+            evs[i][0].record()
+            graph["fwd"].replay()
+            evs[i][1].record()
+            graph["bwd"].replay()
+            evs[i][2].record()
+        last = (g_saved[3], g_grads)
+    else:
+        for i in range(args.steps):
+            last = step(dq_, dk_, dv_, ddo, evs[i])
     e1.record()
     torch.cuda.synchronize()
     t_timed1 = time.time()
-    launches = lib.corope_launch_count() - launches0
+    launches = graph["launches_per_step"] * args.steps if graph else lib.corope_launch_count() - launches0
     total_ms = e0.elapsed_time(e1)
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
@@ -781,7 +819,9 @@ def main():
         "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": dt, "data": "synthetic",
         "config": {"workload": args.workload, "B": B, "Hq": Hq, "Hkv": Hkv, "N": N, "D": D, "causal": True, "sm_scale": sm_scale,
                    "theta": THETA, "units_total": units_total, "units_per_gpu": n_loc,
-                   "api": "autograd entry points" if args.autograd else "forward / backward helpers of the drop-in modules (C-ABI calls without torch.autograd)",
+                   "api": "autograd entry points" if args.autograd else
+                          ("forward / backward helpers of the drop-in modules (C-ABI calls without torch.autograd)" +
+                           (", captured once as two CUDA graphs and replayed every step" if graph else ", " + graph_note)),
                    "partition": ("(batch, KV head) units %d..%d of %d on rank 0; no data-path collective" % (lo, hi - 1, n_units)) if strong else "every rank runs all units",
                    "l2": "inputs+outputs per step (%.0f MB per GPU) %s the 126 MB L2" %
                    (8 * dq_.numel() * dq_.element_size() / 1e6, "exceed" if 8 * dq_.numel() * dq_.element_size() > 126e6 else "do NOT exceed")},
