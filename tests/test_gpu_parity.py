@@ -334,6 +334,53 @@ def test_host_pipeline_matches_direct_call():
         assert maxdiff(got, ref) < 2e-2
 
 
+@pytest.mark.parametrize("op", ["fused_rope", "corope"])
+def test_calls_capture_into_cuda_graphs(op):
+    # The library's calls are stream-ordered and allocate nothing: a forward + backward captured once as a CUDA graph and
+    # replayed on new input values must give what the eager calls give (O, dK, dV of the fused-RoPE op bit for bit).
+    import importlib
+    pkg = importlib.import_module("co-rope_b200")
+    rope_mod = importlib.import_module("co-rope_b200.fused_rope_attn")
+    gqa_mod = importlib.import_module("co-rope_b200.flash_attn_co_rope_gqa_triton")
+    B, Hq, Hkv, N, D = (2, 4, 4, 512, 128) if op == "fused_rope" else (1, 8, 2, 256, 128)
+    dev = torch.device("cuda")
+    sq, sk, sv, sdo = (torch.zeros(shape, dtype=torch.bfloat16, device=dev) for shape in
+                       ((B, Hq, N, D), (B, Hkv, N, D), (B, Hkv, N, D), (B, Hq, N, D)))
+    cos, sin = (t.cuda() for t in oracle.precompute_freqs_cis(D, N, 10000.0))
+
+    def fwd_bwd(q, k, v, do):
+        if op == "fused_rope":
+            saved = rope_mod._forward(q, k, v, True, D ** -0.5, cos, sin)
+            return (saved[3],) + tuple(rope_mod._backward(*saved, do, True, D ** -0.5))
+        saved = gqa_mod._forward(q, k, v, True, D ** -0.5, 10000.0)
+        return (saved[3],) + tuple(gqa_mod._backward(*saved, do, D ** -0.5, 10000.0))
+
+    fwd_bwd(sq, sk, sv, sdo)   # workspaces and lazy initialisation happen outside the capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with pkg._ext.batched_status(dev):
+        with torch.cuda.graph(g, capture_error_mode="relaxed"):
+            outs = fwd_bwd(sq, sk, sv, sdo)
+    for seed in (51, 52):
+        vals = [draw(t.shape, seed + 10 * i, torch.bfloat16).cuda() for i, t in enumerate((sq, sk, sv, sdo))]
+        for dst, src in zip((sq, sk, sv, sdo), vals):
+            dst.copy_(src)
+        g.replay()
+        torch.cuda.synchronize()
+        ext.check_status()
+        got = [t.clone() for t in outs]
+        ref = fwd_bwd(*vals)
+        torch.cuda.synchronize()
+        ext.check_status()
+        if op == "fused_rope":
+            assert torch.equal(got[0], ref[0]) and torch.equal(got[2], ref[2]) and torch.equal(got[3], ref[3])
+            assert maxdiff(got[1], ref[1]) < 1e-2
+        else:
+            assert torch.equal(got[0], ref[0])
+            for a, b in zip(got[1:], ref[1:]):
+                assert maxdiff(a, b) <= TOL_BWD_16
+
+
 def test_fused_rope_tensor_core_results_are_reproducible():
     # O, dK and dV are accumulated in a fixed order (TMEM accumulators), so repeated calls must agree bit for bit; a
     # difference means a race between the warp-specialised roles.  dQ is summed with floating-point reductions whose
