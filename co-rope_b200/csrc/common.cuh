@@ -102,6 +102,7 @@ struct RopeParams {
     float sm_scale;
     int* status;
     int* sched_counter; // zeroed word in the workspace: next work item / unit of the persistent tensor-core kernels
+    int head_chunk;     // heads per chunk of the persistent kernels' work order (set by their launchers)
     const void* k_rot;  // forward: [B,H,N,D] fp16, K already rotated by the pre-pass; null = the kernel rotates K tiles itself
     const void* q_rot;  // backward: [B,H,N,D] fp16, Q rotated and scaled by the pre-pass; null = the kernel rotates Q tiles itself
     Strides sq, sk, sv, so, sdo, sdq, sdk, sdv;   // strides of q, k, v, o (forward output or backward input), dO, dq, dk, dv

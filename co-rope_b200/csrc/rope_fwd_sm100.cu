@@ -49,7 +49,7 @@ constexpr int kLaunchRegs = 72;        // 65536 / 896 rounded down to a multiple
 // rotate Q once per item and the registers serve the softmax groups better: 0.387 against 0.401 ms.
 constexpr int kRegsCtl = 40, kRegsRot = 56, kRegsSmx = 88;
 static_assert(128 * (kRegsCtl + 2 * kRegsRot + 4 * kRegsSmx) <= kThreads * kLaunchRegs, "register budget");
-constexpr int kHeadChunk = 8;
+constexpr int kHeadChunk = 8;   // heads per chunk of the work order for N >= 4096 (more for shorter heads, see head_chunk_for)
 constexpr int kItemSlots = 4;
 constexpr int kItemReaders = 1 + 1 + 8 + 16;   // V producer, MMA warp, rotation warps, softmax warps: one arrival each
 
@@ -82,15 +82,20 @@ static_assert(kSmemBytes <= 232448, "shared memory budget");  // + alignment sla
 struct WorkItem {
     int t, bh;
 };
-__device__ __forceinline__ WorkItem work_item(int w, int n_qt, int BH) {
-    const int chunk_items = kHeadChunk * n_qt;
+__device__ __forceinline__ WorkItem work_item(int w, int n_qt, int BH, int head_chunk) {
+    const int chunk_items = head_chunk * n_qt;
     const int chunk = w / chunk_items, within = w % chunk_items;
-    const int heads_here = min(kHeadChunk, BH - chunk * kHeadChunk);
+    const int heads_here = min(head_chunk, BH - chunk * head_chunk);
     WorkItem it;
     it.t = n_qt - 1 - within / heads_here;
-    it.bh = chunk * kHeadChunk + within % heads_here;
+    it.bh = chunk * head_chunk + within % heads_here;
     return it;
 }
+// Heads per chunk: a chunk's K and V should stay in L2 while its items are in flight, and a chunk should hold a few items per
+// SM, or the light tail of one chunk and the heavy head of the next leave SMs idle (a list-scheduling simulation of the
+// Llama-70B-1K shape: 22 % over the ideal makespan with chunks of 8 heads, 8 % with 64).  8 heads of 4096 rows are 16 MB of
+// K + V; shorter heads get proportionally more heads per chunk.
+inline int head_chunk_for(int N) { return N >= 4096 ? kHeadChunk : kHeadChunk * (4096 / (N < 128 ? 128 : N)); }
 
 // Consumer side of the item ring: the n-th item of this CTA, or -1 when there is none left (or a wait gave up).
 // Warp roles call it with all 32 lanes (one arrival per warp); the V producer calls it from its single thread.
@@ -214,7 +219,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                     item_ring[slot] = w;
                     mbar_arrive(&bars[ITEM_FULL + slot]);
                     if (w < 0) break;
-                    const WorkItem wi = work_item(w, n_qt, BH);
+                    const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
                     const int nk = causal ? 2 * wi.t + 2 : nk_all;
                     const int qb = wi.bh / p.H, qh = wi.bh % p.H;                       // batch and head coordinates of the 4-D maps
                     const int kb = (wi.bh / G) / p.Hkv, kh = (wi.bh / G) % p.Hkv;
@@ -244,7 +249,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 for (int n = 0; ok; ++n) {
                     const int w = fetch_item(bars, item_ring, n, lane, false, p.status, abort_flag);
                     if (w < 0) break;
-                    const WorkItem wi = work_item(w, n_qt, BH);
+                    const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
                     const int nk = causal ? 2 * wi.t + 2 : nk_all;
                     const int kb = (wi.bh / G) / p.Hkv, kh = (wi.bh / G) % p.Hkv;
                     for (int j = 0; j < nk; ++j, ++gv) {
@@ -288,7 +293,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
             for (int n = 0; ok; ++n) {
                 const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
                 if (w < 0) break;
-                const WorkItem wi = work_item(w, n_qt, BH);
+                const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
                 const int nk = causal ? 2 * wi.t + 2 : nk_all, nk0 = causal ? nk - 1 : nk;
                 // first K tile of the item: S0 = Q0 K^T, S1 = Q1 K^T
                 if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
@@ -358,7 +363,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         for (int n = 0; ok; ++n) {
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
             if (w < 0) break;
-            const WorkItem wi = work_item(w, n_qt, BH);
+            const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
             const int nk = causal ? 2 * wi.t + 2 : nk_all;
             for (int i = 0; i < 2 && ok; ++i) {
                 load_table_regs<kHalfRows>(tr, p.packed_tab + (size_t)(wi.t * 2 * kBM + i * kBM + rg * kHalfRows) * (kD / 2), tid);
@@ -404,7 +409,7 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
         for (int n = 0; ok; ++n) {
             const int w = fetch_item(bars, item_ring, n, lane, true, p.status, abort_flag);
             if (w < 0) break;
-            const WorkItem wi = work_item(w, n_qt, BH);
+            const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
             const int nk_i = causal ? 2 * wi.t + 1 + wg : nk_all;
             float m = -INFINITY, l = 0.f;
             for (int j = 0; j < nk_i; ++j, ++gs) {
@@ -539,6 +544,7 @@ int launch_t(const RopeParams& p, int dtype, cudaStream_t s) {
         return e;
     if (int e = encode_rows_map(&mv, &fv, p.v, p.B, p.Hkv, p.N, kD, p.sv, kBN, 64, dtype)) return e;
     pp.flat_q = fq; pp.flat_k = fk; pp.flat_v = fv;
+    pp.head_chunk = head_chunk_for(p.N);
     const bool plain = p.H == p.Hkv && fq && fk && fv && rows_collapse(p.so, p.H, p.N);
     auto kern = plain ? rope_fwd_sm100_kernel<T, true> : rope_fwd_sm100_kernel<T, false>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
