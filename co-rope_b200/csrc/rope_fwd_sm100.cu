@@ -295,31 +295,24 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                 if (w < 0) break;
                 const WorkItem wi = work_item(w, n_qt, BH, p.head_chunk);
                 const int nk = causal ? 2 * wi.t + 2 : nk_all, nk0 = causal ? nk - 1 : nk;
-                // first K tile of the item: S0 = Q0 K^T, S1 = Q1 K^T
-                if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
-                if (!(ok = mbar_wait_warp(&bars[kReadyBar + gk % kKStages], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
-                tc_fence_after();
-                issue_qk(0, gk % kKStages);
-                if (leader) umma_commit(&bars[S_FULL + 0]);
-                if (!(ok = mbar_wait_warp(&bars[Q_ROT + 1], n & 1, p.status, Q_ROT + 1, abort_flag))) break;
-                tc_fence_after();
-                issue_qk(1, gk % kKStages);
-                if (leader) umma_commit(&bars[S_FULL + 1]);
-                if (leader) umma_commit(&bars[K_EMPTY + gk % kKStages]);
-                if (nk0 == 1 && leader) umma_commit(&bars[Q_EMPTY + 0]);      // Q0 sees a single K tile: that was its last use
-                ++gk;
-                for (int j = 0; j < nk; ++j, ++gv) {
-                    const int vs = gv % kVStages;
-                    const int ks1 = gk % kKStages;
+                // One loop body for the whole item, the first tile included (j = -1 only issues the two Q K^T of tile 0): the
+                // instructions that issue the MMAs then exist once (1 % faster than a peeled first tile at the Llama-7B-4K shape).
+                for (int j = -1; j < nk; ++j) {
                     const bool have_next = j + 1 < nk;
-                    if (!(ok = mbar_wait_warp(&bars[kVReadyBar + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
-                    if (j < nk0) {
-                        if (!(ok = mbar_wait_warp(&bars[P_FULL + 0], s0 & 1, p.status, P_FULL, abort_flag))) break;
-                        if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 0], (n - 1) & 1, p.status, O_FREE, abort_flag))) break;
-                        tc_fence_after();
-                        issue_pv(0, vs, j > 0);
-                        if (leader) umma_commit(&bars[O_FULL + 0]);
-                        ++s0;
+                    const int ks1 = gk % kKStages;
+                    const int vs = gv % kVStages;
+                    if (j >= 0) {
+                        if (!(ok = mbar_wait_warp(&bars[kVReadyBar + vs], (gv / kVStages) & 1, p.status, V_FULL, abort_flag))) break;
+                        if (j < nk0) {
+                            if (!(ok = mbar_wait_warp(&bars[P_FULL + 0], s0 & 1, p.status, P_FULL, abort_flag))) break;
+                            if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 0], (n - 1) & 1, p.status, O_FREE, abort_flag))) break;
+                            tc_fence_after();
+                            issue_pv(0, vs, j > 0);
+                            if (leader) umma_commit(&bars[O_FULL + 0]);
+                            ++s0;
+                        }
+                    } else {
+                        if (!(ok = mbar_wait_warp(&bars[Q_ROT + 0], n & 1, p.status, Q_ROT, abort_flag))) break;
                     }
                     if (have_next) {
                         if (!(ok = mbar_wait_warp(&bars[kReadyBar + ks1], (gk / kKStages) & 1, p.status, K_ROT, abort_flag))) break;
@@ -330,13 +323,19 @@ rope_fwd_sm100_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_con
                             if (j + 2 == nk0 && leader) umma_commit(&bars[Q_EMPTY + 0]);   // last use of Q0 in this item
                         }
                     }
-                    if (!(ok = mbar_wait_warp(&bars[P_FULL + 1], s1 & 1, p.status, P_FULL + 1, abort_flag))) break;
-                    if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 1], (n - 1) & 1, p.status, O_FREE + 1, abort_flag))) break;
-                    tc_fence_after();
-                    issue_pv(1, vs, j > 0);
-                    if (leader) umma_commit(&bars[O_FULL + 1]);
-                    if (leader) umma_commit(&bars[V_EMPTY + vs]);
-                    ++s1;
+                    if (j >= 0) {
+                        if (!(ok = mbar_wait_warp(&bars[P_FULL + 1], s1 & 1, p.status, P_FULL + 1, abort_flag))) break;
+                        if (j == 0 && n > 0 && !(ok = mbar_wait_warp(&bars[O_FREE + 1], (n - 1) & 1, p.status, O_FREE + 1, abort_flag))) break;
+                        tc_fence_after();
+                        issue_pv(1, vs, j > 0);
+                        if (leader) umma_commit(&bars[O_FULL + 1]);
+                        if (leader) umma_commit(&bars[V_EMPTY + vs]);
+                        ++s1;
+                        ++gv;
+                    } else {
+                        if (!(ok = mbar_wait_warp(&bars[Q_ROT + 1], n & 1, p.status, Q_ROT + 1, abort_flag))) break;
+                        tc_fence_after();
+                    }
                     if (have_next) {
                         issue_qk(1, ks1);
                         if (leader) umma_commit(&bars[S_FULL + 1]);
