@@ -66,6 +66,9 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t& r0, uint32_t& r1, uint32_t
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
                  : "r"(smem_u32(smem_row)));
 }
+__device__ __forceinline__ void red_add_v4(float* gptr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(gptr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ void red_add_v2(float* gptr, float a, float b) {
     asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(gptr), "f"(a), "f"(b) : "memory");
 }
@@ -435,11 +438,19 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             }
             const int i_last = i0 + kRows - 1;
             const int ka = j0 + mb * 16 + h, kb = ka + 8;
+            // 16-byte reductions: the lanes c and c ^ 1 hold neighbouring column pairs of both rows; the even one takes row ka of
+            // both, the odd one row kb
 #pragma unroll
             for (int n = 0; n < 8; ++n) {
-                const int d = nh * 64 + n * 8 + 2 * c;
-                if (ka <= i_last) red_add_v2(dv_acc + (size_t)ka * kD + d, acc[n][0], acc[n][1]);
-                if (kb <= i_last) red_add_v2(dv_acc + (size_t)kb * kD + d, acc[n][2], acc[n][3]);
+                const bool odd = c & 1;
+                const float s0 = odd ? acc[n][0] : acc[n][2], s1 = odd ? acc[n][1] : acc[n][3];   // what the partner needs
+                const float r0 = __shfl_xor_sync(0xffffffffu, s0, 1), r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+                const int d = nh * 64 + n * 8 + 2 * (c & 2);
+                if (!odd) {
+                    if (ka <= i_last) red_add_v4(dv_acc + (size_t)ka * kD + d, acc[n][0], acc[n][1], r0, r1);
+                } else {
+                    if (kb <= i_last) red_add_v4(dv_acc + (size_t)kb * kD + d, r0, r1, acc[n][2], acc[n][3]);
+                }
             }
             // leader terms of the tile, summed over the CTA's rows by MMAs (K dimension = row):
             //   dk[key][d] += sum_i graw_ik qL_i[d]   -- the same (keys, d) block of the output as above
@@ -477,17 +488,18 @@ __global__ void __launch_bounds__(kThreads, 1) corope_bwd_mma_kernel(GqaParams p
             }
             // the shared dK tile goes to the global accumulator and is cleared for the next tile
             __syncthreads();
-            for (int idx = tid; idx < kKT * 64; idx += kThreads) {
-                const int r = idx >> 6, d2 = (idx & 63) * 2;
-                int* src = dk_t + r * kDkStride + d2;
+            for (int idx = tid; idx < kKT * 32; idx += kThreads) {
+                const int r = idx >> 5, d4 = (idx & 31) * 4;
+                int* src = dk_t + r * kDkStride + d4;
                 // rows of the CTA that did not skip this key's 16-key block: each left one bias in every slot of the block
                 const int cnt = min(kRows, max(0, i_last + 1 - (j0 + (r & ~15))));
                 const unsigned bias = (unsigned)cnt * (unsigned)kDkBias;   // modulo 2^32, like the sums themselves
+                const int4 v = *reinterpret_cast<const int4*>(src);
                 if (j0 + r <= i_last)
-                    red_add_v2(dk_acc + (size_t)(j0 + r) * kD + d2, (float)(int)((unsigned)src[0] - bias) * (1.f / kDkScale),
-                               (float)(int)((unsigned)src[1] - bias) * (1.f / kDkScale));
-                src[0] = 0;
-                src[1] = 0;
+                    red_add_v4(dk_acc + (size_t)(j0 + r) * kD + d4, (float)(int)((unsigned)v.x - bias) * (1.f / kDkScale),
+                               (float)(int)((unsigned)v.y - bias) * (1.f / kDkScale), (float)(int)((unsigned)v.z - bias) * (1.f / kDkScale),
+                               (float)(int)((unsigned)v.w - bias) * (1.f / kDkScale));
+                *reinterpret_cast<int4*>(src) = make_int4(0, 0, 0, 0);
             }
         }
     }
