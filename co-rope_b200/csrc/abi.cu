@@ -295,9 +295,8 @@ int rope_fwd_impl(const void* q, const void* k, const void* v, Rotation rot, voi
         void* vp = (char*)workspace + w.pad[1];
         void* op = (char*)workspace + w.pad[2];   // first the padded k (until it is rotated), then the padded output
         if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
-        if (int e = launch_pad_d64(q, p.sq, qp, B, Hq, N, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, p.sk, op, B, Hkv, N, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, p.sv, vp, B, Hkv, N, 0, dtype, s)) return e;
+        const PadSpec in3[3] = {{q, qp, p.sq, Hq, 1}, {k, op, p.sk, Hkv, 1}, {v, vp, p.sv, Hkv, 0}};
+        if (int e = launch_pad_d64_many(3, in3, B, N, false, dtype, s)) return e;
         if (int e = launch_rope_prerotate(op, contiguous_strides(Hkv, N, 128), k_rot, tab, B, Hkv, N, 1.0f, dtype, s)) return e;
         const Strides so_caller = p.so;
         p.q = qp; p.k = op; p.v = vp; p.out_o = op; p.D = 128;
@@ -369,11 +368,9 @@ int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, co
         void* dkp = (char*)workspace + w.pad[3];   // first the padded q (until it is rotated), then the padded dk
         void* dvp = (char*)workspace + w.pad[4];
         if (int e = launch_pack_tables(p.cos, p.sin, p.table_stride, tab, N, 64, s, 32)) return e;
-        if (int e = launch_pad_d64(q, p.sq, dkp, B, Hq, N, 1, dtype, s)) return e;
+        const PadSpec in4[4] = {{q, dkp, p.sq, Hq, 1}, {k, kp, p.sk, Hkv, 1}, {v, vp, p.sv, Hkv, 0}, {d_o, dop, p.sdo, Hq, 0}};
+        if (int e = launch_pad_d64_many(4, in4, B, N, false, dtype, s)) return e;
         if (int e = launch_rope_prerotate(dkp, contiguous_strides(Hq, N, 128), q_rot, tab, B, Hq, N, sm_scale * kLog2e, dtype, s)) return e;
-        if (int e = launch_pad_d64(k, p.sk, kp, B, Hkv, N, 1, dtype, s)) return e;
-        if (int e = launch_pad_d64(v, p.sv, vp, B, Hkv, N, 0, dtype, s)) return e;
-        if (int e = launch_pad_d64(d_o, p.sdo, dop, B, Hq, N, 0, dtype, s)) return e;
         const Strides sdq_caller = p.sdq, sdk_caller = p.sdk, sdv_caller = p.sdv;
         p.q = dkp; p.k = kp; p.v = vp; p.d_o = dop; p.dq = dop; p.dk = dkp; p.dv = dvp; p.D = 128;
         set_strides(p, nullptr, Hq, Hkv, N, 128);   // the padded copies are contiguous
@@ -383,9 +380,8 @@ int rope_bwd_impl(const void* q, const void* k, const void* v, const void* o, co
         p.q_rot = q_rot;
         g_last_family[kFamBwd] = 1;
         if (int e = launch_rope_bwd_tc(p, dtype, s)) return e;
-        if (int e = launch_unpad_d64(dop, dq, sdq_caller, B, Hq, N, 1, dtype, s)) return e;
-        if (int e = launch_unpad_d64(dkp, dk, sdk_caller, B, Hkv, N, 1, dtype, s)) return e;
-        return launch_unpad_d64(dvp, dv, sdv_caller, B, Hkv, N, 0, dtype, s);
+        const PadSpec out3[3] = {{dq, dop, sdq_caller, Hq, 1}, {dk, dkp, sdk_caller, Hkv, 1}, {dv, dvp, sdv_caller, Hkv, 0}};
+        return launch_pad_d64_many(3, out3, B, N, true, dtype, s);
     }
     if (tc_direct) {
         uint32_t* tab = reinterpret_cast<uint32_t*>((char*)workspace + w.packed_tab);

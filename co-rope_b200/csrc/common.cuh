@@ -601,8 +601,16 @@ int launch_pack_tables(const float* cos, const float* sin, int64_t stride, uint3
 // cos / sin tables [N, half_d] fp32 for positions 0 .. N-1 from per-pair frequencies: angle = float(n) * inv_freq[d]
 int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, int N, int half_d, cudaStream_t s);
 // x / out: [B, H, N, 64] with strides st (the padded side is contiguous [B*H*N, 128])
-int launch_pad_d64(const void* x, const Strides& st, void* out, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s);
 int launch_unpad_d64(const void* xp, void* out, const Strides& st, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s);
+// one tensor of a batched pad / un-pad launch: the caller's [B, H, N, 64] tensor with its strides and its padded copy
+struct PadSpec {
+    const void* tensor;   // written by an un-pad
+    void* padded;
+    Strides strides;
+    int H;
+    int rope_layout;
+};
+int launch_pad_d64_many(int n, const PadSpec* specs, int B, int N, bool unpad, int dtype, cudaStream_t s);
 int launch_rope_prerotate(const void* x, const Strides& st, void* out_f16, const uint32_t* packed, int B, int H, int N, float scale,
                           int dtype, cudaStream_t s);   // H = heads of x; out is contiguous [B*H*N, 128]
 bool rope_fwd_tc_supported(int B, int H, int N, int D, int dtype, int causal);

@@ -402,23 +402,6 @@ __global__ void synth_tables_kernel(const float* __restrict__ inv_freq, float* _
 // D = 128 kernels: first half of the row (32 columns) to columns 0..31, second half to columns 64..95; "plain" layout
 // puts the 64 columns first.  Everything else is zero, so dot products and rotations are unchanged.
 template <typename T>
-__global__ void __launch_bounds__(256) pad_d64_kernel(const T* __restrict__ x, T* __restrict__ out, size_t rows, int rope_layout, RowAddr ax) {
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16 output chunks
-    if (idx >= rows * 16) return;
-    const size_t r = idx >> 4;
-    const int c = (int)(idx & 15);
-    int src = -1;
-    if (rope_layout) {
-        if (c < 4) src = c;
-        else if (c >= 8 && c < 12) src = c - 4;
-    } else if (c < 8) {
-        src = c;
-    }
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (src >= 0) v = *reinterpret_cast<const uint4*>(x + flat_row_offset(ax, r) + src * 8);
-    *reinterpret_cast<uint4*>(out + r * 128 + c * 8) = v;
-}
-template <typename T>
 __global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp, T* __restrict__ out, size_t rows, int rope_layout, RowAddr ax) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 8 output chunks
     if (idx >= rows * 8) return;
@@ -426,6 +409,48 @@ __global__ void __launch_bounds__(256) unpad_d64_kernel(const T* __restrict__ xp
     const int c = (int)(idx & 7);
     const int src = rope_layout ? (c < 4 ? c : c + 4) : c;
     *reinterpret_cast<uint4*>(out + flat_row_offset(ax, r) + c * 8) = *reinterpret_cast<const uint4*>(xp + r * 128 + src * 8);
+}
+
+// Up to four tensors per launch (blockIdx.y picks the tensor): the D = 64 problems that take this path are small, and their
+// time is made of launches.
+struct PadJob {
+    const void* src;
+    void* dst;
+    size_t rows;
+    int rope_layout;
+    RowAddr addr;
+};
+struct PadJobs {
+    PadJob j[4];
+};
+template <typename T>
+__global__ void __launch_bounds__(256) pad_d64_many_kernel(PadJobs jobs) {
+    const PadJob& jb = jobs.j[blockIdx.y];
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 16 output chunks
+    if (idx >= jb.rows * 16) return;
+    const size_t r = idx >> 4;
+    const int c = (int)(idx & 15);
+    int src = -1;
+    if (jb.rope_layout) {
+        if (c < 4) src = c;
+        else if (c >= 8 && c < 12) src = c - 4;
+    } else if (c < 8) {
+        src = c;
+    }
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (src >= 0) v = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(jb.src) + flat_row_offset(jb.addr, r) + src * 8);
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(jb.dst) + r * 128 + c * 8) = v;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) unpad_d64_many_kernel(PadJobs jobs) {
+    const PadJob& jb = jobs.j[blockIdx.y];   // src = padded copy, dst = the caller's tensor
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // rows * 8 output chunks
+    if (idx >= jb.rows * 8) return;
+    const size_t r = idx >> 3;
+    const int c = (int)(idx & 7);
+    const int src = jb.rope_layout ? (c < 4 ? c : c + 4) : c;
+    *reinterpret_cast<uint4*>(reinterpret_cast<T*>(jb.dst) + flat_row_offset(jb.addr, r) + c * 8) =
+        *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(jb.src) + r * 128 + src * 8);
 }
 
 // Rotation as a pass of its own, for the tensor-core kernels at D = 128: out[r, :] = rot(x[r, :]) * scale as fp16, with the
@@ -633,13 +658,27 @@ int launch_synth_tables(const float* inv_freq, float* cos_out, float* sin_out, i
     return (int)cudaGetLastError();
 }
 
-int launch_pad_d64(const void* x, const Strides& st, void* out, int B, int H, int N, int rope_layout, int dtype, cudaStream_t s) {
-    const size_t rows = (size_t)B * H * N;
-    const unsigned grid = (unsigned)((rows * 16 + 255) / 256);
-    if (dtype == COROPE_DTYPE_BF16)
-        pad_d64_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, rows, rope_layout, row_addr(st, H, N));
-    else
-        pad_d64_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (__half*)out, rows, rope_layout, row_addr(st, H, N));
+// n <= 4 tensors [B, H_i, N, 64] <-> their zero-padded [B, H_i, N, 128] copies in one launch (unpad: the other direction)
+int launch_pad_d64_many(int n, const PadSpec* specs, int B, int N, bool unpad, int dtype, cudaStream_t s) {
+    PadJobs jobs{};
+    size_t max_rows = 0;
+    for (int i = 0; i < n; ++i) {
+        const size_t rows = (size_t)B * specs[i].H * N;
+        jobs.j[i].src = unpad ? specs[i].padded : specs[i].tensor;
+        jobs.j[i].dst = unpad ? const_cast<void*>(specs[i].tensor) : specs[i].padded;
+        jobs.j[i].rows = rows;
+        jobs.j[i].rope_layout = specs[i].rope_layout;
+        jobs.j[i].addr = row_addr(specs[i].strides, specs[i].H, N);
+        max_rows = rows > max_rows ? rows : max_rows;
+    }
+    const dim3 grid((unsigned)((max_rows * (unpad ? 8 : 16) + 255) / 256), (unsigned)n);
+    if (dtype == COROPE_DTYPE_BF16) {
+        if (unpad) unpad_d64_many_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(jobs);
+        else pad_d64_many_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(jobs);
+    } else {
+        if (unpad) unpad_d64_many_kernel<__half><<<grid, 256, 0, s>>>(jobs);
+        else pad_d64_many_kernel<__half><<<grid, 256, 0, s>>>(jobs);
+    }
     count_launch();
     return (int)cudaGetLastError();
 }
