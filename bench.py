@@ -292,6 +292,15 @@ def run_sweep(args):
     pkg = importlib.import_module("co-rope_b200")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than the 126 MB L2
     tri = args.sweep_triton
+    # bring the GPU out of its idle clocks before the first (smallest) shape is timed
+    wq, wk, wv, wdo, wcos, wsin = _sweep_inputs(2, 32, 2048, 128, dev)
+    wcos, wsin = wcos[:, :64].contiguous(), wsin[:, :64].contiguous()
+    t_w = time.time()
+    while time.time() - t_w < 0.5:
+        for _ in range(20):
+            pkg.fused_rope_attention(wq, wk, wv, True, 0.5, wcos, wsin)
+        torch.cuda.synchronize()
+    del wq, wk, wv, wdo, wcos, wsin
     print("| configuration (B, H, N, D) | forward | backward | kernels |" + (" reference Triton forward | reference Triton backward | ours / Triton (fwd, bwd) |" if tri else ""))
     print("|---|---|---|---|" + ("---|---|---|" if tri else ""))
     for B, H, N, D, name in SWEEP_SHAPES:
